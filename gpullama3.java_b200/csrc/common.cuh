@@ -1,0 +1,96 @@
+// Shared helpers of the sm_100a kernel libraries.
+//
+// Every library exports plain C functions ("extern \"C\" int b200_*") that take raw device
+// pointers, sizes and a cudaStream_t, launch on that stream and return the cudaError_t of the
+// launch as an int (0 = success).  Nothing here allocates device memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+// Storage types a tensor may have.  The codes are part of the C ABI (python passes them).
+enum DType : int { kF32 = 0, kBF16 = 1 };
+
+// Tokens of one cache page.  A sequence's keys and values live in pages of this many positions.
+constexpr int kPageTokens = 64;
+
+// Error codes returned for arguments a kernel refuses (distinct from cudaError_t values).
+constexpr int kErrBadArgument = 10001;
+constexpr int kErrUnsupportedSize = 10002;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a CTA of up to 1024 threads; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+inline int launch_status() { return (int)cudaPeekAtLastError(); }
+
+}  // namespace b200
+
+// Calls `body` with `T` bound to the storage type of `code`; unknown codes return kErrBadArgument.
+#define B200_DISPATCH_DTYPE(code, T, ...)                                   \
+    do {                                                                    \
+        if ((code) == b200::kF32) { using T = float; __VA_ARGS__; }         \
+        else if ((code) == b200::kBF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return b200::kErrBadArgument;                                  \
+    } while (0)
+
+// Same as B200_DISPATCH_DTYPE; a second and third name because a macro cannot expand inside itself.
+#define B200_DISPATCH_DTYPE2(code, T, ...)                                  \
+    do {                                                                    \
+        if ((code) == b200::kF32) { using T = float; __VA_ARGS__; }         \
+        else if ((code) == b200::kBF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return b200::kErrBadArgument;                                  \
+    } while (0)
+#define B200_DISPATCH_DTYPE3(code, T, ...)                                  \
+    do {                                                                    \
+        if ((code) == b200::kF32) { using T = float; __VA_ARGS__; }         \
+        else if ((code) == b200::kBF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+        else return b200::kErrBadArgument;                                  \
+    } while (0)

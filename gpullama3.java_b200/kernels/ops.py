@@ -1,0 +1,180 @@
+"""Python faces of the CUDA kernels: each function checks its tensors and calls one exported C
+function on torch's current stream.  There is no other implementation behind these names: on a
+machine without a GPU or without the compiled libraries they raise."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .build import KernelBuildError, library
+
+F32, BF16 = 0, 1
+PAGE_TOKENS = 64  # must equal b200::kPageTokens
+
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or its launch failed."""
+
+
+_ERRORS = {
+    10001: "bad argument",
+    10002: "unsupported size",
+    10003: "scratch too small",
+}
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+# C signatures: library, then argument types (the trailing stream is added for all)
+_SIGNATURES = {
+    "b200_embed_gather": ("embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "b200_rmsnorm": ("norm", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float]),
+    "b200_rope_cache_write": ("rope_cache", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_attention_paged": ("attention_generic", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+    "b200_gemm_generic": ("gemm_generic", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                           c_int, c_int, c_int, c_int]),
+    "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
+    "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
+}
+
+
+def _fn(name: str):
+    f = _functions.get(name)
+    if f is None:
+        lib_name, argtypes = _SIGNATURES[name]
+        lib = library(lib_name)
+        try:
+            f = getattr(lib, name)
+        except AttributeError as e:
+            raise KernelBuildError(f"{name} is not exported by the {lib_name} kernel library") from e
+        f.argtypes = list(argtypes) + [c_void_p]
+        f.restype = c_int
+        _functions[name] = f
+    return f
+
+
+def _check(status: int, name: str) -> None:
+    if status != 0:
+        what = _ERRORS.get(status)
+        if what is None:
+            what = f"CUDA error {status}"
+        raise KernelError(f"{name}: {what}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels store float32 or bfloat16, not {dtype}") from None
+
+
+def _dev(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+
+
+# --------------------------------------------------------------------------- embedding, norm
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[tokens[t]] into the float32 residual stream.  tokens int32 [T]."""
+    _dev(table, tokens, out)
+    assert out.dtype == torch.float32 and tokens.dtype == torch.int32
+    assert table.is_contiguous() and out.is_contiguous()
+    n, dim = out.shape
+    _check(_fn("b200_embed_gather")(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(),
+                                    n, dim, table.shape[0], _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> None:
+    """out[r] = weight * x[rows[r]] / sqrt(mean(x^2) + eps).  x float32 [T, dim]."""
+    _dev(x, weight, out, rows)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and weight.is_contiguous()
+    n_rows, dim = out.shape
+    assert x.shape[1] == dim and weight.numel() == dim
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    _check(_fn("b200_rmsnorm")(x.data_ptr(), weight.data_ptr(), dtype_code(weight.dtype), out.data_ptr(),
+                               dtype_code(out.dtype), rows.data_ptr() if rows is not None else None, n_rows, dim,
+                               float(eps), _stream()), "rmsnorm")
+
+
+# --------------------------------------------------------------------------- position encoding + cache write
+def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor, page_table: torch.Tensor,
+                     inv_freq: torch.Tensor, k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, n_heads: int,
+                     n_kv_heads: int, head_dim: int, rotary_dim: int, pairing: int, write_cache: bool = True) -> None:
+    """Rotate the queries of ``qkv`` [T, (H + 2 KVH) D] in place; write rotated keys and the values
+    into the cache pages of their positions."""
+    _dev(qkv, positions, seq_ids, page_table, inv_freq, k_pool, v_pool)
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(rotary_dim // 2, 0)
+    assert page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.is_contiguous()
+    if write_cache:
+        assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
+        assert k_pool.is_contiguous() and v_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    _check(_fn("b200_rope_cache_write")(
+        qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], inv_freq.data_ptr(), k_pool.data_ptr() if write_cache else None,
+        v_pool.data_ptr() if write_cache else None, qkv.shape[0], n_heads, n_kv_heads, head_dim, rotary_dim, pairing,
+        1 if write_cache else 0, _stream()), "rope_cache_write")
+
+
+# --------------------------------------------------------------------------- attention
+def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, positions: torch.Tensor,
+                    seq_ids: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                    n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0) -> None:
+    """Causal grouped-query attention of every token of ``q`` over the cached keys 0..position of
+    its sequence.  q: rows of ``q_row_stride`` elements whose first H*D are the rotated queries."""
+    _dev(q, out, positions, seq_ids, page_table, k_pool, v_pool)
+    assert out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.dtype == q.dtype == k_pool.dtype
+    assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    _check(_fn("b200_attention_paged")(
+        q.data_ptr(), q_row_stride, out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(), seq_ids.data_ptr(),
+        page_table.data_ptr(), page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), out.shape[0], n_heads,
+        n_kv_heads, head_dim, int(window), _stream()), "attention_paged")
+
+
+# --------------------------------------------------------------------------- matrix products
+EPILOGUE_STORE, EPILOGUE_RESIDUAL_ADD, EPILOGUE_GATED_SILU = 0, 1, 2
+
+
+def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+    """c = a @ w.T (store), c += a @ w.T (residual add, c float32) or c = silu(gate) * up with
+    gate/up rows interleaved in w.  32-bit FMA accumulation, no tensor cores."""
+    _dev(a, w, c)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
+    assert c.shape[0] == M and c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    _check(_fn("b200_gemm_generic")(
+        a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), w.stride(0), c.data_ptr(),
+        dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_generic")
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of logits[r] (float32 [R, V]); out int32 [R]."""
+    _dev(logits, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _check(_fn("b200_argmax_rows")(logits.data_ptr(), logits.stride(0), out.data_ptr(), logits.shape[0],
+                                   logits.shape[1], _stream()), "argmax_rows")
+
+
+def sample_rows(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor, temperature: float,
+                top_p: float) -> None:
+    """Temperature softmax and inverse-CDF draw (nucleus when 0 < top_p < 1) per row."""
+    _dev(logits, uniforms, out)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert uniforms.dtype == torch.float32 and uniforms.numel() == logits.shape[0]
+    _check(_fn("b200_sample_rows")(logits.data_ptr(), logits.stride(0), uniforms.data_ptr(), out.data_ptr(),
+                                   logits.shape[0], logits.shape[1], float(temperature), float(top_p), _stream()),
+           "sample_rows")

@@ -1,0 +1,57 @@
+"""Grouped-query causal attention over the paged cache: the mixer of the Llama 3 decoder.
+
+One run: project the normalised input to queries, keys and values with one fused weight
+(inference/InferenceCore.java:78-80 of the reference project computes the three separately),
+rotate queries and keys and store keys and values at each token's position (:83-101), attend over
+everything the sequence has cached up to each token (:106-145), project back and add to the
+residual stream (:148-151).  Sizes, the position encoding and an optional window are parameters."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.sequence_cache import KVCacheNeed, KVView
+from ..kernels import ops
+from ..weights.loader import ParamSpec
+from .base import Mixer, PositionEncoding, StepContext, register_mixer
+from .linear import Linear
+
+
+class GroupedQueryAttention(Mixer):
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
+                 window: int | None = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
+        self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
+        self.position, self.window = position, window
+        self.q_dim, self.kv_dim = n_heads * head_dim, n_kv_heads * head_dim
+        self.qkv: Linear | None = None
+        self.o: Linear | None = None
+
+    def parameters(self):
+        return {"q": ParamSpec((self.q_dim, self.hidden_size)), "k": ParamSpec((self.kv_dim, self.hidden_size)),
+                "v": ParamSpec((self.kv_dim, self.hidden_size)), "o": ParamSpec((self.hidden_size, self.q_dim))}
+
+    def cache_need(self):
+        return KVCacheNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def load(self, tensors, dtype, device):
+        q, k, v, o = (tensors[n].to(device) for n in ("q", "k", "v", "o"))
+        common = torch.float32 if (dtype == torch.float32 or torch.float32 in (q.dtype, k.dtype, v.dtype)) else q.dtype
+        self.qkv = Linear(torch.cat([q.to(common), k.to(common), v.to(common)], dim=0).contiguous())
+        self.o = Linear(o.to(torch.float32 if dtype == torch.float32 else o.dtype).contiguous())
+
+    def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True):
+        qkv = self.qkv.store(x, ctx.dtype)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
+        table = ctx.page_tables[cache.group]
+        ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
+                             cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                             self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
+        out = torch.empty((x.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
+        from ..kernels import fast
+        if not fast.try_attention(qkv, out, ctx, table, cache, self):
+            ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
+                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
+        self.o.add_to(out, residual)
+
+
+register_mixer("attention", GroupedQueryAttention)

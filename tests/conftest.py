@@ -1,0 +1,96 @@
+"""Shared fixtures: the two tiny Llama 3 configurations, random model folders, tolerances."""
+from __future__ import annotations
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (str(ROOT), str(ROOT / "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# The two tiny configurations differ in every size and option: layers, width, heads and groups
+# (4/2 against 3/1), head size, feed-forward width, vocabulary, rope base and scaling, eps, tying,
+# norm weights (ones against 1 + N(0, 0.1)).
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 192, "vocab_size": 256, "rope_theta": 10000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 128,
+    "eos_token_id": 7,
+}
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 256, "vocab_size": 384, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 32},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 256, "eos_token_id": [3, 5],
+}
+TINY = {"A": (TINY_A, 0.0), "B": (TINY_B, 0.1)}  # name -> (config.json, std of the norm weights around 1)
+
+
+def make_model_dir(tmp_path: Path, config_json: dict, seed: int = 0, norm_std: float = 0.0,
+                   dtype=torch.bfloat16, norm_dtype=None, **overrides) -> Path:
+    """Write a random model folder for ``config_json`` (with overrides) and return its path."""
+    from gpullama3.java_b200.config import config_from_dict
+    from gpullama3.java_b200.weights import write_random_model
+
+    d = dict(config_json)
+    d.update(overrides)
+    cfg = config_from_dict(d)
+    out = tmp_path / f"model_{abs(hash(json.dumps(d, sort_keys=True))) % 10**8}_{seed}"
+    write_random_model(cfg, seed, out, dtype=dtype, norm_std=norm_std, norm_dtype=norm_dtype)
+    return out
+
+
+def plain_inputs(model_dir: Path):
+    """config.json as a dict and the weights as float32 tensors by checkpoint name, read with the
+    safetensors package (not with the product's reader)."""
+    from safetensors.torch import load_file
+
+    cfg = json.loads((Path(model_dir) / "config.json").read_text())
+    weights = {k: v.to(torch.float32) for k, v in load_file(str(Path(model_dir) / "model.safetensors")).items()}
+    return cfg, weights
+
+
+# Tolerances, fixed once.  float32: accumulation-order noise only.  bfloat16: the plain
+# implementation rounds activations to bfloat16 at the same places as the engine, what remains are
+# roundings that fall on the other side of a tie (2^-8 relative on single values).
+BF16_EPS = 2.0 ** -8
+
+
+def assert_close_logits(got: torch.Tensor, ref: torch.Tensor, dtype, what: str = "") -> None:
+    got = got.detach().to("cpu", torch.float32)
+    ref = ref.detach().to("cpu", torch.float32)
+    assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    scale = float(ref.abs().max()) + 1e-30
+    err = (got - ref).abs()
+    if dtype == torch.float32:
+        assert float(err.max()) <= 2e-5 * scale, f"{what}: max err {float(err.max()):.3e} vs scale {scale:.3e}"
+    else:
+        assert float(err.max()) <= 4 * BF16_EPS * scale, f"{what}: max err {float(err.max()):.3e} vs scale {scale:.3e}"
+        assert float(err.mean()) <= 0.5 * BF16_EPS * scale, f"{what}: mean err {float(err.mean()):.3e} vs scale {scale:.3e}"
+
+
+@pytest.fixture(scope="session")
+def session_tmp(tmp_path_factory):
+    return tmp_path_factory.mktemp("models")
