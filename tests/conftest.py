@@ -48,16 +48,28 @@ TINY = {"A": (TINY_A, 0.0), "B": (TINY_B, 0.1)}  # name -> (config.json, std of 
 
 
 def make_model_dir(tmp_path: Path, config_json: dict, seed: int = 0, norm_std: float = 0.0,
-                   dtype=torch.bfloat16, norm_dtype=None, **overrides) -> Path:
-    """Write a random model folder for ``config_json`` (with overrides) and return its path."""
+                   dtype=torch.bfloat16, norm_dtype=None, scale: dict | None = None, **overrides) -> Path:
+    """Write a random model folder for ``config_json`` (with overrides) and return its path.
+    ``scale`` maps a substring of checkpoint names to a factor (``{"q_proj": 8.0}``): it makes the
+    attention peaked so that a single wrong key or cache slot changes the logits visibly."""
     from gpullama3.java_b200.config import config_from_dict
-    from gpullama3.java_b200.weights import write_random_model
+    from gpullama3.java_b200.weights import random_checkpoint, write_safetensors
 
     d = dict(config_json)
     d.update(overrides)
     cfg = config_from_dict(d)
-    out = tmp_path / f"model_{abs(hash(json.dumps(d, sort_keys=True))) % 10**8}_{seed}"
-    write_random_model(cfg, seed, out, dtype=dtype, norm_std=norm_std, norm_dtype=norm_dtype)
+    tag = json.dumps([d, seed, norm_std, str(dtype), str(norm_dtype), scale], sort_keys=True)
+    out = tmp_path / f"model_{abs(hash(tag)) % 10**10}"
+    if (out / "model.safetensors").is_file():
+        return out
+    out.mkdir(parents=True, exist_ok=True)
+    tensors = dict(random_checkpoint(cfg, seed, dtype=dtype, norm_std=norm_std, norm_dtype=norm_dtype))
+    for key, factor in (scale or {}).items():
+        for name in tensors:
+            if key in name:
+                tensors[name] = (tensors[name].to(torch.float32) * factor).to(tensors[name].dtype)
+    (out / "config.json").write_text(json.dumps(cfg.to_dict(), indent=2))
+    write_safetensors(out / "model.safetensors", tensors)
     return out
 
 
@@ -94,3 +106,11 @@ def assert_close_logits(got: torch.Tensor, ref: torch.Tensor, dtype, what: str =
 @pytest.fixture(scope="session")
 def session_tmp(tmp_path_factory):
     return tmp_path_factory.mktemp("models")
+
+
+PEAKED = {"q_proj": 8.0, "k_proj": 8.0}  # attention scores of a few units: single keys matter
+
+
+def random_prompts(vocab: int, lengths, seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]

@@ -1,0 +1,89 @@
+"""Replay of the same requests cut in different ways: whole, with the last 32 tokens decoded one by
+one, and in batches of unequal lengths whose shorter requests end earlier, one batch after another
+with a cache so small that slots and pages are used again.  Every way must give the plain
+implementation's logits at every position that is asked for.  The weights make attention peaked,
+so one wrong key, position or cache page shows."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_llama
+from conftest import PEAKED, ROOT, TINY, assert_close_logits, make_model_dir, plain_inputs, random_prompts
+from replay_helpers import (max_live_tokens, read_rows, run_in_process, trace_batches, trace_tail_one_by_one,
+                            trace_whole, write_trace)
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = [33, 64, 65, 100, 129, 40, 200, 70]
+
+
+def _reference(cfg, weights, requests, dtype):
+    rt = None if dtype == torch.float32 else torch.bfloat16
+    return {rid: plain_llama.forward(cfg, weights, toks, round_to=rt) for rid, toks in requests.items()}
+
+
+def _check(got, ref, dtype, what):
+    by_req: dict = {}
+    for (rid, pos), row in got.items():
+        by_req.setdefault(rid, []).append((pos, row))
+    for rid, items in by_req.items():
+        items.sort()
+        g = torch.stack([r for _, r in items])
+        r = ref[rid][[p for p, _ in items]]
+        assert_close_logits(g, r, dtype, f"{what} request {rid}")
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def setup(request, session_tmp):
+    cfg_json, norm_std = TINY[request.param]
+    d = make_model_dir(session_tmp, cfg_json, seed=3, norm_std=norm_std, scale=PEAKED)
+    cfg, weights = plain_inputs(d)
+    prompts = random_prompts(cfg["vocab_size"], LENGTHS, seed=11)
+    requests = {f"r{i}": p for i, p in enumerate(prompts)}
+    refs = {}
+    return d, cfg, weights, requests, refs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("cut", ["whole", "tail32", "batches3", "batches8"])
+def test_replay_cuts_match_plain(setup, tmp_path, dtype, cut):
+    from gpullama3.java_b200.engine.trace import load_model
+
+    d, cfg, weights, requests, refs = setup
+    if dtype not in refs:
+        refs[dtype] = _reference(cfg, weights, requests, dtype)
+    if cut == "whole":
+        steps, rows = trace_whole(requests)
+    elif cut == "tail32":
+        steps, rows = trace_tail_one_by_one(requests, 32)
+    elif cut == "batches3":
+        steps, rows = trace_batches(requests, 3)
+    else:
+        steps, rows = trace_batches(requests, 8, prompt_fraction=0.3)
+    model = load_model(d, dtype)
+    run_in_process(model, steps, tmp_path, max_live_tokens(steps))  # the smallest cache the trace is promised
+    got = read_rows(tmp_path, rows, cfg["vocab_size"])
+    _check(got, refs[dtype], dtype, cut)
+
+
+def test_trace_run_program(setup, tmp_path):
+    """The program itself, as a user starts it: steps on standard input, 'done <step>' lines out."""
+    d, cfg, weights, requests, refs = setup
+    few = dict(list(requests.items())[:4])
+    steps, rows = trace_batches(few, 2)
+    trace = tmp_path / "trace.jsonl"
+    write_trace(trace, steps)
+    out = tmp_path / "out"
+    env = dict(os.environ, PYTHON=sys.executable)
+    with open(trace) as f:
+        p = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(d), "--dtype", "float32", "--out", str(out),
+                            "--max-tokens", str(max_live_tokens(steps))], stdin=f, capture_output=True, text=True,
+                           env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    got = read_rows(out, rows, cfg["vocab_size"])
+    _check(got, _reference(cfg, weights, few, torch.float32), torch.float32, "trace_run")
