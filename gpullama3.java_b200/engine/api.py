@@ -1,0 +1,83 @@
+"""The Python entry point: an ``Engine`` holds a loaded model, its cache, the step function and the
+generation loop.
+
+    engine = Engine.from_folder("model_dir", dtype="bfloat16", max_tokens=32768)
+    outputs = engine.generate([[1, 2, 3], [4, 5]], max_new_tokens=16)          # greedy
+    outputs = engine.generate(prompts, max_new_tokens=16, temperature=0.8, seed=1)
+
+Token ids go in and come out as Python lists; everything between runs on the GPU."""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from ..config.base import ModelConfig, read_config_json
+from ..config.registry import architecture_of
+from ..sampling.sampler import Sampler, SamplingParams
+from .generate import GenerationResult, Generator
+from .step import SequenceInput, StepFunction
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+class Engine:
+    def __init__(self, model, *, max_tokens: int = 32768, max_batch: int = 64, max_length: int | None = None):
+        if not torch.cuda.is_available() or model.device.type != "cuda":
+            raise RuntimeError("the engine needs a CUDA device; it has no CPU path")
+        self.model = model
+        self.config: ModelConfig = model.config
+        self.cache = model.new_cache(max_tokens, max_slots=max(max_batch, 1))
+        self.step_fn = StepFunction(model, self.cache)
+        self.max_length = max_length if max_length is not None else self.cache.n_pages * 64
+        self.generator = Generator(self.step_fn, self.cache, Sampler, max_batch=max_batch, max_length=self.max_length)
+
+    # ---- construction
+    @classmethod
+    def from_folder(cls, model_dir: str | Path, *, dtype="bfloat16", device="cuda", **kw) -> "Engine":
+        d = read_config_json(model_dir)
+        arch = architecture_of(d)
+        model = arch.model_factory(arch.config_class.from_dict(d), _resolve_dtype(dtype), device)
+        model.load_folder(model_dir)
+        return cls(model, **kw)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig | dict, seed: int = 0, *, dtype="bfloat16", device="cuda",
+                    norm_std: float = 0.0, **kw) -> "Engine":
+        if isinstance(config, dict):
+            arch = architecture_of(config)
+            config = arch.config_class.from_dict(config)
+        else:
+            arch = architecture_of({"architectures": [config.architecture]})
+        model = arch.model_factory(config, _resolve_dtype(dtype), device)
+        model.load_random(seed, norm_std=norm_std)
+        return cls(model, **kw)
+
+    # ---- use
+    def generate(self, prompts: list[list[int]], max_new_tokens: int = 16, *, temperature: float = 0.0,
+                 top_p: float = 1.0, seed: int = 0, stop_ids=None, on_token=None,
+                 return_results: bool = False):
+        """Generated token ids per prompt (the stop token included when one ended the sequence)."""
+        if stop_ids is None:
+            stop_ids = self.config.stop_token_ids
+        results = self.generator.generate([list(p) for p in prompts], max_new_tokens,
+                                          SamplingParams(temperature, top_p, seed), stop_ids, on_token)
+        return results if return_results else [r.tokens for r in results]
+
+    @property
+    def last_metrics(self):
+        return self.generator.last_metrics
+
+    def step(self, inputs: list[SequenceInput]) -> torch.Tensor | None:
+        return self.step_fn(inputs)
+
+
+__all__ = ["Engine", "GenerationResult", "SequenceInput", "SamplingParams"]
