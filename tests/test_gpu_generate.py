@@ -1,0 +1,135 @@
+"""Generation through the Python entry point and the command line against the plain
+implementation: greedy tokens, sampled tokens for given uniform numbers, batches whose shorter
+requests end earlier, long decoding, the first tokens of a sequence."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as P
+from conftest import PEAKED, ROOT, TINY, assert_close_logits, make_model_dir, plain_inputs, random_prompts
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("B", "bfloat16")])
+def test_greedy_generation_matches_plain(session_tmp, name, dtype):
+    from gpullama3.java_b200.engine.api import Engine
+
+    cfg_json, norm_std = TINY[name]
+    d = make_model_dir(session_tmp, cfg_json, seed=21, norm_std=norm_std, scale={"embed_tokens": 8.0, "lm_head": 8.0})
+    cfg, w = plain_inputs(d)
+    lengths = [5, 11, 17] if name == "A" else [1, 7, 30, 64]
+    prompts = random_prompts(cfg["vocab_size"], lengths, seed=2)
+    engine = Engine.from_folder(d, dtype=dtype, max_tokens=64 * 8, max_batch=4)
+    got = engine.generate(prompts, max_new_tokens=8, stop_ids=())
+    rt = None if dtype == "float32" else torch.bfloat16
+    for p, g in zip(prompts, got):
+        if dtype == "float32":
+            assert g == P.generate_greedy(cfg, w, p, 8, round_to=rt)
+        else:   # a near-tie may flip in bfloat16: every token must be the plain arg-max or within rounding of it
+            seq = list(p)
+            for tok in g:
+                logits = P.forward(cfg, w, seq, round_to=rt)[-1]
+                assert float(logits.max() - logits[tok]) <= 4 * 2.0 ** -8 * float(logits.abs().max())
+                seq.append(tok)
+    assert engine.cache.live_slots() == []
+    m = engine.last_metrics
+    assert m.prompt_tokens == sum(lengths) and m.generated_tokens == 8 * len(lengths)
+
+
+def test_stop_tokens_end_sequences_early_and_batches_reuse_slots(session_tmp):
+    from gpullama3.java_b200.engine.api import Engine
+
+    cfg_json, norm_std = TINY["A"]
+    d = make_model_dir(session_tmp, cfg_json, seed=21, scale={"embed_tokens": 8.0})
+    cfg, w = plain_inputs(d)
+    prompts = random_prompts(256, [9, 3, 20, 14, 6, 33, 2], seed=4)
+    free = [P.generate_greedy(cfg, w, p, 12) for p in prompts]
+    stop = {free[0][3], free[4][1]}
+    want = [P.generate_greedy(cfg, w, p, 12, stop_ids=stop) for p in prompts]
+    assert len({len(x) for x in want}) > 1                           # some end early, some do not
+    engine = Engine.from_folder(d, dtype="float32", max_tokens=64 * 3, max_batch=3)   # three batches through 3 slots
+    res = engine.generate(prompts, max_new_tokens=12, stop_ids=stop, return_results=True)
+    assert [r.tokens for r in res] == want
+    assert [r.finish_reason for r in res] == ["stop" if x[-1] in stop else "length" for x in want]
+    assert engine.cache.live_slots() == []
+    engine.cache.check_invariants()
+
+
+def test_temperature_sampling_follows_the_uniform_numbers(session_tmp):
+    """Tiny B, 16 tokens at temperature 0.8: every sampled token is the inverse-CDF token of the
+    plain softmax for the same uniform number, whatever batch the request sits in."""
+    from gpullama3.java_b200.engine.api import Engine
+    from gpullama3.java_b200.sampling import uniform
+
+    cfg_json, norm_std = TINY["B"]
+    d = make_model_dir(session_tmp, cfg_json, seed=22, norm_std=norm_std, scale={"lm_head": 30.0})
+    cfg, w = plain_inputs(d)
+    prompts = random_prompts(cfg["vocab_size"], [1, 7, 30, 64], seed=5)
+    engine = Engine.from_folder(d, dtype="float32", max_tokens=64 * 8, max_batch=4)
+    got = engine.generate(prompts, max_new_tokens=16, temperature=0.8, seed=1234, stop_ids=())
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        seq = list(p)
+        for n, tok in enumerate(g):
+            probs = P.temperature_softmax(P.forward(cfg, w, seq)[-1], 0.8).double()
+            cdf = torch.cumsum(probs, 0)
+            u = uniform(1234, i, n)
+            lo = float(cdf[tok - 1]) if tok else 0.0
+            assert lo - 1e-5 <= u < float(cdf[tok]) + 1e-5, (i, n, tok, u)
+            seq.append(tok)
+    alone = Engine.from_folder(d, dtype="float32", max_tokens=64 * 2, max_batch=1)
+    one = alone.generator.generate([prompts[2]], 16, __import__("gpullama3.java_b200.sampling", fromlist=["SamplingParams"])
+                                   .SamplingParams(0.8, 1.0, 1234), (), request_ids=[2])
+    assert one[0].tokens == got[2]                                   # same draws alone as in the batch
+    nucleus = engine.generate(prompts, max_new_tokens=8, temperature=0.8, top_p=0.9, seed=5, stop_ids=())
+    assert all(len(x) == 8 and all(0 <= t < cfg["vocab_size"] for t in x) for x in nucleus)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_long_decoding_and_first_tokens(session_tmp, dtype):
+    """One token a step from the very first token on, for 330 positions (five page boundaries), and
+    the first three positions of a sequence on their own."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    cfg_json, norm_std = TINY["B"]
+    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale=PEAKED)
+    cfg, w = plain_inputs(d)
+    toks = random_prompts(cfg["vocab_size"], [330], seed=6)[0]
+    ref = P.forward(cfg, w, toks, round_to=None if dtype == torch.float32 else torch.bfloat16)
+    model = load_model(d, dtype)
+    cache = model.new_cache(64 * 6)
+    step = StepFunction(model, cache)
+    slot = cache.acquire()
+    rows = [step([SequenceInput(slot, [t], [0])])[0] for t in toks]
+    assert_close_logits(torch.stack(rows), ref, dtype, "token by token from position 0")
+    assert_close_logits(torch.stack(rows[:3]), ref[:3], dtype, "first tokens")
+    cache.release(slot)
+    for n in (1, 2, 3):
+        slot = cache.acquire()
+        out = step([SequenceInput(slot, toks[:n], list(range(n)))])
+        assert_close_logits(out, ref[:n], dtype, f"first {n} tokens in one step")
+        cache.release(slot)
+
+
+def test_command_line(session_tmp, tmp_path):
+    cfg_json, _ = TINY["A"]
+    d = make_model_dir(session_tmp, cfg_json, seed=21, scale={"embed_tokens": 8.0})
+    cfg, w = plain_inputs(d)
+    env = dict(os.environ, PYTHON=sys.executable)
+    cmd = [str(ROOT / "bin" / "llama-b200"), "--model", str(d), "--dtype", "float32", "--temperature", "0",
+           "-n", "6", "--stream", "false", "--prompt", "3 1 4 1 5", "--prompt", "9,2,6", "--stop", "300"]
+    p = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.strip().splitlines() if l.strip()]
+    assert [list(map(int, l.split())) for l in lines] == [P.generate_greedy(cfg, w, [3, 1, 4, 1, 5], 6),
+                                                          P.generate_greedy(cfg, w, [9, 2, 6], 6)]
+    assert "achieved tok/s" in p.stderr
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    p = subprocess.run([str(ROOT / "bin" / "llama-b200"), "--config", str(tmp_path / "config.json"), "--random-weights", "3",
+                        "--prompt", "1 2 3", "-n", "4", "--seed", "1"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0 and len(p.stdout.split()) == 4, p.stderr[-2000:]

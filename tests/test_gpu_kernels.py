@@ -1,0 +1,253 @@
+"""Each CUDA kernel alone against its plain formula, at sizes other than the tiny models': widths
+and vocabularies that are no power of two, head sizes in steps of 16, odd head counts and groups,
+scattered cache pages, windows."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, ref=None):
+    """float32: accumulation-order noise, 2e-5 of the largest value.  bfloat16 (inputs already
+    rounded, the reference rounded at the end): two units in the last place of each value."""
+    scale = float(ref.abs().max()) if ref is not None else 1.0
+    if dtype == torch.float32:
+        return dict(rtol=0.0, atol=2e-5 * scale)
+    return dict(rtol=2.0 ** -7, atol=2e-5 * scale)
+
+
+def ops():
+    from gpullama3.java_b200.kernels import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab, dim", [(37, 24), (1000, 1030)])
+def test_embed_gather(dtype, vocab, dim):
+    table = torch.randn(vocab, dim, device="cuda").to(dtype)
+    tokens = torch.randint(0, vocab, (19,), device="cuda", dtype=torch.int32)
+    out = torch.empty(19, dim, device="cuda")
+    ops().embed_gather(table, tokens, out)
+    assert torch.equal(out, table.float()[tokens.long()])
+
+
+@pytest.mark.parametrize("w_dtype", DTYPES)
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("dim, eps", [(24, 1e-5), (1030, 1e-6), (4096, 1e-2)])
+def test_rmsnorm(w_dtype, out_dtype, dim, eps):
+    x = torch.randn(7, dim, device="cuda") * 3
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(w_dtype)
+    out = torch.empty(7, dim, device="cuda", dtype=out_dtype)
+    ops().rmsnorm(x, w, out, eps)
+    ref = P.rmsnorm(x.cpu(), w.float().cpu(), eps)
+    torch.testing.assert_close(out.float().cpu(), ref.to(out_dtype).float(), **tol(out_dtype, ref))
+    rows = torch.tensor([5, 0, 5], device="cuda", dtype=torch.int32)
+    out2 = torch.empty(3, dim, device="cuda", dtype=out_dtype)
+    ops().rmsnorm(x, w, out2, eps, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+def _paged_setup(dtype, n_seqs, kv_lens, KVH, D, n_pages, seed=0):
+    """Random keys/values laid out in scattered pages; returns pools, the page table and the dense
+    per-sequence keys/values."""
+    g = torch.Generator().manual_seed(seed)
+    width = max(-(-n // 64) for n in kv_lens)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(n_seqs, width, dtype=torch.int32)
+    k_pool = torch.zeros(n_pages, KVH, 64, D)
+    v_pool = torch.zeros(n_pages, KVH, 64, D)
+    dense = []
+    for s, n in enumerate(kv_lens):
+        k = torch.randn(n, KVH, D, generator=g).to(dtype).float()
+        v = torch.randn(n, KVH, D, generator=g).to(dtype).float()
+        dense.append((k, v))
+        for lp in range(-(-n // 64)):
+            page = perm.pop()
+            table[s, lp] = page
+            m = min(64, n - lp * 64)
+            k_pool[page, :, :m] = k[lp * 64:lp * 64 + m].transpose(0, 1)
+            v_pool[page, :, :m] = v[lp * 64:lp * 64 + m].transpose(0, 1)
+    return k_pool.to(dtype).cuda(), v_pool.to(dtype).cuda(), table.cuda(), dense
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H, KVH, D, window", [(4, 2, 16, 0), (3, 1, 32, 0), (6, 3, 48, 0), (8, 8, 64, 0),
+                                               (5, 5, 80, 0), (8, 2, 128, 0), (2, 1, 256, 0), (4, 1, 64, 37),
+                                               (4, 2, 32, 200)])
+def test_attention_paged_against_plain(dtype, H, KVH, D, window):
+    """Queries of several sequences at scattered positions (chunks continuing a prefix and single
+    decoded tokens together) over scattered pages."""
+    kv_lens = [1, 64, 65, 300, 129]
+    q_starts = [0, 60, 64, 299, 100]   # each sequence's queries cover positions q_start .. kv_len-1
+    k_pool, v_pool, table, dense = _paged_setup(dtype, len(kv_lens), kv_lens, KVH, D, n_pages=40, seed=D + H)
+    g = torch.Generator().manual_seed(1)
+    qs, positions, seq_ids, refs = [], [], [], []
+    for s, (n, q0) in enumerate(zip(kv_lens, q_starts)):
+        k, v = dense[s]
+        q_full = (torch.randn(n, H, D, generator=g) * 2).to(dtype).float()
+        ref_full = P.causal_attention(q_full, k, v, window or None)
+        qs.append(q_full[q0:])
+        refs.append(ref_full[q0:])
+        positions += list(range(q0, n))
+        seq_ids += [s] * (n - q0)
+    q = torch.cat(qs).reshape(-1, H * D)
+    # queries sit at the start of wider rows, as in the fused qkv buffer
+    qkv = torch.cat([q, torch.randn(q.shape[0], 2 * KVH * D)], dim=1).to(dtype).cuda().contiguous()
+    out = torch.empty(q.shape[0], H * D, dtype=dtype, device="cuda")
+    pos_t = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    seq_t = torch.tensor(seq_ids, dtype=torch.int32, device="cuda")
+    ops().attention_paged(qkv, qkv.shape[1], out, pos_t, seq_t, table, k_pool, v_pool, H, KVH, D, window)
+    ref = torch.cat(refs).reshape(-1, H * D)
+    torch.testing.assert_close(out.float().cpu(), ref.to(dtype).float(), **tol(dtype, ref))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """One key far back matches the query strongly: the output must be that key's value."""
+    H, KVH, D, n = 2, 1, 32, 700
+    k_pool, v_pool, table, dense = _paged_setup(dtype, 1, [n], KVH, D, n_pages=16, seed=9)
+    k, v = dense[0]
+    target = 123
+    q = (k[target, 0] * 6.0).repeat(H).reshape(1, H * D)      # score ~ 6 |k|^2 / sqrt(D), far above the rest
+    qkv = torch.cat([q, torch.zeros(1, 2 * KVH * D)], dim=1).to(dtype).cuda()
+    out = torch.empty(1, H * D, dtype=dtype, device="cuda")
+    ops().attention_paged(qkv, qkv.shape[1], out, torch.tensor([n - 1], dtype=torch.int32, device="cuda"),
+                          torch.tensor([0], dtype=torch.int32, device="cuda"), table, k_pool, v_pool, H, KVH, D, 0)
+    ref = P.causal_attention(q.to(dtype).float().reshape(1, H, D).expand(n, H, D).contiguous(), k, v)[-1]
+    torch.testing.assert_close(out.float().cpu().reshape(H, D), ref.to(dtype).float(), **tol(dtype, ref))
+    assert float((out.float().cpu().reshape(H, D)[0] - v[target, 0]).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["interleaved", "half"])
+@pytest.mark.parametrize("H, KVH, D, rotary", [(4, 2, 16, 16), (3, 1, 32, 32), (2, 2, 48, 32), (1, 1, 128, 0)])
+def test_rope_and_cache_write(dtype, pairing, H, KVH, D, rotary):
+    from gpullama3.java_b200.parts.position import PAIRING_CODES
+
+    positions = [0, 1, 63, 64, 65, 200, 4095, 7]
+    seq_ids = [0, 0, 0, 0, 0, 0, 1, 1]
+    T = len(positions)
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(T, (H + 2 * KVH) * D, generator=g).to(dtype)
+    scaling = {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32}
+    inv = P.rope_inverse_frequencies(rotary, 5e5, scaling) if rotary else torch.zeros(1, dtype=torch.float64)
+    n_pages = 70
+    table = torch.zeros(2, 64, dtype=torch.int32)
+    table[0] = torch.arange(64)[torch.randperm(64, generator=g)][:64]
+    table[1, 63] = 65
+    table[1, 0] = 66
+    k_pool = torch.zeros(n_pages, KVH, 64, D, dtype=dtype, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    buf = qkv.clone().cuda()
+    ops().rope_cache_write(buf, torch.tensor(positions, dtype=torch.int32, device="cuda"),
+                           torch.tensor(seq_ids, dtype=torch.int32, device="cuda"), table.cuda(),
+                           inv.to(torch.float32).cuda(), k_pool, v_pool, H, KVH, D, rotary, PAIRING_CODES[pairing])
+    x = qkv.float()
+    q, k, v = x[:, :H * D].reshape(T, H, D), x[:, H * D:(H + KVH) * D].reshape(T, KVH, D), x[:, (H + KVH) * D:].reshape(T, KVH, D)
+    if rotary:
+        cos, sin = P.rope_tables(torch.tensor(positions), inv, torch.float32)
+        q = torch.cat([P.apply_rope(q[..., :rotary], cos, sin, pairing), q[..., rotary:]], dim=-1)
+        k = torch.cat([P.apply_rope(k[..., :rotary], cos, sin, pairing), k[..., rotary:]], dim=-1)
+    t = tol(dtype, x)
+    torch.testing.assert_close(buf[:, :H * D].float().cpu(), q.reshape(T, H * D).to(dtype).float(), **t)
+    for i, (p, s) in enumerate(zip(positions, seq_ids)):
+        page = int(table[s, p // 64])
+        torch.testing.assert_close(k_pool[page, :, p % 64].float().cpu(), k[i].to(dtype).float(), **t)
+        assert torch.equal(v_pool[page, :, p % 64].float().cpu(), v[i])
+    assert int((k_pool.float().abs().sum(dim=(1, 3)) > 0).sum()) == T   # no other cache row was touched
+
+
+@pytest.mark.parametrize("a_dtype, w_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                              (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M, N, K", [(1, 40, 24), (7, 130, 100), (65, 64, 17), (200, 258, 1030)])
+def test_gemm_generic_and_its_epilogues(a_dtype, w_dtype, M, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(a_dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(w_dtype).cuda()
+    ref = a.float().cpu().double() @ w.float().cpu().double().t()
+    c = torch.empty(M, N, dtype=a_dtype, device="cuda")
+    o.gemm_generic(a, w, c, o.EPILOGUE_STORE)
+    torch.testing.assert_close(c.float().cpu(), ref.float().to(a_dtype).float(), **tol(a_dtype, ref))
+    res0 = torch.randn(M, N, generator=g)
+    res = res0.clone().cuda()
+    o.gemm_generic(a, w, res, o.EPILOGUE_RESIDUAL_ADD)
+    torch.testing.assert_close(res.cpu(), (res0.double() + ref).float(), **tol(torch.float32, ref))
+    h = torch.empty(M, N // 2, dtype=a_dtype, device="cuda")
+    o.gemm_generic(a, w, h, o.EPILOGUE_GATED_SILU)
+    gated = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+    torch.testing.assert_close(h.float().cpu(), gated.float().to(a_dtype).float(), **tol(a_dtype, gated))
+
+
+@pytest.mark.parametrize("V", [5, 384, 1000, 128256])
+def test_argmax_first_maximum_wins(V):
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(6, V, generator=g)
+    logits[1, V // 2] = logits[1, V - 1] = 9.0       # a tie: the lower index wins
+    logits[2, 0] = 50.0
+    logits[3, V - 1] = 50.0
+    logits[4] = -float("inf")
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops().argmax_rows(logits.cuda(), out)
+    assert out.tolist() == [P.argmax_first(r) if torch.isfinite(r).any() else 0 for r in logits]
+    assert out.tolist()[1] == V // 2
+
+
+@pytest.mark.parametrize("V, temperature", [(11, 1.0), (384, 0.8), (5003, 0.3)])
+def test_temperature_sampling_is_the_inverse_cdf_in_index_order(V, temperature):
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(1, V, generator=g) * 2
+    us = [0.0, 0.001, 0.25, 0.5, 0.75, 0.999, 0.99999994]
+    rows = logits.repeat(len(us), 1).cuda()
+    out = torch.empty(len(us), dtype=torch.int32, device="cuda")
+    ops().sample_rows(rows, torch.tensor(us, dtype=torch.float32, device="cuda"), out, temperature, 1.0)
+    p = P.temperature_softmax(logits[0], temperature).double()
+    cdf = torch.cumsum(p, 0)
+    for u, tok in zip(us, out.tolist()):
+        want = P.sample_categorical(p.float(), u)
+        lo = float(cdf[tok - 1]) if tok > 0 else 0.0
+        # the same token, or a neighbour when u falls within rounding of a boundary of the cdf
+        assert tok == want or min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (u, tok, want)
+
+
+@pytest.mark.parametrize("V, top_p, temperature", [(9, 0.6, 1.0), (384, 0.95, 0.8), (5003, 0.9, 0.5), (700, 0.05, 1.0)])
+def test_nucleus_sampling_matches_plain(V, top_p, temperature):
+    g = torch.Generator().manual_seed(V + 1)
+    logits = torch.randn(1, V, generator=g) * 3
+    logits[0, 5] = logits[0, 3]                      # equal probabilities are ordered by index
+    us = [0.0, 0.1, 0.33, 0.5, 0.8, 0.95, 0.9999]
+    rows = logits.repeat(len(us), 1).cuda()
+    out = torch.empty(len(us), dtype=torch.int32, device="cuda")
+    ops().sample_rows(rows, torch.tensor(us, dtype=torch.float32, device="cuda"), out, temperature, top_p)
+    p = P.temperature_softmax(logits[0], temperature)
+    order = sorted(range(V), key=lambda i: (-float(p[i]), i))
+    csum = torch.cumsum(p[order].double(), 0)
+    for u, tok in zip(us, out.tolist()):
+        want = P.sample_top_p(p, top_p, u)
+        if tok != want:   # allowed only when r falls within rounding of a boundary between neighbours
+            kept = int((csum <= top_p).sum()) + 1
+            r = u * float(csum[kept - 1])
+            j = order.index(tok)
+            assert j < kept and min(abs(r - float(csum[j])), abs(r - (float(csum[j - 1]) if j else 0.0))) < 1e-5, (u, tok, want)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    o = ops()
+    from gpullama3.java_b200.kernels.ops import KernelError
+    q = torch.zeros(1, 3 * 24, device="cuda")
+    out = torch.zeros(1, 24, device="cuda")
+    pool = torch.zeros(1, 1, 64, 24, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(KernelError, match="unsupported size"):
+        o.attention_paged(q, 72, out, z, z, z.reshape(1, 1), pool, pool, 1, 1, 24, 0)   # head size not a step of 16
+    with pytest.raises(KernelError):
+        o.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4))   # CPU tensors
+    with pytest.raises(KernelError, match="bad argument"):
+        o.sample_rows(torch.zeros(1, 8, device="cuda"), torch.zeros(1, device="cuda"),
+                      torch.zeros(1, dtype=torch.int32, device="cuda"), 0.0, 1.0)       # temperature 0 is argmax's job

@@ -1,0 +1,309 @@
+"""Each part alone against the plain formulas, and the generality of their arrangement: a toy
+architecture, defined here, with a mixer that keeps fixed-size state of its own, a layer that runs
+twice, a layer that reads another layer's cache and a windowed attention layer -- registered, built
+and stepped without a change to the package."""
+import json
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama as P
+from conftest import TINY, assert_close_logits, make_model_dir, plain_inputs
+from gpullama3.java_b200.cache import KVCacheNeed, SequenceCache, StateNeed
+from gpullama3.java_b200.config import (LayerSpec, LlamaConfig, PartSpec, ScheduleEntry, register_architecture,
+                                        unregister_architecture)
+from gpullama3.java_b200.parts import (GroupedQueryAttention, Mixer, OutputHead, PreNormBlock, RMSNorm,
+                                       RotaryPositionEncoding, SwiGLUFeedForward, TokenEmbedding, register_mixer,
+                                       unregister)
+from gpullama3.java_b200.weights import ParamSpec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ctx(cache, dtype, slots, token_lists):
+    from gpullama3.java_b200.engine.step import build_context
+    start = [cache.length(s) for s in slots]
+    cache.reserve([(s, len(t)) for s, t in zip(slots, token_lists)])
+    ctx, _ = build_context(dtype, torch.device(DEV), cache, slots, start, token_lists, [])
+    return ctx
+
+
+def _close(got, ref, dtype):
+    scale = float(ref.abs().max())
+    if dtype == torch.float32:
+        torch.testing.assert_close(got.float().cpu(), ref, rtol=0, atol=2e-5 * scale)
+    else:
+        torch.testing.assert_close(got.float().cpu(), ref, rtol=0, atol=2.0 ** -6 * scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("w_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype, w_dtype):
+    n = RMSNorm(dim=100, eps=1e-3)
+    assert n.parameters()["weight"].shape == (100,)
+    w = (1 + 0.2 * torch.randn(100)).to(w_dtype)
+    n.load({"weight": w}, dtype, DEV)
+    assert n.weight.dtype == (torch.float32 if (dtype == torch.float32 or w_dtype == torch.float32) else torch.bfloat16)
+    x = torch.randn(5, 100) * 4
+    out = n.forward(x.to(DEV), dtype)
+    assert out.dtype == dtype
+    _close(out, P.rmsnorm(x, w.float(), 1e-3), dtype)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_rotary_frequencies(name):
+    cfg = TINY[name][0]
+    r = RotaryPositionEncoding(cfg["head_dim"], cfg["rope_theta"], "half", cfg["rope_scaling"])
+    ours = r.inverse_frequencies(DEV).cpu()
+    ref = P.rope_inverse_frequencies(cfg["head_dim"], cfg["rope_theta"], cfg["rope_scaling"]).to(torch.float32)
+    assert torch.equal(ours, ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H, KVH, D, hidden, pairing, window", [(4, 2, 16, 72, "half", None), (3, 1, 32, 40, "interleaved", None),
+                                                                (6, 2, 48, 100, "half", 50)])
+def test_attention_part_alone(dtype, H, KVH, D, hidden, pairing, window):
+    rope = RotaryPositionEncoding(D, 1e4, pairing)
+    att = GroupedQueryAttention(hidden, H, KVH, D, rope, window)
+    specs = att.parameters()
+    assert specs["q"].shape == (H * D, hidden) and specs["k"].shape == (KVH * D, hidden) and specs["o"].shape == (hidden, H * D)
+    assert att.cache_need() == KVCacheNeed(KVH, D, window)
+    g = torch.Generator().manual_seed(H)
+    w = {k: (torch.randn(s.shape, generator=g) * 0.2).to(torch.bfloat16) for k, s in specs.items()}
+    att.load(w, dtype, DEV)
+    cache = SequenceCache({0: att.cache_need()}, max_tokens=64 * 8, dtype=dtype, device=DEV, window_slack=128)
+    lens = [70, 5, 128]
+    xs = [torch.randn(n, hidden, generator=g).to(dtype).float() for n in lens]
+    slots = [cache.acquire() for _ in lens]
+    ctx = _ctx(cache, dtype, slots, [[0] * n for n in lens])
+    residual = torch.zeros(sum(lens), hidden, device=DEV)
+    att.forward(torch.cat(xs).to(dtype).to(DEV), ctx, cache.view(0), residual)
+    rt = (lambda t: t) if dtype == torch.float32 else (lambda t: t.to(torch.bfloat16).float())
+    refs = []
+    for x in xs:
+        T = x.shape[0]
+        q = rt(P.linear(x, w["q"].float())).view(T, H, D)
+        k = rt(P.linear(x, w["k"].float())).view(T, KVH, D)
+        v = rt(P.linear(x, w["v"].float())).view(T, KVH, D)
+        cos, sin = P.rope_tables(torch.arange(T), P.rope_inverse_frequencies(D, 1e4, None), torch.float32)
+        q, k = rt(P.apply_rope(q, cos, sin, pairing)), rt(P.apply_rope(k, cos, sin, pairing))
+        a = rt(P.causal_attention(q, k, v, window)).reshape(T, H * D)
+        refs.append(P.linear(a, w["o"].float()))
+    _close(residual, torch.cat(refs), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part_alone(dtype):
+    ff = SwiGLUFeedForward(hidden_size=72, intermediate_size=200)
+    g = torch.Generator().manual_seed(2)
+    w = {k: (torch.randn(s.shape, generator=g) * 0.2).to(torch.bfloat16) for k, s in ff.parameters().items()}
+    ff.load(w, dtype, DEV)
+    assert tuple(ff.gate_up.weight.shape) == (400, 72)
+    assert torch.equal(ff.gate_up.weight[0::2].float().cpu(), w["gate"].float())     # rows interleaved gate, up
+    x = torch.randn(9, 72, generator=g).to(dtype).float()
+    residual0 = torch.randn(9, 72, generator=g)
+    residual = residual0.clone().to(DEV)
+    ff.forward(x.to(dtype).to(DEV), None if False else _Dummy(dtype), residual)
+    rt = (lambda t: t) if dtype == torch.float32 else (lambda t: t.to(torch.bfloat16).float())
+    h = rt(P.swiglu(P.linear(x, w["gate"].float()), P.linear(x, w["up"].float())))
+    _close(residual, residual0 + P.linear(h, w["down"].float()), dtype)
+
+
+class _Dummy:
+    def __init__(self, dtype):
+        self.dtype = dtype
+
+
+def test_embedding_and_tied_head_share_memory():
+    emb = TokenEmbedding(50, 24)
+    table = torch.randn(50, 24).to(torch.bfloat16)
+    emb.load({"table": table}, torch.bfloat16, DEV)
+    head = OutputHead(50, 24, tied_to=emb)
+    assert head.parameters() == {}
+    head.load({}, torch.bfloat16, DEV)
+    assert head.linear.weight.data_ptr() == emb.table.data_ptr()
+    toks = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(toks).cpu(), table.float()[[3, 49, 0]])
+    x = torch.randn(2, 24).to(torch.bfloat16)
+    logits = head.forward(x.to(DEV))
+    assert logits.dtype == torch.float32
+    _close(logits, x.float() @ table.float().t(), torch.float32)
+    assert OutputHead(50, 24).parameters()["weight"].shape == (50, 24)
+
+
+# --------------------------------------------------------------------------- a toy architecture
+class RunningMeanMixer(Mixer):
+    """Toy mixer with fixed-size state: adds proj(mean of the inputs seen so far).  Its state per
+    sequence is the running sum and the count; it keeps no keys or values."""
+
+    def __init__(self, hidden_size: int):
+        self.h = hidden_size
+
+    def parameters(self):
+        return {"proj": ParamSpec((self.h, self.h))}
+
+    def cache_need(self):
+        return StateNeed((self.h + 1,), torch.float32)
+
+    def load(self, tensors, dtype, device):
+        self.proj = tensors["proj"].to(device=device, dtype=torch.float32)
+
+    def forward(self, x, ctx, cache, residual, writes_cache=True):
+        off = 0
+        for slot, n in zip(ctx.slots, ctx.q_lens):
+            st = cache.data[slot]
+            csum = st[: self.h] + torch.cumsum(x[off:off + n].float(), 0)
+            cnt = st[self.h] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+            residual[off:off + n] += (csum / cnt[:, None]) @ self.proj.t()
+            if writes_cache:
+                st[: self.h] = csum[-1]
+                st[self.h] = cnt[-1]
+            off += n
+
+
+@dataclass(frozen=True)
+class ToyConfig(LlamaConfig):
+    """Layers: 0 attention, 1 running mean, 2 attention with a window, 3 attention that keeps
+    nothing of its own.  Schedule: 0, 1, 0 again (a second cache entry), 2, 3 reading layer 0's first
+    cache."""
+    architecture = "ToyStateForCausalLM"
+    window: int = 40
+
+    def layer_specs(self):
+        base = super().layer_specs()[0]
+        toy = LayerSpec(PartSpec("test_running_mean", {"hidden_size": self.hidden_size}), base.feed_forward,
+                        base.mixer_norm, base.feed_forward_norm)
+        windowed = LayerSpec(PartSpec("attention", dict(base.mixer.args, window=self.window)), base.feed_forward,
+                             base.mixer_norm, base.feed_forward_norm)
+        return [base, toy, windowed, base]
+
+    def schedule(self):
+        return [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 3),
+                ScheduleEntry(3, 0, writes_cache=False)]
+
+    def tensor_names(self):
+        names = {"embedding.table": "tok.weight", "final_norm.weight": "out_norm.weight", "head.weight": "out.weight"}
+        for i, kind in enumerate(["att", "mean", "att", "att"]):
+            p, c = f"layers.{i}.", f"blk.{i}."
+            names[p + "mixer_norm.weight"] = c + "norm1"
+            names[p + "feed_forward_norm.weight"] = c + "norm2"
+            for w in ("gate", "up", "down"):
+                names[p + f"feed_forward.{w}"] = c + f"ffn_{w}"
+            if kind == "att":
+                for w in ("q", "k", "v", "o"):
+                    names[p + f"mixer.{w}"] = c + f"attn_{w}"
+            else:
+                names[p + "mixer.proj"] = c + "mean_proj"
+        return names
+
+
+TOY = dict(TINY["A"][0], architectures=["ToyStateForCausalLM"], num_hidden_layers=4, tie_word_embeddings=False)
+
+
+def plain_toy_forward(cfg, w, tokens, window):
+    """The toy architecture written out with the plain functions, whole sequence, no cache."""
+    T = len(tokens)
+    H, KVH, D, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    cos, sin = P.rope_tables(torch.arange(T), P.rope_inverse_frequencies(D, cfg["rope_theta"], None), torch.float32)
+    x = P.embedding(w["tok.weight"], torch.tensor(tokens))
+
+    def kv(i, xb):
+        k = P.apply_rope(P.linear(xb, w[f"blk.{i}.attn_k"]).view(T, KVH, D), cos, sin, "half")
+        return k, P.linear(xb, w[f"blk.{i}.attn_v"]).view(T, KVH, D)
+
+    def attend(i, xb, k, v, win):
+        q = P.apply_rope(P.linear(xb, w[f"blk.{i}.attn_q"]).view(T, H, D), cos, sin, "half")
+        return P.linear(P.causal_attention(q, k, v, win).reshape(T, H * D), w[f"blk.{i}.attn_o"])
+
+    def ffn(i, x):
+        xb = P.rmsnorm(x, w[f"blk.{i}.norm2"], eps)
+        return x + P.linear(P.swiglu(P.linear(xb, w[f"blk.{i}.ffn_gate"]), P.linear(xb, w[f"blk.{i}.ffn_up"])),
+                            w[f"blk.{i}.ffn_down"])
+
+    xb = P.rmsnorm(x, w["blk.0.norm1"], eps)
+    k0, v0 = kv(0, xb)                                   # what cache entry 0 holds
+    x = ffn(0, x + attend(0, xb, k0, v0, None))
+    xb = P.rmsnorm(x, w["blk.1.norm1"], eps)
+    mean = torch.cumsum(xb, 0) / torch.arange(1, T + 1)[:, None]
+    x = ffn(1, x + mean @ w["blk.1.mean_proj"].t())
+    xb = P.rmsnorm(x, w["blk.0.norm1"], eps)             # layer 0 again, with keys of its own
+    x = ffn(0, x + attend(0, xb, *kv(0, xb), None))
+    xb = P.rmsnorm(x, w["blk.2.norm1"], eps)
+    x = ffn(2, x + attend(2, xb, *kv(2, xb), window))
+    xb = P.rmsnorm(x, w["blk.3.norm1"], eps)             # reads what layer 0's first run cached
+    x = ffn(3, x + attend(3, xb, k0, v0, None))
+    return P.linear(P.rmsnorm(x, w["out_norm.weight"], eps), w["out.weight"])
+
+
+@pytest.fixture()
+def toy_registered():
+    register_mixer("test_running_mean", RunningMeanMixer)
+    register_architecture("ToyStateForCausalLM", ToyConfig)
+    yield
+    unregister("mixer", "test_running_mean")
+    unregister_architecture("ToyStateForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_architecture_with_state_is_registered_built_and_stepped(toy_registered, tmp_path, dtype):
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    d = make_model_dir(tmp_path, TOY, seed=6, scale={"attn_q": 8.0, "attn_k": 8.0})
+    cfg, w = plain_inputs(d)
+    model = load_model(d, dtype)
+    needs = model.cache_needs()
+    assert needs[1] == StateNeed((65,), torch.float32) and needs[3] == KVCacheNeed(2, 16, 40)
+    assert needs[0] == needs[2] == KVCacheNeed(2, 16, None) and set(needs) == {0, 1, 2, 3}
+    cache = model.new_cache(64 * 12, max_slots=3, window_slack=256)
+    assert len(cache.kv_groups) == 2 and len(cache.state_groups) == 1
+    step = StepFunction(model, cache)
+    prompts = [torch.randint(0, 256, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (150, 70, 9)]
+
+    # whole prompts together, then again as a prefix in one step plus the rest token by token
+    slots = [cache.acquire() for _ in prompts]
+    whole = step([SequenceInput(s, p, list(range(len(p)))) for s, p in zip(slots, prompts)])
+    for s in slots:
+        cache.release(s)
+    slots = [cache.acquire() for _ in prompts]           # the same slots again: state must start from zero
+    heads = [max(1, len(p) - 20) for p in prompts]
+    first = step([SequenceInput(s, p[:h], [h - 1]) for s, p, h in zip(slots, prompts, heads)])
+    tails = {i: [first[i]] for i in range(3)}
+    for t in range(20):
+        live = [i for i in range(3) if heads[i] + t < len(prompts[i])]
+        if not live:
+            break
+        out = step([SequenceInput(slots[i], [prompts[i][heads[i] + t]], [0]) for i in live])
+        for j, i in enumerate(live):
+            tails[i].append(out[j])
+    cache.check_invariants()
+    off = 0
+    for i, p in enumerate(prompts):
+        ref = plain_toy_forward(cfg, w, p, 40)
+        got_whole = whole[off:off + len(p)]
+        off += len(p)
+        if dtype == torch.float32:
+            assert_close_logits(got_whole, ref, dtype, f"toy whole {i}")
+            assert_close_logits(torch.stack(tails[i]), ref[heads[i] - 1:], dtype, f"toy stepped {i}")
+        else:   # the plain toy forward does not round; compare the two cuts with each other
+            assert_close_logits(torch.stack(tails[i]), got_whole[heads[i] - 1:].cpu(), dtype, f"toy cuts {i}")
+            assert float((got_whole.cpu() - ref).abs().max()) < 0.1 * float(ref.abs().max())
+
+
+def test_schedule_mistakes_are_refused(toy_registered):
+    from gpullama3.java_b200.config import ConfigError, config_from_dict
+    from gpullama3.java_b200.engine.model import CausalLM
+
+    class Bad(ToyConfig):
+        def schedule(self):
+            return [ScheduleEntry(3, 0, writes_cache=False), ScheduleEntry(0, 0)]   # read before any write
+    with pytest.raises(ConfigError, match="before any entry writes"):
+        CausalLM(Bad.from_dict(TOY), torch.float32, "cpu")
+
+    class Bad2(ToyConfig):
+        def schedule(self):
+            return [ScheduleEntry(0, 0), ScheduleEntry(2, 0, writes_cache=False)]   # window differs from cache 0's
+    with pytest.raises(ConfigError, match="different needs"):
+        CausalLM(Bad2.from_dict(TOY), torch.float32, "cpu")
