@@ -58,7 +58,17 @@ def _fn(name: str):
     return f
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launches this process has issued through these functions."""
+    return _launches
+
+
 def _check(status: int, name: str) -> None:
+    global _launches
+    _launches += 1
     if status != 0:
         what = _ERRORS.get(status)
         if what is None:
