@@ -6,7 +6,8 @@ sequence (inference/state/LlamaState.java:44-46,61-64 of the reference project).
 
 * a *cache entry* is what one run of a mixer keeps (the schedule names it by an integer);
 * entries with the same need form a *group* with storage of its own: a group of growing
-  key/value entries owns a pool of pages ``[entry][page][kv_head][64][head_dim]`` and one page
+  key/value entries owns a pool of pages (keys ``[entry][page][kv_head][64][head_dim]``, values
+  transposed ``[entry][page][kv_head][head_dim][64]``) and one page
   table per sequence (shared by the group's entries); a group whose need has a ``window`` only
   keeps the pages that a query can still reach; a group of fixed-size state owns
   ``[entry][slot][...shape]``, zeroed when a slot is acquired;
@@ -45,9 +46,9 @@ class KVGroup:
         self.need = need
         self.entries = entries
         self.pool = PagePool(n_pages)
-        shape = (len(entries), n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # keys: a row per position; values: transposed, a row per dimension (positions contiguous)
+        self.k = torch.zeros((len(entries), n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim), dtype=dtype, device=device)
+        self.v = torch.zeros((len(entries), n_pages, need.n_kv_heads, need.head_dim, PAGE_TOKENS), dtype=dtype, device=device)
         self.entry_pos = {e: i for i, e in enumerate(entries)}
 
 
@@ -66,7 +67,7 @@ class KVView:
     group whose page table (in the step context) addresses them."""
     group: int
     k: torch.Tensor  # [n_pages, kv_heads, PAGE_TOKENS, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor  # [n_pages, kv_heads, head_dim, PAGE_TOKENS]
     window: int | None
 
 

@@ -1,0 +1,280 @@
+// Decode attention in bfloat16: one new token per sequence attends over its cached keys and values.
+//
+// The cache of the live sequences is, next to the weights, what a decode step has to read, so the
+// kernel is a stream of K and V pages from HBM.  One CTA takes (a span of keys, one kv head, one
+// sequence); the query heads that share the kv head (n_heads / n_kv_heads, up to 16) are the rows
+// of the tensor-core tiles, so each key and value is read once for all of them.  Long sequences
+// are cut into `n_splits` spans so that a small batch still fills the GPU; every span leaves an
+// unnormalised partial (running max m, sum l, output o) in scratch memory and a second kernel
+// merges the spans in a fixed order (no atomics).  The mathematics is the reference's
+// (inference/InferenceCore.java:106-145 of the reference project): scores q.k / sqrt(d) over the
+// cached positions, softmax, weighted sum of values; the online form with running max is the one
+// its GPU kernel uses (tornadovm/TransformerComputeKernelsLayered.java:431-502).
+//
+// Layouts: keys [page][kv_head][64][d]; values transposed [page][kv_head][d][64].  Both are
+// loaded 16 bytes per lane straight into mma.m16n8k16 fragments:
+//   S[heads x keys] = Q K^T : K rows are the "col" operand; lane (g, t) takes dims 8t..8t+7 of a
+//       key row.  Within a block of 32 keys, tile i column c holds key (c/2)*8 + 2i + (c%2), so
+//       that over the four tiles lane t ends up with the probabilities of keys 8t..8t+7 ...
+//   O[heads x d] += P V : ... which is exactly one 16-byte load of a V^T row (dim, keys 8t..8t+7).
+//
+// Sizes: head_dim 32, 64, 96 or 128; group size (heads per kv head) <= 16.  Others are refused.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kAttnDecodeWarps = 4;
+constexpr int kAttnDecodeThreads = kAttnDecodeWarps * 32;
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// keep the first n (0..8) bfloat16 of a 16-byte register group, zero the rest
+__device__ __forceinline__ uint4 keep_first(uint4 v, int n) {
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int left = n - 2 * i;
+        w[i] = left >= 2 ? w[i] : (left == 1 ? (w[i] & 0xffffu) : 0u);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Partials in scratch: o [seq][head][split][d] floats, then ml [seq][head][split][2] floats.
+template <int KB>  // head_dim / 32
+__global__ void __launch_bounds__(kAttnDecodeThreads)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ kv_lens, const int* __restrict__ page_table, int table_stride,
+                        const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv_heads,
+                        int window, int n_splits) {
+    constexpr int D = KB * 32;
+    constexpr int NJ = D / 8;  // output tiles of 8 dims
+    extern __shared__ float smem[];  // [warps][16][D] outputs, then [warps][16][2] (m, l)
+    float* o_s = smem;
+    float* ml_s = smem + kAttnDecodeWarps * 16 * D;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int group = n_heads / n_kv_heads;
+    const int kv_len = kv_lens[seq];
+    const int lo = window > 0 ? max(0, kv_len - window) : 0;
+    const int first_block = lo / 32, last_block = (kv_len - 1) / 32;
+    const int per_split = (last_block - first_block + 1 + n_splits - 1) / n_splits;
+    const int blk_begin = first_block + split * per_split;
+    const int blk_end = min(blk_begin + per_split, last_block + 1);
+    const int* pages = page_table + (size_t)seq * table_stride;
+    const size_t page_stride = (size_t)n_kv_heads * kPageTokens * D;
+    const size_t head_off = (size_t)kvh * kPageTokens * D;
+
+    // query fragments: rows = the heads of this group (rows >= group are zero)
+    uint4 ql[KB], qh[KB];
+    {
+        const __nv_bfloat16* qrow = q + (size_t)seq * q_row_stride + (size_t)kvh * group * D;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            ql[kb] = g < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+            qh[kb] = g + 8 < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    float o[NJ][4];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8; l is this lane's share
+    const float sqrt_d = sqrtf((float)D);
+
+    for (int blk = blk_begin + warp; blk < blk_end; blk += kAttnDecodeWarps) {
+        const int base = blk * 32;
+        const size_t page_base = (size_t)pages[base / kPageTokens] * page_stride + head_off;
+        const int in_page = base % kPageTokens;
+        const __nv_bfloat16* kp = k_pool + page_base;
+        const __nv_bfloat16* vp = v_pool + page_base;
+
+        // all loads of the block are issued before the arithmetic that needs them
+        uint4 kf[4][KB];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = (g >> 1) * 8 + 2 * i + (g & 1);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+                kf[i][kb] = ldg_stream(kp + (size_t)(in_page + key) * D + kb * 32 + t * 8);
+        }
+        uint4 vf[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) vf[j] = ldg_stream(vp + (size_t)(8 * j + g) * kPageTokens + in_page + t * 8);
+
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[i][c] = 0.f;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                mma16816(s[i], ql[kb].x, qh[kb].x, ql[kb].y, qh[kb].y, kf[i][kb].x, kf[i][kb].y);
+                mma16816(s[i], ql[kb].z, qh[kb].z, ql[kb].w, qh[kb].w, kf[i][kb].z, kf[i][kb].w);
+            }
+        }
+        // lane t's columns of tile i are keys base + 8t + 2i and + 2i + 1
+        float bm_lo = -INFINITY, bm_hi = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = base + 8 * t + 2 * i + e;
+                const bool ok = key >= lo && key < kv_len;
+                s[i][e] = ok ? s[i][e] / sqrt_d : -INFINITY;
+                s[i][2 + e] = ok ? s[i][2 + e] / sqrt_d : -INFINITY;
+                bm_lo = fmaxf(bm_lo, s[i][e]);
+                bm_hi = fmaxf(bm_hi, s[i][2 + e]);
+            }
+        bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));
+        bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 2));
+        bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
+        bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
+        const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
+        // a block always holds at least one valid key (blocks run from lo/32 to (kv_len-1)/32), so mn is finite
+        const float c_lo = expf(m_lo - mn_lo), c_hi = expf(m_hi - mn_hi);
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        l_lo *= c_lo;
+        l_hi *= c_hi;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) { o[j][0] *= c_lo; o[j][1] *= c_lo; o[j][2] *= c_hi; o[j][3] *= c_hi; }
+        uint32_t pa[4][2];  // per tile: packed probabilities of rows g and g + 8
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float p0 = expf(s[i][0] - mn_lo), p1 = expf(s[i][1] - mn_lo);
+            const float p2 = expf(s[i][2] - mn_hi), p3 = expf(s[i][3] - mn_hi);
+            l_lo += p0 + p1;
+            l_hi += p2 + p3;
+            pa[i][0] = pack_bf16(p0, p1);
+            pa[i][1] = pack_bf16(p2, p3);
+        }
+        const int n_valid = kv_len - (base + 8 * t);  // keys of this lane's V slice that exist
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const uint4 v = n_valid >= 8 ? vf[j] : keep_first(vf[j], max(n_valid, 0));
+            mma16816(o[j], pa[0][0], pa[0][1], pa[1][0], pa[1][1], v.x, v.y);
+            mma16816(o[j], pa[2][0], pa[2][1], pa[3][0], pa[3][1], v.z, v.w);
+        }
+    }
+
+    // the lanes of a row share l; then the warps of the CTA are merged through shared memory
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* ow = o_s + (size_t)warp * 16 * D;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        ow[g * D + 8 * j + 2 * t] = o[j][0];
+        ow[g * D + 8 * j + 2 * t + 1] = o[j][1];
+        ow[(g + 8) * D + 8 * j + 2 * t] = o[j][2];
+        ow[(g + 8) * D + 8 * j + 2 * t + 1] = o[j][3];
+    }
+    if (t == 0) {
+        ml_s[(warp * 16 + g) * 2] = m_lo;
+        ml_s[(warp * 16 + g) * 2 + 1] = l_lo;
+        ml_s[(warp * 16 + g + 8) * 2] = m_hi;
+        ml_s[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads) {
+        const int row = idx / D, d = idx % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnDecodeWarps; ++w) m = fmaxf(m, ml_s[(w * 16 + row) * 2]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnDecodeWarps; ++w) {
+            const float mw = ml_s[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - m);
+            l += ml_s[(w * 16 + row) * 2 + 1] * f;
+            acc += o_s[((size_t)w * 16 + row) * D + d] * f;
+        }
+        const int head = kvh * group + row;
+        if (n_splits == 1) {
+            out[((size_t)seq * n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            const size_t p = ((size_t)seq * n_heads + head) * n_splits + split;
+            part_o[p * D + d] = acc;
+            if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
+        }
+    }
+}
+
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+    const size_t row = blockIdx.x;  // seq * n_heads + head
+    const float* ml = part_ml + row * n_splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float l = 0.f, acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = ml[2 * s];
+            const float f = ms == -INFINITY ? 0.f : expf(ms - m);
+            l += ml[2 * s + 1] * f;
+            acc += part_o[(row * n_splits + s) * D + d] * f;
+        }
+        out[row * D + d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
+}  // namespace b200
+
+// Floats of scratch the call needs for (n_seqs, n_heads, head_dim, n_splits); 0 when n_splits == 1.
+extern "C" long long b200_attention_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits) {
+    if (n_splits <= 1) return 0;
+    return (long long)n_seqs * n_heads * n_splits * (head_dim + 2);
+}
+
+extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens,
+                                     const int* page_table, int table_stride, const void* k_pool, const void* v_pool,
+                                     float* scratch, long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads,
+                                     int head_dim, int window, int n_splits, cudaStream_t stream) {
+    using namespace b200;
+    if (n_seqs <= 0) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits < 1) return kErrBadArgument;
+    const int group = n_heads / n_kv_heads;
+    if (group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128 || q_row_stride % 8 != 0) return kErrUnsupportedSize;
+    if (n_seqs > 65535 || n_kv_heads > 65535) return kErrUnsupportedSize;
+    if (scratch_floats < b200_attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)) return 10003;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * head_dim;
+    dim3 grid(n_splits, n_kv_heads, n_seqs);
+    const size_t smem = sizeof(float) * kAttnDecodeWarps * 16 * (head_dim + 2);
+    auto qq = (const __nv_bfloat16*)q;
+    auto kk = (const __nv_bfloat16*)k_pool;
+    auto vv = (const __nv_bfloat16*)v_pool;
+    auto oo = (__nv_bfloat16*)out;
+#define B200_LAUNCH(KB)                                                                                          \
+    attention_decode_kernel<KB><<<grid, kAttnDecodeThreads, smem, stream>>>(qq, q_row_stride, oo, kv_lens, page_table, \
+        table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits)
+    switch (head_dim / 32) {
+        case 1: B200_LAUNCH(1); break;
+        case 2: B200_LAUNCH(2); break;
+        case 3: B200_LAUNCH(3); break;
+        default: B200_LAUNCH(4); break;
+    }
+#undef B200_LAUNCH
+    int st = launch_status();
+    if (st != 0 || n_splits == 1) return st;
+    attention_decode_merge_kernel<<<n_seqs * n_heads, head_dim <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, oo, n_splits, head_dim);
+    return launch_status();
+}

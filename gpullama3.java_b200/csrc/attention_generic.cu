@@ -98,11 +98,11 @@ attention_paged_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict_
             const int n_keys = min(kAttnThreads, pos - base + 1);
             for (int i = grp; i < n_keys; i += groups) {
                 const int kk = base + i;
-                const T* vr = v_pool + (size_t)pages[kk / kPageTokens] * page_stride + head_off +
-                              (size_t)(kk % kPageTokens) * head_dim;
+                // values are stored transposed: [head_dim][kPageTokens] per page and kv head
+                const T* vr = v_pool + (size_t)pages[kk / kPageTokens] * page_stride + head_off + (kk % kPageTokens);
                 const float pi = s_s[i];
-                if (d0 < head_dim) acc0 += pi * to_f32<T>(vr[d0]);
-                if (d1 < head_dim) acc1 += pi * to_f32<T>(vr[d1]);
+                if (d0 < head_dim) acc0 += pi * to_f32<T>(vr[(size_t)d0 * kPageTokens]);
+                if (d1 < head_dim) acc1 += pi * to_f32<T>(vr[(size_t)d1 * kPageTokens]);
             }
         }
         __syncthreads();

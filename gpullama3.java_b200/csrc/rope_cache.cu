@@ -9,8 +9,11 @@
 // 1 pairs (j, j + rotary_dim/2), the layout of checkpoints whose q/k rows were not permuted.
 // Dimensions at and beyond rotary_dim pass through unrotated.
 //
-// Cache layout of one cache entry: [page][kv_head][kPageTokens][head_dim]; the page of position p
-// of sequence s is page_table[s * table_stride + p / kPageTokens].
+// Cache layout of one cache entry.  Keys: [page][kv_head][kPageTokens][head_dim] (a row per
+// position).  Values: [page][kv_head][head_dim][kPageTokens] (transposed: a row per dimension,
+// positions contiguous), which is the operand layout the attention kernels multiply
+// probabilities with.  The page of position p of sequence s is
+// page_table[s * table_stride + p / kPageTokens].
 #include "common.cuh"
 
 namespace b200 {
@@ -27,10 +30,11 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     T* row = qkv + (size_t)t * (q_dim + 2 * kv_dim);
     const int half = rotary_dim / 2;
 
-    size_t cache_base = 0;
+    size_t cache_base = 0, v_base = 0;
     if (write_cache) {
         const int page = page_table[(size_t)seq_ids[t] * table_stride + pos / kPageTokens];
         cache_base = ((size_t)page * n_kv_heads * kPageTokens + (pos % kPageTokens)) * head_dim;
+        v_base = (size_t)page * n_kv_heads * kPageTokens * head_dim + (pos % kPageTokens);
     }
     const size_t head_stride = (size_t)kPageTokens * head_dim;
 
@@ -65,7 +69,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     }
     for (int u = threadIdx.x; u < kv_dim; u += blockDim.x) {
         const int g = u / head_dim, d = u % head_dim;
-        v_pool[cache_base + g * head_stride + d] = row[q_dim + kv_dim + u];
+        v_pool[v_base + g * head_stride + (size_t)d * kPageTokens] = row[q_dim + kv_dim + u];
     }
 }
 

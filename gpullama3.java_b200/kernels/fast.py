@@ -8,10 +8,23 @@ from __future__ import annotations
 
 import torch
 
+from . import ops
+
 
 def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -> bool:
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    if a.shape[0] <= 16:
+        return ops.gemm_decode(a, w, c, epilogue)
     return False
 
 
 def try_attention(qkv, out, ctx, page_table, cache, mixer) -> bool:
+    if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
+        splits = ctx.extras.get("decode_splits")
+        if splits is None:
+            splits = ops.attention_decode_splits(ctx.n_seqs, mixer.n_kv_heads, ctx.max_kv_len)
+        ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,
+                             mixer.n_kv_heads, mixer.head_dim, mixer.window or 0, splits)
+        return True
     return False

@@ -38,6 +38,11 @@ _SIGNATURES = {
                                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
     "b200_gemm_generic": ("gemm_generic", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                            c_int, c_int, c_int, c_int]),
+    "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_int]),
+    "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                   c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
+                                                   c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
 }
@@ -131,6 +136,7 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, seq_ids: torch.
         assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
         assert k_pool.is_contiguous() and v_pool.is_contiguous()
         assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+        assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
     _check(_fn("b200_rope_cache_write")(
         qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], inv_freq.data_ptr(), k_pool.data_ptr() if write_cache else None,
@@ -147,6 +153,7 @@ def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, posit
     _dev(q, out, positions, seq_ids, page_table, k_pool, v_pool)
     assert out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.dtype == q.dtype == k_pool.dtype
     assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
     _check(_fn("b200_attention_paged")(
         q.data_ptr(), q_row_stride, out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(), seq_ids.data_ptr(),
         page_table.data_ptr(), page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), out.shape[0], n_heads,
@@ -168,6 +175,53 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     _check(_fn("b200_gemm_generic")(
         a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), w.stride(0), c.data_ptr(),
         dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_generic")
+
+
+def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
+    """The decode-step matrix product (bfloat16 operands, at most 16 tokens, K a multiple of 32).
+    Returns False, having done nothing, for operands it does not take."""
+    M, K = a.shape
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M > 16 or K % 32 or a.stride(1) != 1
+            or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
+        return False
+    _dev(a, w, c)
+    N = w.shape[0]
+    assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
+    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    _check(_fn("b200_gemm_decode")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
+                                   dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_decode")
+    return True
+
+
+def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) and n_heads // n_kv_heads <= 16
+
+
+def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, target_ctas: int = 592) -> int:
+    """How many spans each sequence's keys are cut into so that the grid fills the GPU."""
+    blocks = max(1, (max_kv_len + 31) // 32)
+    want = -(-target_ctas // max(1, n_seqs * n_kv_heads))
+    return max(1, min(want, blocks // 2 if blocks >= 2 else 1, 64))
+
+
+def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,
+                     page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int,
+                     n_kv_heads: int, head_dim: int, window: int, n_splits: int,
+                     scratch: torch.Tensor | None = None) -> None:
+    """One query token per sequence (row i of q belongs to sequence i) over kv_lens[i] cached keys.
+    ``scratch``: float32 workspace for the spans' partial results (allocated here when absent)."""
+    _dev(q, out, kv_lens, page_table, k_pool, v_pool)
+    n_seqs = out.shape[0]
+    assert q.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    need = n_seqs * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+    if need and (scratch is None or scratch.numel() < need):
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    _check(_fn("b200_attention_decode")(
+        q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
+        n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, _stream()), "attention_decode")
 
 
 # --------------------------------------------------------------------------- sampling

@@ -47,7 +47,7 @@ def test_groups_have_storage_of_their_own():
     assert len(c.kv_groups) == 2
     g0, g1 = c.kv_groups
     assert g0.entries == [0, 1] and g1.entries == [2]
-    assert tuple(g0.k.shape) == (2, 6, 2, PAGE_TOKENS, 16) and tuple(g1.v.shape) == (1, 6, 1, PAGE_TOKENS, 32)
+    assert tuple(g0.k.shape) == (2, 6, 2, PAGE_TOKENS, 16) and tuple(g1.v.shape) == (1, 6, 1, 32, PAGE_TOKENS)
     v0, v1, v2 = c.view(0), c.view(1), c.view(2)
     assert v0.group == v1.group == 0 and v2.group == 1
     assert v0.k.data_ptr() != v1.k.data_ptr() and tuple(v2.k.shape) == (6, 1, PAGE_TOKENS, 32)

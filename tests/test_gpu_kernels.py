@@ -61,7 +61,7 @@ def _paged_setup(dtype, n_seqs, kv_lens, KVH, D, n_pages, seed=0):
     perm = torch.randperm(n_pages, generator=g).tolist()
     table = torch.zeros(n_seqs, width, dtype=torch.int32)
     k_pool = torch.zeros(n_pages, KVH, 64, D)
-    v_pool = torch.zeros(n_pages, KVH, 64, D)
+    v_pool = torch.zeros(n_pages, KVH, D, 64)
     dense = []
     for s, n in enumerate(kv_lens):
         k = torch.randn(n, KVH, D, generator=g).to(dtype).float()
@@ -72,7 +72,7 @@ def _paged_setup(dtype, n_seqs, kv_lens, KVH, D, n_pages, seed=0):
             table[s, lp] = page
             m = min(64, n - lp * 64)
             k_pool[page, :, :m] = k[lp * 64:lp * 64 + m].transpose(0, 1)
-            v_pool[page, :, :m] = v[lp * 64:lp * 64 + m].transpose(0, 1)
+            v_pool[page, :, :, :m] = v[lp * 64:lp * 64 + m].permute(1, 2, 0)
     return k_pool.to(dtype).cuda(), v_pool.to(dtype).cuda(), table.cuda(), dense
 
 
@@ -143,7 +143,7 @@ def test_rope_and_cache_write(dtype, pairing, H, KVH, D, rotary):
     table[1, 63] = 65
     table[1, 0] = 66
     k_pool = torch.zeros(n_pages, KVH, 64, D, dtype=dtype, device="cuda")
-    v_pool = torch.zeros_like(k_pool)
+    v_pool = torch.zeros(n_pages, KVH, D, 64, dtype=dtype, device="cuda")
     buf = qkv.clone().cuda()
     ops().rope_cache_write(buf, torch.tensor(positions, dtype=torch.int32, device="cuda"),
                            torch.tensor(seq_ids, dtype=torch.int32, device="cuda"), table.cuda(),
@@ -159,7 +159,7 @@ def test_rope_and_cache_write(dtype, pairing, H, KVH, D, rotary):
     for i, (p, s) in enumerate(zip(positions, seq_ids)):
         page = int(table[s, p // 64])
         torch.testing.assert_close(k_pool[page, :, p % 64].float().cpu(), k[i].to(dtype).float(), **t)
-        assert torch.equal(v_pool[page, :, p % 64].float().cpu(), v[i])
+        assert torch.equal(v_pool[page, :, :, p % 64].float().cpu(), v[i])
     assert int((k_pool.float().abs().sum(dim=(1, 3)) > 0).sum()) == T   # no other cache row was touched
 
 
@@ -183,6 +183,80 @@ def test_gemm_generic_and_its_epilogues(a_dtype, w_dtype, M, N, K):
     o.gemm_generic(a, w, h, o.EPILOGUE_GATED_SILU)
     gated = P.swiglu(ref[:, 0::2], ref[:, 1::2])
     torch.testing.assert_close(h.float().cpu(), gated.float().to(a_dtype).float(), **tol(a_dtype, gated))
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N, K", [(16, 32), (50, 96), (200, 2048), (4098, 64), (5000, 1056)])
+def test_gemm_decode_and_its_epilogues(M, N, K):
+    o = ops()
+    g = torch.Generator().manual_seed(M * N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    ref = a.float().cpu().double() @ w.float().cpu().double().t()
+    for c_dtype in (torch.bfloat16, torch.float32):
+        c = torch.full((M, N), 7.0, dtype=c_dtype, device="cuda")
+        assert o.gemm_decode(a, w, c, o.EPILOGUE_STORE)
+        torch.testing.assert_close(c.float().cpu(), ref.float().to(c_dtype).float(), **tol(c_dtype, ref))
+    res0 = torch.randn(M, N, generator=g)
+    res = res0.clone().cuda()
+    assert o.gemm_decode(a, w, res, o.EPILOGUE_RESIDUAL_ADD)
+    torch.testing.assert_close(res.cpu(), (res0.double() + ref).float(), **tol(torch.float32, ref))
+    h = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+    assert o.gemm_decode(a, w, h, o.EPILOGUE_GATED_SILU)
+    gated = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+    torch.testing.assert_close(h.float().cpu(), gated.float().to(torch.bfloat16).float(), **tol(torch.bfloat16, gated))
+    # a strided view of a wider buffer, and shapes the kernel leaves to the plain one
+    wide = torch.randn(M, K + 64, generator=g).to(torch.bfloat16).cuda()
+    c = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    assert o.gemm_decode(wide[:, :K], w, c)
+    torch.testing.assert_close(c.cpu(), (wide[:, :K].float().cpu().double() @ w.float().cpu().double().t()).float(),
+                               **tol(torch.float32, ref))
+    assert not o.gemm_decode(torch.zeros(17, K, dtype=torch.bfloat16, device="cuda"), w, c)
+    assert not o.gemm_decode(a.float(), w, c)
+
+
+@pytest.mark.parametrize("H, KVH, D, window", [(4, 2, 32, 0), (32, 8, 64, 0), (3, 1, 96, 0), (16, 1, 128, 0),
+                                               (8, 8, 64, 0), (24, 2, 32, 0), (8, 2, 64, 100), (4, 1, 128, 33)])
+@pytest.mark.parametrize("n_splits", [1, 3, 16])
+def test_attention_decode_against_plain(H, KVH, D, window, n_splits):
+    kv_lens = [1, 31, 32, 33, 64, 65, 300, 517]
+    k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=40, seed=D + H)
+    g = torch.Generator().manual_seed(2)
+    B = len(kv_lens)
+    q = (torch.randn(B, H, D, generator=g) * 2).to(torch.bfloat16)
+    refs = []
+    for s, n in enumerate(kv_lens):
+        k, v = dense[s]
+        lo = max(0, n - window) if window else 0
+        qq = q[s].float().reshape(1, H, D).expand(n - lo, H, D).contiguous()
+        refs.append(P.causal_attention(qq, k[lo:], v[lo:])[-1])
+    ref = torch.stack(refs).reshape(B, H * D)
+    qkv = torch.cat([q.reshape(B, H * D), torch.randn(B, 2 * KVH * D).to(torch.bfloat16)], dim=1).cuda().contiguous()
+    out = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    ops().attention_decode(qkv, qkv.shape[1], out, lens, table, k_pool, v_pool, H, KVH, D, window, n_splits)
+    # probabilities are rounded to bfloat16 before they meet the values: 2^-8 of the largest output
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
+
+
+def test_attention_decode_ignores_what_lies_beyond_a_sequence():
+    """Slots are used again without clearing: stale or non-finite numbers after a sequence's last
+    position (same page) and in pages of other sequences must not reach the output."""
+    H, KVH, D = 8, 2, 64
+    kv_lens = [37, 70]
+    k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, 2, kv_lens, KVH, D, n_pages=8, seed=4)
+    q = torch.randn(2, H * D).to(torch.bfloat16)
+    qkv = torch.cat([q, torch.zeros(2, 2 * KVH * D, dtype=torch.bfloat16)], dim=1).cuda()
+    lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    clean = torch.empty(2, H * D, dtype=torch.bfloat16, device="cuda")
+    ops().attention_decode(qkv, qkv.shape[1], clean, lens, table, k_pool, v_pool, H, KVH, D, 0, 2)
+    for s, n in enumerate(kv_lens):
+        page = int(table[s, (n - 1) // 64])
+        k_pool[page, :, n % 64:] = float("nan")
+        v_pool[page, :, :, n % 64:] = float("inf")
+    dirty = torch.empty_like(clean)
+    ops().attention_decode(qkv, qkv.shape[1], dirty, lens, table, k_pool, v_pool, H, KVH, D, 0, 2)
+    assert torch.equal(clean, dirty)
 
 
 @pytest.mark.parametrize("V", [5, 384, 1000, 128256])
@@ -245,7 +319,7 @@ def test_kernels_refuse_what_they_cannot_do():
     pool = torch.zeros(1, 1, 64, 24, device="cuda")
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(KernelError, match="unsupported size"):
-        o.attention_paged(q, 72, out, z, z, z.reshape(1, 1), pool, pool, 1, 1, 24, 0)   # head size not a step of 16
+        o.attention_paged(q, 72, out, z, z, z.reshape(1, 1), pool, pool.transpose(2, 3).contiguous(), 1, 1, 24, 0)   # head size not a step of 16
     with pytest.raises(KernelError):
         o.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4))   # CPU tensors
     with pytest.raises(KernelError, match="bad argument"):
