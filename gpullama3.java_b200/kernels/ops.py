@@ -43,6 +43,8 @@ _SIGNATURES = {
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                    c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
                                                    c_int, c_int]),
+    "b200_attention_prefill": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
 }
@@ -222,6 +224,21 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_l
         q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
         n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, _stream()), "attention_decode")
+
+
+def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,
+                      kv_lens: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                      n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int) -> None:
+    """Causal attention of packed query tokens: sequence i owns rows cu_seqlens[i]..cu_seqlens[i+1],
+    which are its last positions (kv_lens[i] - q_len .. kv_lens[i] - 1); keys come from the cache."""
+    _dev(q, out, cu_seqlens, kv_lens, page_table, k_pool, v_pool)
+    assert q.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    _check(_fn("b200_attention_prefill")(
+        q.data_ptr(), q_row_stride, out.data_ptr(), cu_seqlens.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), n_seqs, max_q_len, n_heads, n_kv_heads, head_dim,
+        int(window), _stream()), "attention_prefill")
 
 
 # --------------------------------------------------------------------------- sampling
