@@ -38,7 +38,8 @@ class Engine:
         self.cache = model.new_cache(max_tokens, max_slots=max(max_batch, 1))
         self.step_fn = StepFunction(model, self.cache)
         self.max_length = max_length if max_length is not None else self.cache.n_pages * 64
-        self.generator = Generator(self.step_fn, self.cache, Sampler, max_batch=max_batch, max_length=self.max_length)
+        # the generation loop samples from a step's logits before it runs the next step
+        self.generator = Generator(lambda inputs: self.step_fn(inputs, reuse_output=True), self.cache, Sampler, max_batch=max_batch, max_length=self.max_length)
 
     # ---- construction
     @classmethod

@@ -67,6 +67,11 @@ class CausalLM:
                 raise ConfigError(f"schedule entry {i} reads cache {e.cache} before any entry writes it")
         self._cache_needs = needs
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be recorded once and replayed as a CUDA graph."""
+        return all(p.graph_safe for p in self.named_parts().values()) and all(b.graph_safe for b in self.blocks)
+
     def cache_needs(self) -> dict[int, KVCacheNeed | StateNeed]:
         return dict(self._cache_needs)
 

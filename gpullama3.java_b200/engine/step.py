@@ -29,12 +29,10 @@ class SequenceInput:
     want: list[int] = field(default_factory=list)  # places among ``tokens`` whose logits are wanted
 
 
-def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_pos: list[int],
-                  token_lists: list, logit_rows: list[int]) -> tuple[StepContext, torch.Tensor | None]:
-    """Pack one pass into a StepContext.  All integers go to the device in one copy."""
+def _pack(cache: SequenceCache, slots, start_pos, token_lists, logit_rows, widths=None):
+    """The integer arrays of one pass, in the order they are laid out on the device."""
     n = len(slots)
     q_lens = [len(t) for t in token_lists]
-    T = sum(q_lens)
     tokens = np.concatenate([np.asarray(t, dtype=np.int32) for t in token_lists])
     positions = np.concatenate([np.arange(s, s + q, dtype=np.int32) for s, q in zip(start_pos, q_lens)])
     seq_ids = np.repeat(np.arange(n, dtype=np.int32), q_lens)
@@ -44,43 +42,156 @@ def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_p
     tables = []
     for gi in range(len(cache.kv_groups)):
         rows = cache.page_rows(gi, slots)
-        width = max(1, max(len(r) for r in rows))
-        tab = np.zeros((n, width), dtype=np.int32)
+        width = widths[gi] if widths is not None else max(1, max(len(r) for r in rows))
+        tab = np.zeros((n, width), dtype=np.int32)  # unused entries name page 0: never read, never out of range
         for i, r in enumerate(rows):
             if r:
                 tab[i, :len(r)] = np.maximum(np.asarray(r, dtype=np.int32), 0)
         tables.append(tab)
     pieces = [tokens, positions, seq_ids, cu, kv_lens, np.asarray(slots, dtype=np.int32),
               np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
-    flat = np.concatenate(pieces)
-    host = torch.from_numpy(flat)
+    return pieces, q_lens, [t.shape for t in tables]
+
+
+def _context_over(dev: torch.Tensor, sizes, table_shapes, dtype, device, slots, start_pos, q_lens):
+    views, off = [], 0
+    for n in sizes:
+        views.append(dev[off:off + n])
+        off += n
+    ctx = StepContext(
+        dtype=dtype, device=device, n_seqs=len(slots), n_tokens=sum(q_lens), slots=list(slots),
+        start_pos=list(start_pos), q_lens=list(q_lens), all_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens),
+        max_kv_len=max(s + q for s, q in zip(start_pos, q_lens)), tokens=views[0], positions=views[1],
+        seq_ids=views[2], cu_seqlens=views[3], kv_lens=views[4], slots_dev=views[5],
+        page_tables=[v.view(shape) for v, shape in zip(views[7:], table_shapes)])
+    return ctx, views[6]
+
+
+def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_pos: list[int],
+                  token_lists: list, logit_rows: list[int]) -> tuple[StepContext, torch.Tensor | None]:
+    """Pack one pass into a StepContext.  All integers go to the device in one copy."""
+    pieces, q_lens, table_shapes = _pack(cache, slots, start_pos, token_lists, logit_rows)
+    host = torch.from_numpy(np.concatenate(pieces))
     if device.type == "cuda":
         host = host.pin_memory()
     dev = host.to(device, non_blocking=True)
-    views, off = [], 0
-    for p in pieces:
-        views.append(dev[off:off + p.size])
-        off += p.size
-    ctx = StepContext(
-        dtype=dtype, device=device, n_seqs=n, n_tokens=T, slots=list(slots), start_pos=list(start_pos),
-        q_lens=q_lens, all_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens),
-        max_kv_len=int(kv_lens.max()), tokens=views[0], positions=views[1], seq_ids=views[2], cu_seqlens=views[3],
-        kv_lens=views[4], slots_dev=views[5],
-        page_tables=[v.view(t.shape) for v, t in zip(views[7:], tables)])
+    ctx, rows = _context_over(dev, [p.size for p in pieces], table_shapes, dtype, device, slots, start_pos, q_lens)
     ctx.extras["host_buffer"] = host  # keep the pinned source alive until the copy has run
-    rows = views[6] if logit_rows else None
-    return ctx, rows
+    return ctx, (rows if logit_rows else None)
+
+
+class DecodeGraph:
+    """One captured decode step for a fixed number of sequences and fixed page-table widths.
+
+    Everything that changes from step to step (tokens, positions, lengths, page tables) lives in
+    one device buffer at fixed addresses that is refreshed by a single copy before each replay, so
+    the captured launch sequence is valid for any lengths the table widths can address.  The
+    reference rebuilds nothing per token either: its plan is a list of pre-built task graphs
+    replayed for every token (tornadovm/TornadoVMMasterPlan.java:149-175 of the reference
+    project)."""
+
+    def __init__(self, model, cache: SequenceCache, n_seqs: int, widths: list[int]):
+        from ..kernels import ops
+
+        self.model, self.cache, self.n, self.widths = model, cache, n_seqs, list(widths)
+        self.sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs, n_seqs] + [n_seqs * w for w in widths]
+        self.table_shapes = [(n_seqs, w) for w in widths]
+        total = sum(self.sizes)
+        self.host = torch.empty(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.empty(total, dtype=torch.int32, device=model.device)
+        self.copied = torch.cuda.Event()
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.n_launches = 0
+        kv_heads = [g.need.n_kv_heads for g in cache.kv_groups] or [1]
+        self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), max(widths, default=1) * PAGE_TOKENS)
+
+    def refresh(self, slots, start_pos, tokens) -> None:
+        pieces, _, _ = _pack(self.cache, slots, start_pos, [[t] for t in tokens], list(range(self.n)), self.widths)
+        self.copied.synchronize()  # the previous step's copy must have left the staging buffer
+        np.concatenate(pieces, out=self.host.numpy())
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+    def _forward(self, slots, start_pos):
+        ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, slots,
+                                  start_pos, [1] * self.n)
+        ctx.extras["decode_splits"] = self.splits
+        return self.model.forward(ctx, self.cache, rows)
+
+    def run(self, slots, start_pos, tokens) -> torch.Tensor:
+        from ..kernels import ops
+
+        self.refresh(slots, start_pos, tokens)
+        if self.graph is None:
+            # the first step runs as ordinary launches (this also loads every kernel library the step
+            # needs); the same launch sequence is then recorded, without running, for later steps
+            out = self._forward(slots, start_pos)
+            torch.cuda.synchronize()
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            import gc
+            gc_was_on = gc.isenabled()
+            gc.disable()  # a collection while recording could free device or pinned memory, which is not allowed then
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = self._forward(slots, start_pos)
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            self.n_launches = ops.launch_count() - before
+            self.graph = graph
+            return out
+        self.graph.replay()
+        return self.logits
 
 
 class StepFunction:
     """``step(inputs)`` -> float32 logits [number of wanted places, vocab] on the device, in the
     order of the inputs and of each input's ``want``."""
 
-    def __init__(self, model, cache: SequenceCache, *, max_pass_tokens: int = 16384, max_sequence_chunk: int = 8192):
+    def __init__(self, model, cache: SequenceCache, *, max_pass_tokens: int = 16384, max_sequence_chunk: int = 8192,
+                 use_graphs: bool = True, max_graph_batch: int = 256):
         self.model, self.cache = model, cache
         self.max_pass_tokens = max_pass_tokens
         self.max_sequence_chunk = max_sequence_chunk
         self.vocab_size = model.config.vocab_size
+        # decode steps are replayed from CUDA graphs when every part says its launches do not depend on
+        # host-side values of the step (parts default to "no": a part written without that in mind stays right)
+        self.use_graphs = bool(use_graphs and model.device.type == "cuda" and getattr(model, "graph_safe", False))
+        self.max_graph_batch = max_graph_batch
+        self.reuse_output = False   # True: the caller consumes the logits before the next step (no copy is made)
+        self._graphs: dict[tuple, DecodeGraph] = {}
+        self.graph_launches = 0     # kernel launches replayed from graphs so far
+
+    def _decode_with_graph(self, inputs: list[SequenceInput], reuse_output: bool) -> torch.Tensor | None:
+        cache = self.cache
+        n = len(inputs)
+        slots = [s.slot for s in inputs]
+        start = [cache.length(s) for s in slots]
+        widths = []
+        for gi in range(len(cache.kv_groups)):
+            need = max(len(r) for r in cache.page_rows(gi, slots))
+            w = 4
+            while w < need:
+                w *= 2
+            widths.append(w)
+        key = (n, tuple(widths))
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = DecodeGraph(self.model, cache, n, widths)
+        replayed = g.graph is not None
+        logits = g.run(slots, start, [s.tokens[0] for s in inputs])
+        if replayed:
+            self.graph_launches += g.n_launches
+        for s in slots:
+            cache.commit(s, 1)
+        wanted = [i for i, s in enumerate(inputs) if s.want]
+        if not wanted:
+            return None
+        if len(wanted) != n:
+            return logits[torch.tensor(wanted, device=logits.device)]
+        return logits if (reuse_output or not replayed) else logits.clone()
 
     def _validate(self, inputs: list[SequenceInput]) -> None:
         if not inputs:
@@ -101,11 +212,15 @@ class StepFunction:
                 if not (0 <= w < len(s.tokens)):
                     raise StepError(f"input {i}: wanted place {w} is outside its {len(s.tokens)} tokens")
 
-    def __call__(self, inputs: list[SequenceInput]) -> torch.Tensor | None:
+    def __call__(self, inputs: list[SequenceInput], reuse_output: bool | None = None) -> torch.Tensor | None:
+        """``reuse_output=True``: the caller is done with the returned logits before the next step (the
+        tensor may be the fixed output buffer of a recorded decode step, which the next step overwrites)."""
         self._validate(inputs)
         cache, model = self.cache, self.model
         # room for every token of the step is taken before anything is written
         cache.reserve([(s.slot, len(s.tokens)) for s in inputs])
+        if self.use_graphs and len(inputs) <= self.max_graph_batch and all(len(s.tokens) == 1 for s in inputs):
+            return self._decode_with_graph(inputs, self.reuse_output if reuse_output is None else reuse_output)
         n_want = sum(len(s.want) for s in inputs)
         out_offsets, off = [], 0
         for s in inputs:

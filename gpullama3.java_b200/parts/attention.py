@@ -17,6 +17,8 @@ from .linear import Linear
 
 
 class GroupedQueryAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  window: int | None = None):
         if n_heads % n_kv_heads:

@@ -48,6 +48,11 @@ class StepContext:
 class Part:
     """Common face of all parts."""
 
+    # True when the part's launches in a decode step depend only on device memory (the step
+    # context's tensors, the cache), never on host-side numbers of the step such as slots or
+    # lengths: only then may a decode step be recorded once and replayed as a CUDA graph.
+    graph_safe: bool = False
+
     def parameters(self) -> dict[str, ParamSpec]:
         """Local parameter names -> shape and random-init kind."""
         return {}

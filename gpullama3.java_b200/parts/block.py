@@ -6,6 +6,10 @@ from .base import Block, StepContext, register_block
 
 
 class PreNormBlock(Block):
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.children().values())
+
     def forward(self, residual, ctx: StepContext, cache, writes_cache=True):
         self.mixer.forward(self.mixer_norm.forward(residual, ctx.dtype), ctx, cache, residual, writes_cache)
         self.feed_forward.forward(self.feed_forward_norm.forward(residual, ctx.dtype), ctx, residual)

@@ -15,6 +15,8 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
         self.table: torch.Tensor | None = None
@@ -33,6 +35,8 @@ class TokenEmbedding(Part):
 
 
 class OutputHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None):
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to
         self.linear: Linear | None = None

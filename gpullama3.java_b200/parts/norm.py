@@ -10,6 +10,8 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, dim: int, eps: float):
         self.dim, self.eps = int(dim), float(eps)
         self.weight: torch.Tensor | None = None

@@ -50,6 +50,8 @@ def llama3_inverse_frequencies(head_dim: int, theta: float, scaling: dict | None
 
 
 class RotaryPositionEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, theta: float, pairing: str = "half", scaling: dict | None = None,
                  rotary_dim: int | None = None):
         if pairing not in PAIRING_CODES:
@@ -73,6 +75,8 @@ class RotaryPositionEncoding(PositionEncoding):
 
 
 class NoPositionEncoding(PositionEncoding):
+    graph_safe = True
+
     """Queries and keys pass unrotated (rotary_dim = 0)."""
 
     def __init__(self, head_dim: int = 0):
