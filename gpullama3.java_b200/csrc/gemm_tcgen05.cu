@@ -1,0 +1,301 @@
+// Prefill matrix product in bfloat16 on the 5th-generation tensor cores:
+//     C[M, N] = A[M, K] W[N, K]^T      (A activations, W a weight as stored: one row per output)
+// The reference computes the same products row by row on CUDA cores
+// (tornadovm/TransformerComputeKernelsLayered.java:901-930 of the reference project, fused
+// residual :766-784, fused SiLU gate :808-826); here a 128 x BN tile of C is accumulated in
+// tensor memory by tcgen05.mma, fed by TMA through a ring of shared-memory stages.
+//
+// One CTA computes one tile.  Roles (192 threads):
+//   warp 0, one lane   producer: waits for a free stage, arms its mbarrier with the byte count and
+//                      issues two TMA loads (A box 64x128, W box 64xBN; 128-byte swizzle)
+//   warp 1, one lane   issues four tcgen05.mma (K = 16 each) per stage into the TMEM accumulator,
+//                      then tcgen05.commit onto the stage's "empty" mbarrier; after the last stage
+//                      a commit onto the "accumulator full" mbarrier.  Warp 1 also owns the TMEM
+//                      allocation (BN columns) and frees it at the end.
+//   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns at a time, then one of
+//                      0 store (bfloat16 or float32), 1 residual add into float32 C,
+//                      2 silu(gate) * up on interleaved gate/up columns (bfloat16 out, N/2 wide).
+// Edges: TMA zero-fills rows and K beyond the tensors, stores are bounds-checked, so any M, N and
+// any K that keeps rows 16-byte aligned (K % 8 == 0) are accepted.
+// Every mbarrier wait is bounded: when a wait gives up, the kernel records a code in a status
+// word, all roles fall through to the common exit, TMEM is freed and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128, BK = 64;
+constexpr int kGemmTcThreads = 192;
+constexpr unsigned long long kWaitLimit = 200000ull;  // polls (each suspends up to ~10 us) before a wait gives up
+
+__device__ int g_gemm_status = 0;  // 0 ok; else (role << 8 | stage) of the wait that gave up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity.  Returns false when it gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned long long i = 0; i < kWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done) : "r"(addr), "r"(parity), "r"(10000u) : "memory");
+        if (done) return true;
+        if ((i & 15) == 15 && *abort_flag) return false;  // another role already gave up
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+    const uint32_t addr = smem_u32(tile);
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);        // start address
+    d |= (uint64_t)1 << 16;                        // leading-dimension offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride between 8-row groups
+    d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    alignas(1024) __nv_bfloat16 a[STAGES][BM * BK];
+    alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(kGemmTcThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    TC* __restrict__ C, int ldc, int M, int N, int K) {
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int k_iters = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_full, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) {  // tensor memory for the accumulator: BN columns of 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % STAGES;
+            if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (1 << 8) | s); break;
+            }
+            mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+            tma_load_2d(sm.a[s], &map_a, it * BK, m0, &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_w, it * BK, n0, &sm.full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer.  Instruction descriptor: D f32, A and B bf16, both K-major, N x 128.
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        bool ok = true;
+        for (int it = 0; it < k_iters && ok; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (2 << 8) | s); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)  // 16 elements = 32 bytes further along K: +2 in the address field
+                umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (it | k) != 0);
+            umma_commit(&sm.empty[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&sm.acc_full);
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+        if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (3 << 8) | quarter); }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;  // uniform: whole chunk beyond the matrix
+                float v[32];
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                if (row >= M) continue;
+                const int col = n0 + c0;
+                if (EPI == 2) {
+                    TC* dst = C + (size_t)row * ldc + (col >> 1);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>((v[2 * j] / (1.0f + expf(-v[2 * j]))) * v[2 * j + 1]);
+                } else {
+                    TC* dst = C + (size_t)row * ldc + col;
+                    const bool whole = col + 32 <= N && ((uintptr_t)dst & 15) == 0;
+                    if (EPI == 1) {  // C is the float32 residual stream
+                        float* d = reinterpret_cast<float*>(dst);
+                        if (whole) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 r = *reinterpret_cast<float4*>(d + j);
+                                r.x += v[j]; r.y += v[j + 1]; r.z += v[j + 2]; r.w += v[j + 3];
+                                *reinterpret_cast<float4*>(d + j) = r;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) if (col + j < N) d[j] += v[j];
+                        }
+                    } else if (sizeof(TC) == 2 && whole) {
+                        uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                            d[j] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                              *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (col + j < N) dst[j] = from_f32<TC>(v[j]);
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    }
+}
+
+// ---- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D bfloat16 tensor [rows, K] with row stride ld (elements); boxes of box_rows x 64 elements, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, int EPI, typename TC>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    static bool configured = false;
+    auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    kernel<<<grid, kGemmTcThreads, smem, stream>>>(ma, mw, (TC*)C, ldc, M, N, K);
+    return launch_status();
+}
+
+}  // namespace b200
+
+// Reads and clears the status word of the tensor-core GEMM (0 = every wait completed).  Synchronises.
+extern "C" int b200_gemm_tcgen05_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, b200::g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(b200::g_gemm_status, &zero, sizeof(int));
+    return v;
+}
+
+// A, W bfloat16; C bfloat16 or float32; epilogue 0 store, 1 residual add (C float32), 2 gated SiLU (C bfloat16).
+extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
+                                 int N, int K, int epilogue, cudaStream_t stream) {
+    using namespace b200;
+    if (M <= 0 || N <= 0) return 0;
+    if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
+    if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
+        return kErrBadArgument;
+    if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
+    if ((M + BM - 1) / BM > 65535) return kErrUnsupportedSize;
+    constexpr int BN = 256, STAGES = 4;
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;
+    if (epilogue == 2) return launch_tc<BN, STAGES, 2, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, stream);
+    if (epilogue == 1) return launch_tc<BN, STAGES, 1, float>(ma, mw, C, ldc, M, N, K, stream);
+    if (c_dtype == kF32) return launch_tc<BN, STAGES, 0, float>(ma, mw, C, ldc, M, N, K, stream);
+    return launch_tc<BN, STAGES, 0, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, stream);
+}

@@ -40,6 +40,8 @@ _SIGNATURES = {
                                            c_int, c_int, c_int, c_int]),
     "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_int]),
+    "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                    c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
                                                    c_int, c_int]),
@@ -193,6 +195,31 @@ def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     _check(_fn("b200_gemm_decode")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_decode")
     return True
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
+    """The prefill matrix product on tcgen05 tensor cores (bfloat16 operands, rows 16-byte aligned).
+    Returns False, having done nothing, for operands it does not take."""
+    M, K = a.shape
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or K < 8 or a.stride(1) != 1
+            or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
+        return False
+    if epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16:
+        return False
+    _dev(a, w, c)
+    N = w.shape[0]
+    assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
+    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    _check(_fn("b200_gemm_tcgen05")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
+                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_tcgen05")
+    return True
+
+
+def gemm_tcgen05_status() -> int:
+    """0 when every wait inside the tensor-core GEMM completed since the last call; synchronises."""
+    lib = library("gemm_tcgen05")
+    lib.b200_gemm_tcgen05_status.restype = c_int
+    return int(lib.b200_gemm_tcgen05_status())
 
 
 def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
