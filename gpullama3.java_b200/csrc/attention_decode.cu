@@ -70,6 +70,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int group = n_heads / n_kv_heads;
+    pdl_launch_dependents();
+    pdl_wait();  // queries, the new keys and values, lengths and page tables come from earlier kernels
     const int kv_len = kv_lens[seq];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
     const int first_block = lo / 32, last_block = (kv_len - 1) / 32;
@@ -220,6 +222,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_heads + head
     const float* ml = part_ml + row * n_splits * 2;
     float m = -INFINITY;
@@ -263,9 +267,10 @@ extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out,
     auto kk = (const __nv_bfloat16*)k_pool;
     auto vv = (const __nv_bfloat16*)v_pool;
     auto oo = (__nv_bfloat16*)out;
+    int st = 0;
 #define B200_LAUNCH(KB)                                                                                          \
-    attention_decode_kernel<KB><<<grid, kAttnDecodeThreads, smem, stream>>>(qq, q_row_stride, oo, kv_lens, page_table, \
-        table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits)
+    st = launch_pdl(attention_decode_kernel<KB>, grid, dim3(kAttnDecodeThreads), smem, stream, qq, q_row_stride, oo, \
+                    kv_lens, page_table, table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits)
     switch (head_dim / 32) {
         case 1: B200_LAUNCH(1); break;
         case 2: B200_LAUNCH(2); break;
@@ -273,8 +278,7 @@ extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out,
         default: B200_LAUNCH(4); break;
     }
 #undef B200_LAUNCH
-    int st = launch_status();
     if (st != 0 || n_splits == 1) return st;
-    attention_decode_merge_kernel<<<n_seqs * n_heads, head_dim <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, oo, n_splits, head_dim);
-    return launch_status();
+    return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
+                      (const float*)part_o, (const float*)part_ml, oo, n_splits, head_dim);
 }

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace b200 {
 
@@ -70,6 +71,40 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 inline int launch_status() { return (int)cudaPeekAtLastError(); }
+
+// Programmatic dependent launch.  A kernel launched with launch_pdl may start while its
+// predecessor on the stream is still running; it must call pdl_wait() before it touches anything a
+// predecessor wrote (or writes anything a predecessor reads).  What it does before that call
+// (index arithmetic, loading weights, which no kernel writes) overlaps the predecessor's tail and
+// the launch latency.  pdl_launch_dependents() lets the successor be scheduled as soon as every
+// CTA of this kernel has started.  Every thread of such a kernel calls pdl_wait(), so that the
+// completion of a kernel implies the completion of everything before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("GPULLAMA3_B200_NO_PDL");
+        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace b200
 

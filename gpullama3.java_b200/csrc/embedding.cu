@@ -8,6 +8,8 @@ namespace b200 {
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                     float* __restrict__ out, int dim, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * dim;
@@ -25,6 +27,7 @@ extern "C" int b200_embed_gather(const void* table, int table_dtype, const int* 
                                  int n_tokens, int dim, int vocab, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     B200_DISPATCH_DTYPE(table_dtype, TW,
-        b200::embed_gather_kernel<TW><<<n_tokens, 256, 0, stream>>>((const TW*)table, tokens, out, dim, vocab));
+        return b200::launch_pdl(b200::embed_gather_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, (const TW*)table,
+                                tokens, out, dim, vocab));
     return b200::launch_status();
 }

@@ -69,28 +69,36 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
     const int n_blocks = K / 32;
-    for (int kb0 = warp * kUnroll; kb0 < n_blocks; kb0 += kDecodeWarps * kUnroll) {
-        uint4 wl[kUnroll], wh[kUnroll], av[kUnroll][NT];
+    uint4 wl[kUnroll], wh[kUnroll];
+    auto load_weights = [&](int kb0) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const int kb = kb0 + u;
-            if (kb < n_blocks) {
-                wl[u] = load_stream(w_lo + kb * 32);
-                wh[u] = ROWS == 16 ? load_stream(w_hi + kb * 32) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int n = 0; n < NT; ++n) av[u][n] = a_ok[n] ? load_cached(a_row[n] + kb * 32) : make_uint4(0, 0, 0, 0);
-            } else {
-                wl[u] = wh[u] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int n = 0; n < NT; ++n) av[u][n] = make_uint4(0, 0, 0, 0);
-            }
+            wl[u] = kb < n_blocks ? load_stream(w_lo + kb * 32) : make_uint4(0, 0, 0, 0);
+            wh[u] = (ROWS == 16 && kb < n_blocks) ? load_stream(w_hi + kb * 32) : make_uint4(0, 0, 0, 0);
         }
+    };
+    // the first weights are on their way before the kernel that produces the activations has finished
+    load_weights(warp * kUnroll);
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int kb0 = warp * kUnroll; kb0 < n_blocks; kb0 += kDecodeWarps * kUnroll) {
+        uint4 av[kUnroll][NT];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                av[u][n] = (a_ok[n] && kb0 + u < n_blocks) ? load_cached(a_row[n] + (kb0 + u) * 32) : make_uint4(0, 0, 0, 0);
+        uint4 cl[kUnroll], ch[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) { cl[u] = wl[u]; ch[u] = wh[u]; }
+        load_weights(kb0 + kDecodeWarps * kUnroll);  // next round's weights, in flight during this round's MMAs
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                mma_bf16(acc[n], wl[u].x, wh[u].x, wl[u].y, wh[u].y, av[u][n].x, av[u][n].y);
-                mma_bf16(acc[n], wl[u].z, wh[u].z, wl[u].w, wh[u].w, av[u][n].z, av[u][n].w);
+                mma_bf16(acc[n], cl[u].x, ch[u].x, cl[u].y, ch[u].y, av[u][n].x, av[u][n].y);
+                mma_bf16(acc[n], cl[u].z, ch[u].z, cl[u].w, ch[u].w, av[u][n].z, av[u][n].w);
             }
     }
 
@@ -136,10 +144,10 @@ static int launch_epi(const void* A, int lda, const void* W, int ldw, void* C, i
     const int grid = (N + ROWS - 1) / ROWS;
     auto a = (const __nv_bfloat16*)A;
     auto w = (const __nv_bfloat16*)W;
-    if (epi == 0) gemm_decode_kernel<ROWS, NT, 0, TC><<<grid, kDecodeThreads, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K);
-    else if (epi == 1) gemm_decode_kernel<ROWS, NT, 1, TC><<<grid, kDecodeThreads, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K);
-    else gemm_decode_kernel<ROWS, NT, 2, TC><<<grid, kDecodeThreads, 0, stream>>>(a, lda, w, ldw, (TC*)C, ldc, M, N, K);
-    return launch_status();
+    const dim3 g(grid), b(kDecodeThreads);
+    if (epi == 0) return launch_pdl(gemm_decode_kernel<ROWS, NT, 0, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
+    if (epi == 1) return launch_pdl(gemm_decode_kernel<ROWS, NT, 1, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
+    return launch_pdl(gemm_decode_kernel<ROWS, NT, 2, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
 }
 
 }  // namespace b200

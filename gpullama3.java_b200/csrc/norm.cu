@@ -12,6 +12,8 @@ template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ rows, int dim, float eps) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
     float ss = 0.f;
@@ -29,6 +31,7 @@ extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* ou
     if (n_rows <= 0) return 0;
     const int threads = dim >= 1024 ? 256 : 128;
     B200_DISPATCH_DTYPE(w_dtype, TW, B200_DISPATCH_DTYPE2(out_dtype, TO,
-        b200::rmsnorm_kernel<TW, TO><<<n_rows, threads, 0, stream>>>(x, (const TW*)w, (TO*)out, rows, dim, eps)));
+        return b200::launch_pdl(b200::rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, (const TW*)w,
+                                (TO*)out, rows, dim, eps)));
     return b200::launch_status();
 }

@@ -24,6 +24,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         int table_stride, const float* __restrict__ inv_freq, T* __restrict__ k_pool,
                                         T* __restrict__ v_pool, int n_heads, int n_kv_heads, int head_dim,
                                         int rotary_dim, int pairing, int write_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int q_dim = n_heads * head_dim, kv_dim = n_kv_heads * head_dim;
@@ -83,8 +85,8 @@ extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions,
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || (pairing != 0 && pairing != 1))
         return b200::kErrBadArgument;
     B200_DISPATCH_DTYPE(dtype, T,
-        b200::rope_cache_write_kernel<T><<<n_tokens, 256, 0, stream>>>(
-            (T*)qkv, positions, seq_ids, page_table, table_stride, inv_freq, (T*)k_pool, (T*)v_pool, n_heads,
-            n_kv_heads, head_dim, rotary_dim, pairing, write_cache));
+        return b200::launch_pdl(b200::rope_cache_write_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)qkv,
+                                positions, seq_ids, page_table, table_stride, inv_freq, (T*)k_pool, (T*)v_pool, n_heads,
+                                n_kv_heads, head_dim, rotary_dim, pairing, write_cache));
     return b200::launch_status();
 }

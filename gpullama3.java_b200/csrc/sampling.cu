@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(kSampleThreads)
 argmax_rows_kernel(const float* __restrict__ logits, int ld, int* __restrict__ out, int V) {
     __shared__ float best_s[kSampleWarps];
     __shared__ int idx_s[kSampleWarps];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int idx = INT_MAX;
@@ -276,8 +278,8 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
 extern "C" int b200_argmax_rows(const float* logits, int ld, int* out, int n_rows, int vocab, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0) return b200::kErrBadArgument;
-    b200::argmax_rows_kernel<<<n_rows, b200::kSampleThreads, 0, stream>>>(logits, ld, out, vocab);
-    return b200::launch_status();
+    return b200::launch_pdl(b200::argmax_rows_kernel, dim3(n_rows), dim3(b200::kSampleThreads), 0, stream, logits, ld, out,
+                            vocab);
 }
 
 extern "C" int b200_sample_rows(const float* logits, int ld, const float* uniforms, int* out, int n_rows, int vocab,

@@ -226,11 +226,17 @@ def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int
     return dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) and n_heads // n_kv_heads <= 16
 
 
-def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, target_ctas: int = 592) -> int:
-    """How many spans each sequence's keys are cut into so that the grid fills the GPU."""
+def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resident_ctas: int = 592) -> int:
+    """How many spans each sequence's keys are cut into.  The grid (spans x kv heads x sequences)
+    should fill the GPU in one wave (148 SMs x 4 resident CTAs) without spilling into a second one,
+    and a span should keep at least 8 blocks of 32 keys so that its start-up and the merge pay."""
     blocks = max(1, (max_kv_len + 31) // 32)
-    want = -(-target_ctas // max(1, n_seqs * n_kv_heads))
-    return max(1, min(want, blocks // 2 if blocks >= 2 else 1, 64))
+    cap = max(1, resident_ctas // max(1, n_seqs * n_kv_heads))
+    want = max(1, min(cap, blocks // 8, 64))
+    p = 1
+    while p * 2 <= want:
+        p *= 2
+    return p
 
 
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,
