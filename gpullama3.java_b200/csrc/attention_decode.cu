@@ -19,6 +19,7 @@
 //   O[heads x d] += P V : ... which is exactly one 16-byte load of a V^T row (dim, keys 8t..8t+7).
 //
 // Sizes: head_dim 32, 64, 96 or 128; group size (heads per kv head) <= 16.  Others are refused.
+#include "attention_decode_static.h"
 #include "common.cuh"
 
 namespace b200 {
@@ -281,4 +282,44 @@ extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out,
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
                       (const float*)part_o, (const float*)part_ml, oo, n_splits, head_dim);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The variant with built-in scratch (see attention_decode_static.h for who needs it and why).
+namespace b200 {
+
+constexpr long long kStaticScratchFloats = 2ll << 20;  // 2 Mi floats = 8 MiB per GPU that loads this library
+constexpr int kErrStaticScratchExceeded = 10004;
+constexpr int kMaxDevices = 64;
+
+// In host code this name is only a handle of the symbol, not a device address: the address each
+// device gave the array is looked up below and it is that pointer the kernels receive.
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static float* g_static_scratch_address[kMaxDevices];  // per device; filled by the first call on it
+
+}  // namespace b200
+
+extern "C" long long b200_attention_decode_static_capacity(void) { return b200::kStaticScratchFloats; }
+
+extern "C" int b200_attention_decode_static(const void* q, int q_row_stride, void* out, const int* kv_lens,
+                                            const int* page_table, int table_stride, const void* k_pool,
+                                            const void* v_pool, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
+                                            int window, int n_splits, cudaStream_t stream) {
+    using namespace b200;
+    if (n_seqs <= 0) return 0;
+    if (n_splits < 1) return kErrBadArgument;
+    const long long need = b200_attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits);
+    if (need > kStaticScratchFloats) return kErrStaticScratchExceeded;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= kMaxDevices) return kErrBadArgument;
+    float* scratch = g_static_scratch_address[device];
+    if (scratch == nullptr) {  // set-up, once per device, with that device current
+        e = cudaGetSymbolAddress((void**)&scratch, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_address[device] = scratch;
+    }
+    return b200_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, k_pool, v_pool, scratch,
+                                 kStaticScratchFloats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, stream);
 }

@@ -67,7 +67,7 @@ def available_libraries() -> list[str]:
 def _source_hash(name: str, nvcc: str) -> str:
     h = hashlib.sha256()
     h.update((CSRC_DIR / f"{name}.cu").read_bytes())
-    for header in sorted(CSRC_DIR.glob("*.cuh")):
+    for header in sorted(list(CSRC_DIR.glob("*.cuh")) + list(CSRC_DIR.glob("*.h"))):
         h.update(header.name.encode())
         h.update(header.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())

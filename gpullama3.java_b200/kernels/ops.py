@@ -24,6 +24,7 @@ _ERRORS = {
     10001: "bad argument",
     10002: "unsupported size",
     10003: "scratch too small",
+    10004: "the call needs more scratch than the built-in array of the no-allocation entry point holds",
 }
 
 _functions: dict[str, ctypes._CFuncPtr] = {}
