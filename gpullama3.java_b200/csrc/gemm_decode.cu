@@ -1,4 +1,4 @@
-// Matrix product for decode steps in bfloat16: C[M, N] = A[M, K] W[N, K]^T for M <= 16 tokens.
+// Matrix product for decode steps in bfloat16: C[M, N] = A[M, K] W[N, K]^T for M <= 64 tokens.
 //
 // A decode step reads every weight once and does little arithmetic with it, so this kernel is
 // built around the stream of W from HBM: each lane loads 16 contiguous bytes of a weight row
@@ -14,7 +14,7 @@
 // lane (g, t) takes the 8 consecutive elements k0 + 8t .. 8t+7 of row g (one 16-byte load) and
 // feeds them to two MMAs; the activation fragment is the same 16-byte slice of the token's row.
 //
-// Sizes: K a multiple of 32, rows 16-byte aligned; any N; M <= 16.  Other shapes are refused
+// Sizes: K a multiple of 32, rows 16-byte aligned; any N; M <= 64.  Other shapes are refused
 // (kErrUnsupportedSize) and the caller takes the plain kernel.
 #include "common.cuh"
 
@@ -40,21 +40,29 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// ROWS: weight rows per CTA (16, or 8 for narrow outputs so that more CTAs pull on HBM).
-// NT: token tiles of 8.  EPI: 0 store, 1 residual add (C float), 2 gated SiLU.
-template <int ROWS, int NT, int EPI, typename TC>
+// MT: 16-row tiles of weight rows per CTA (ROWS = 16 * MT), or MT = 0 for 8 rows (narrow outputs, so that
+// more CTAs pull on HBM).  NT: token tiles of 8.  EPI: 0 store, 1 residual add (C float), 2 gated SiLU.
+template <int MT, int NT, int EPI, typename TC>
 __global__ void __launch_bounds__(kDecodeThreads)
 gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
                    TC* __restrict__ C, int ldc, int M, int N, int K) {
-    __shared__ float red[kDecodeWarps][NT * 8][ROWS];
-    __shared__ float fin[NT * 8][ROWS];
+    constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
+    constexpr int MTT = MT == 0 ? 1 : MT;            // tiles actually multiplied
+    constexpr bool HI = MT != 0;                     // rows g + 8 of a tile exist
+    constexpr int U = (MTT * NT >= 8) ? 2 : kUnroll;  // k-blocks in flight per warp
+    extern __shared__ float red_raw[];               // [warps][NT * 8][ROWS] partial sums, then [NT * 8][ROWS]
+    float (*red)[NT * 8][ROWS] = reinterpret_cast<float (*)[NT * 8][ROWS]>(red_raw);
+    float (*fin)[ROWS] = reinterpret_cast<float (*)[ROWS]>(red_raw + kDecodeWarps * NT * 8 * ROWS);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = blockIdx.x * ROWS;
-    const int r_lo = min(row0 + g, N - 1);            // clamped: rows past N are read but never stored
-    const int r_hi = min(row0 + g + 8, N - 1);
-    const __nv_bfloat16* w_lo = W + (size_t)r_lo * ldw + t * 8;
-    const __nv_bfloat16* w_hi = W + (size_t)r_hi * ldw + t * 8;
+    const __nv_bfloat16* w_lo[MTT];
+    const __nv_bfloat16* w_hi[MTT];
+#pragma unroll
+    for (int m = 0; m < MTT; ++m) {  // clamped: rows past N are read but never stored
+        w_lo[m] = W + (size_t)min(row0 + 16 * m + g, N - 1) * ldw + t * 8;
+        w_hi[m] = W + (size_t)min(row0 + 16 * m + g + 8, N - 1) * ldw + t * 8;
+    }
     const __nv_bfloat16* a_row[NT];
     bool a_ok[NT];
 #pragma unroll
@@ -62,56 +70,65 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         a_ok[n] = n * 8 + g < M;
         a_row[n] = A + (size_t)min(n * 8 + g, M - 1) * lda + t * 8;
     }
-    float acc[NT][4];
+    float acc[MTT][NT][4];
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
+    for (int m = 0; m < MTT; ++m)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
     const int n_blocks = K / 32;
-    uint4 wl[kUnroll], wh[kUnroll];
+    uint4 wl[U][MTT], wh[U][MTT];
     auto load_weights = [&](int kb0) {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int kb = kb0 + u;
-            wl[u] = kb < n_blocks ? load_stream(w_lo + kb * 32) : make_uint4(0, 0, 0, 0);
-            wh[u] = (ROWS == 16 && kb < n_blocks) ? load_stream(w_hi + kb * 32) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int m = 0; m < MTT; ++m) {
+                wl[u][m] = kb < n_blocks ? load_stream(w_lo[m] + kb * 32) : make_uint4(0, 0, 0, 0);
+                wh[u][m] = (HI && kb < n_blocks) ? load_stream(w_hi[m] + kb * 32) : make_uint4(0, 0, 0, 0);
+            }
         }
     };
     // the first weights are on their way before the kernel that produces the activations has finished
-    load_weights(warp * kUnroll);
+    load_weights(warp * U);
     pdl_launch_dependents();
     pdl_wait();
-    for (int kb0 = warp * kUnroll; kb0 < n_blocks; kb0 += kDecodeWarps * kUnroll) {
-        uint4 av[kUnroll][NT];
+    for (int kb0 = warp * U; kb0 < n_blocks; kb0 += kDecodeWarps * U) {
+        uint4 cl[U][MTT], ch[U][MTT];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u)
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
-                av[u][n] = (a_ok[n] && kb0 + u < n_blocks) ? load_cached(a_row[n] + (kb0 + u) * 32) : make_uint4(0, 0, 0, 0);
-        uint4 cl[kUnroll], ch[kUnroll];
+            for (int m = 0; m < MTT; ++m) { cl[u][m] = wl[u][m]; ch[u][m] = wh[u][m]; }
+        load_weights(kb0 + kDecodeWarps * U);  // next round's weights, in flight during this round's MMAs
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) { cl[u] = wl[u]; ch[u] = wh[u]; }
-        load_weights(kb0 + kDecodeWarps * kUnroll);  // next round's weights, in flight during this round's MMAs
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u)
+        for (int u = 0; u < U; ++u) {
+            const bool k_ok = kb0 + u < n_blocks;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                mma_bf16(acc[n], cl[u].x, ch[u].x, cl[u].y, ch[u].y, av[u][n].x, av[u][n].y);
-                mma_bf16(acc[n], cl[u].z, ch[u].z, cl[u].w, ch[u].w, av[u][n].z, av[u][n].w);
+                const uint4 av = (a_ok[n] && k_ok) ? load_cached(a_row[n] + (kb0 + u) * 32) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int m = 0; m < MTT; ++m) {
+                    mma_bf16(acc[m][n], cl[u][m].x, ch[u][m].x, cl[u][m].y, ch[u][m].y, av.x, av.y);
+                    mma_bf16(acc[m][n], cl[u][m].z, ch[u][m].z, cl[u][m].w, ch[u][m].w, av.z, av.w);
+                }
             }
+        }
     }
 
     // partial sums of the warps meet in shared memory; thread (row, token) adds them in warp order
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-        red[warp][n * 8 + 2 * t][g] = acc[n][0];
-        red[warp][n * 8 + 2 * t + 1][g] = acc[n][1];
-        if (ROWS == 16) {
-            red[warp][n * 8 + 2 * t][g + 8] = acc[n][2];
-            red[warp][n * 8 + 2 * t + 1][g + 8] = acc[n][3];
+    for (int m = 0; m < MTT; ++m)
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            red[warp][n * 8 + 2 * t][16 * m + g] = acc[m][n][0];
+            red[warp][n * 8 + 2 * t + 1][16 * m + g] = acc[m][n][1];
+            if (HI) {
+                red[warp][n * 8 + 2 * t][16 * m + g + 8] = acc[m][n][2];
+                red[warp][n * 8 + 2 * t + 1][16 * m + g + 8] = acc[m][n][3];
+            }
         }
-    }
     __syncthreads();
     for (int idx = threadIdx.x; idx < NT * 8 * ROWS; idx += kDecodeThreads) {
         const int token = idx / ROWS, row = idx % ROWS;
@@ -138,16 +155,32 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     }
 }
 
-template <int ROWS, int NT, typename TC>
+template <int MT, int NT, int EPI, typename TC>
+static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
+                      int K, cudaStream_t stream) {
+    constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
+    const size_t smem = sizeof(float) * (kDecodeWarps + 1) * NT * 8 * ROWS;
+    auto kernel = gemm_decode_kernel<MT, NT, EPI, TC>;
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+                return (int)cudaGetLastError();
+            configured = true;
+        }
+    }
+    return launch_pdl(kernel, dim3((N + ROWS - 1) / ROWS), dim3(kDecodeThreads), smem, stream, a, lda, w, ldw, (TC*)C, ldc,
+                      M, N, K);
+}
+
+template <int MT, int NT, typename TC>
 static int launch_epi(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi,
                       cudaStream_t stream) {
-    const int grid = (N + ROWS - 1) / ROWS;
     auto a = (const __nv_bfloat16*)A;
     auto w = (const __nv_bfloat16*)W;
-    const dim3 g(grid), b(kDecodeThreads);
-    if (epi == 0) return launch_pdl(gemm_decode_kernel<ROWS, NT, 0, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
-    if (epi == 1) return launch_pdl(gemm_decode_kernel<ROWS, NT, 1, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
-    return launch_pdl(gemm_decode_kernel<ROWS, NT, 2, TC>, g, b, 0, stream, a, lda, w, ldw, (TC*)C, ldc, M, N, K);
+    if (epi == 0) return launch_one<MT, NT, 0, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    if (epi == 1) return launch_one<MT, NT, 1, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    return launch_one<MT, NT, 2, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
 }
 
 }  // namespace b200
@@ -157,17 +190,20 @@ extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, 
                                 int N, int K, int epilogue, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16 || K < 32 || K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0) return kErrUnsupportedSize;
+    if (M > 64 || K < 32 || K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0) return kErrUnsupportedSize;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && (N & 1)))
         return kErrBadArgument;
-    const bool narrow = N <= 4096;  // few rows: 8 per CTA so that at least ~2 CTAs per SM stream weights
-    const bool two = M > 8;
-#define B200_GO(ROWS, NT)                                                                                     \
-    return c_dtype == kF32 ? launch_epi<ROWS, NT, float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)   \
-                           : launch_epi<ROWS, NT, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
-    if (narrow) { if (two) { B200_GO(8, 2); } else { B200_GO(8, 1); } }
-    if (two) { B200_GO(16, 2); } else { B200_GO(16, 1); }
+    const bool narrow = N <= 4096;  // few rows: fewer per CTA so that enough CTAs stream weights
+#define B200_GO(MT, NT)                                                                                       \
+    return c_dtype == kF32 ? launch_epi<MT, NT, float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)     \
+                           : launch_epi<MT, NT, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)
+    if (M <= 8) { if (narrow) { B200_GO(0, 1); } else { B200_GO(1, 1); } }
+    if (M <= 16) { if (narrow) { B200_GO(0, 2); } else { B200_GO(1, 2); } }
+    // more tokens: every weight fragment meets 4 or 8 token tiles; wide outputs take 32 rows per CTA so
+    // that the activations, which each CTA reads in full, are re-read half as often
+    if (M <= 32) { if (narrow) { B200_GO(1, 4); } else { B200_GO(2, 4); } }
+    if (narrow) { B200_GO(1, 8); } else { B200_GO(2, 8); }
 #undef B200_GO
 }

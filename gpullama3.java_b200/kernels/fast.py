@@ -14,17 +14,7 @@ from . import ops
 def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -> bool:
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         return False
-    M = a.shape[0]
-    if M <= 16:
-        return ops.gemm_decode(a, w, c, epilogue)
-    if M <= 64 and a.shape[1] % 32 == 0:
-        # between the decode kernel's 16 tokens and a full tensor-core tile: the weight-streaming kernel
-        # over slices of 16 tokens
-        for m0 in range(0, M, 16):
-            if not ops.gemm_decode(a[m0:m0 + 16], w, c[m0:m0 + 16], epilogue):
-                if m0:
-                    raise ops.KernelError("gemm_decode refused a later slice of a batch it had started")
-                return False
+    if a.shape[0] <= 64 and ops.gemm_decode(a, w, c, epilogue):
         return True
     return ops.gemm_tcgen05(a, w, c, epilogue)
 

@@ -183,10 +183,10 @@ def gemm_generic(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
 
 
 def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
-    """The decode-step matrix product (bfloat16 operands, at most 16 tokens, K a multiple of 32).
+    """The decode-step matrix product (bfloat16 operands, at most 64 tokens, K a multiple of 32).
     Returns False, having done nothing, for operands it does not take."""
     M, K = a.shape
-    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M > 16 or K % 32 or a.stride(1) != 1
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or M > 64 or K % 32 or a.stride(1) != 1
             or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
         return False
     _dev(a, w, c)

@@ -185,7 +185,7 @@ def test_gemm_generic_and_its_epilogues(a_dtype, w_dtype, M, N, K):
     torch.testing.assert_close(h.float().cpu(), gated.float().to(a_dtype).float(), **tol(a_dtype, gated))
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 50, 64])
 @pytest.mark.parametrize("N, K", [(16, 32), (50, 96), (200, 2048), (4098, 64), (5000, 1056)])
 def test_gemm_decode_and_its_epilogues(M, N, K):
     o = ops()
@@ -211,7 +211,7 @@ def test_gemm_decode_and_its_epilogues(M, N, K):
     assert o.gemm_decode(wide[:, :K], w, c)
     torch.testing.assert_close(c.cpu(), (wide[:, :K].float().cpu().double() @ w.float().cpu().double().t()).float(),
                                **tol(torch.float32, ref))
-    assert not o.gemm_decode(torch.zeros(17, K, dtype=torch.bfloat16, device="cuda"), w, c)
+    assert not o.gemm_decode(torch.zeros(65, K, dtype=torch.bfloat16, device="cuda"), w, c)
     assert not o.gemm_decode(a.float(), w, c)
 
 
