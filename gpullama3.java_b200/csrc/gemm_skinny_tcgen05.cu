@@ -1,0 +1,271 @@
+// Matrix product for steps with few tokens (17 .. 128) in bfloat16 on tcgen05 tensor cores:
+//     C[M, N] = A[M, K] W[N, K]^T,  M small, N and K large.
+// With so few tokens the product is a stream of W from HBM, so the roles of the operands are
+// swapped against the prefill kernel: 128 weight rows are the M side of the tensor-core tile and
+// the tokens are its N side (BT = 32, 64 or 128 columns of tensor memory).  TMA brings a
+// 128 x 64 slice of W and a BT x 64 slice of A per stage through a deep ring (24 KB per stage,
+// 8 stages in flight), one thread issues tcgen05.mma, four warps read the accumulator back.
+// (The reference does these products one output row per work-group,
+// tornadovm/TransformerComputeKernelsLayered.java:901-930 of the reference project.)
+//
+// Narrow outputs (few tiles of 128 rows) would leave most SMs idle, so K is also cut into
+// `k_splits` spans, one CTA each.  A span's CTA leaves its partial tile in scratch memory and
+// bumps the tile's counter; the CTA that arrives last adds the partials of all spans in span
+// order (so the sum does not depend on which CTA came last), applies the epilogue and resets
+// the counter.  Counters must be zero before the first call; every call leaves them zero.
+//
+// Epilogues: 0 store, 1 residual add into float32 C, 2 silu(gate) * up on interleaved rows.
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+constexpr int kSkinnyThreads = 192;
+constexpr int kRowsPerTile = 128;
+
+__device__ int g_skinny_status = 0;
+
+template <int BT, int STAGES>
+struct SkinnySmem {
+    alignas(1024) __nv_bfloat16 w[STAGES][kRowsPerTile * BK];
+    alignas(1024) __nv_bfloat16 a[STAGES][BT * BK];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    int is_last;
+};
+
+template <int EPI, typename TC>
+__device__ __forceinline__ void skinny_emit(TC* __restrict__ C, int ldc, int token, int n, int N, float v, int lane) {
+    if (EPI == 2) {
+        const float other = __shfl_xor_sync(0xffffffffu, v, 1);  // lanes 2i, 2i+1 hold a gate row and its up row
+        if ((lane & 1) == 0 && n + 1 < N) C[(size_t)token * ldc + (n >> 1)] = from_f32<TC>((v / (1.0f + expf(-v))) * other);
+    } else if (n < N) {
+        TC* c = C + (size_t)token * ldc + n;
+        if (EPI == 1) *c = from_f32<TC>(to_f32<TC>(*c) + v);
+        else *c = from_f32<TC>(v);
+    }
+}
+
+template <int BT, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                   TC* __restrict__ C, int ldc, int M, int N, int K, int blocks_per_split,
+                   float* __restrict__ partial, int* __restrict__ counters) {
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<SkinnySmem<BT, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, k_splits = gridDim.y, n_tiles = gridDim.x;
+    const int n0 = tile * kRowsPerTile;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = split * blocks_per_split;
+    const int k_iters = max(0, min(kb_total, kb_begin + blocks_per_split) - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_full, 1);
+        sm.abort_flag = 0;
+        sm.is_last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(BT) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer.  Weights do not depend on earlier kernels: the first stages of W are on their way
+        // before the wait for the kernel that produces the activations.
+        const int early = min(k_iters, STAGES);
+        for (int it = 0; it < early; ++it) {
+            mbar_expect_tx(&sm.full[it], (kRowsPerTile + BT) * BK * 2);
+            tma_load_2d(sm.w[it], &map_w, (kb_begin + it) * BK, n0, &sm.full[it]);
+        }
+        pdl_wait();
+        for (int it = 0; it < early; ++it) tma_load_2d(sm.a[it], &map_a, (kb_begin + it) * BK, 0, &sm.full[it]);
+        for (int it = STAGES; it < k_iters; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_skinny_status, 0, (1 << 8) | s); break;
+            }
+            mbar_expect_tx(&sm.full[s], (kRowsPerTile + BT) * BK * 2);
+            tma_load_2d(sm.w[s], &map_w, (kb_begin + it) * BK, n0, &sm.full[s]);
+            tma_load_2d(sm.a[s], &map_a, (kb_begin + it) * BK, 0, &sm.full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer: 128 weight rows x BT tokens
+        constexpr uint32_t idesc = umma_idesc_bf16(kRowsPerTile, BT);
+        bool ok = true;
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % STAGES;
+            if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_skinny_status, 0, (2 << 8) | s); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t wd = umma_desc(sm.w[s]), ad = umma_desc(sm.a[s]);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) umma_bf16(tmem, wd + 2 * k, ad + 2 * k, idesc, (it | k) != 0);
+            umma_commit(&sm.empty[s]);
+        }
+        if (ok && k_iters > 0) umma_commit(&sm.acc_full);
+    }
+    // every thread waits for the predecessor before global memory written by earlier kernels is touched below
+    pdl_wait();
+
+    if (warp >= 2) {
+        // ---- epilogue.  Thread (quarter, lane) owns weight row n0 + 32 * quarter + lane; a TMEM load gives it
+        // 32 tokens of that row; for one token the lanes of a warp are 32 consecutive outputs.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane, n = n0 + r;
+        bool ok = true;
+        if (k_iters > 0) {
+            ok = mbar_wait(&sm.acc_full, 0, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_skinny_status, 0, (3 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BT; c0 += 32) {
+                if (c0 >= M) break;
+                float v[32];
+                if (k_iters > 0) {
+                    tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                }
+                if (k_splits == 1) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < M) skinny_emit<EPI, TC>(C, ldc, c0 + j, n, N, v[j], lane);
+                } else {
+                    float* p = partial + (((size_t)split * n_tiles + tile) * BT + c0) * kRowsPerTile + r;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < M) p[(size_t)j * kRowsPerTile] = v[j];
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    if (k_splits > 1) {
+        __threadfence();  // this CTA's partial tile is visible before its arrival is counted
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int arrived = atomicAdd(&counters[tile], 1);
+            sm.is_last = arrived == k_splits - 1;
+        }
+        __syncthreads();
+        if (sm.is_last && warp >= 2 && !sm.abort_flag) {
+            __threadfence();
+            const int quarter = warp & 3;
+            const int r = quarter * 32 + lane, n = n0 + r;
+            for (int token = 0; token < M; ++token) {
+                float s = 0.f;
+                for (int sp = 0; sp < k_splits; ++sp)
+                    s += __ldcg(partial + (((size_t)sp * n_tiles + tile) * BT + token) * kRowsPerTile + r);
+                skinny_emit<EPI, TC>(C, ldc, token, n, N, s, lane);
+            }
+        }
+        if (sm.is_last && threadIdx.x == 0) counters[tile] = 0;
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BT) : "memory");
+    }
+}
+
+template <int BT, int STAGES, int EPI, typename TC>
+static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int ldc, int M, int N, int K,
+                         int k_splits, int blocks_per_split, float* partial, int* counters, cudaStream_t stream) {
+    const size_t smem = sizeof(SkinnySmem<BT, STAGES>) + 1024;
+    static bool configured = false;
+    auto kernel = gemm_skinny_kernel<BT, STAGES, EPI, TC>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid((N + kRowsPerTile - 1) / kRowsPerTile, k_splits);
+    return launch_pdl(kernel, grid, dim3(kSkinnyThreads), smem, stream, mw, ma, (TC*)C, ldc, M, N, K, blocks_per_split,
+                      partial, counters);
+}
+
+template <int BT, int STAGES>
+static int dispatch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int c_dtype, int ldc, int M, int N,
+                           int K, int epilogue, int k_splits, int bps, float* partial, int* counters, cudaStream_t st) {
+    if (epilogue == 2) return launch_skinny<BT, STAGES, 2, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
+    if (epilogue == 1) return launch_skinny<BT, STAGES, 1, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
+    if (c_dtype == kF32) return launch_skinny<BT, STAGES, 0, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
+    return launch_skinny<BT, STAGES, 0, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
+}
+
+static int token_tile(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
+
+}  // namespace b200
+
+extern "C" int b200_gemm_skinny_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, b200::g_skinny_status, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(b200::g_skinny_status, &zero, sizeof(int));
+    return v;
+}
+
+// How the product would be cut: spans of K (k_splits), and what the workspace must hold: floats of
+// partial tiles and ints of tile counters (zero before the first call).  Returns 0 or an error.
+extern "C" int b200_gemm_skinny_plan(int M, int N, int K, int n_sms, int* k_splits, long long* partial_floats,
+                                     int* n_counters) {
+    using namespace b200;
+    if (M <= 0 || M > 128 || N <= 0 || K < 8) return kErrUnsupportedSize;
+    const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
+    const int kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (tiles < n_sms) {
+        splits = n_sms / tiles;                  // one CTA per SM at most (shared memory), one wave
+        splits = splits < 1 ? 1 : splits;
+        if (splits > kb / 4) splits = kb / 4;    // at least 4 stages of work per span
+        if (splits < 1) splits = 1;
+        if (splits > 16) splits = 16;
+    }
+    const int bps = (kb + splits - 1) / splits;
+    splits = (kb + bps - 1) / bps;               // no empty span
+    *k_splits = splits;
+    *partial_floats = splits > 1 ? (long long)splits * tiles * token_tile(M) * kRowsPerTile : 0;
+    *n_counters = tiles;
+    return 0;
+}
+
+extern "C" int b200_gemm_skinny(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
+                                int N, int K, int epilogue, int k_splits, float* partial, long long partial_floats,
+                                int* counters, int n_counters, cudaStream_t stream) {
+    using namespace b200;
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 128 || K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
+    if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
+        return kErrBadArgument;
+    if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
+    const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
+    const int kb = (K + BK - 1) / BK;
+    if (k_splits < 1 || k_splits > kb || k_splits > 65535) return kErrBadArgument;
+    const int bps = (kb + k_splits - 1) / k_splits;
+    const int bt = token_tile(M);
+    if (k_splits > 1 && (partial == nullptr || counters == nullptr || n_counters < tiles ||
+                         partial_floats < (long long)k_splits * tiles * bt * kRowsPerTile))
+        return 10003;
+    CUtensorMap mw, ma;
+    if (!make_map(&mw, W, N, K, ldw, kRowsPerTile) || !make_map(&ma, A, M, K, lda, bt)) return kErrUnsupportedSize;
+    if (bt == 32) return dispatch_skinny<32, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
+    if (bt == 64) return dispatch_skinny<64, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
+    return dispatch_skinny<128, 6>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
+}

@@ -244,6 +244,36 @@ def test_gemm_tcgen05_and_its_epilogues(M, N, K):
         assert not o.gemm_tcgen05(a[:, 4:], w[:, 4:], torch.empty(M, N, device="cuda"))
 
 
+@pytest.mark.parametrize("M", [1, 17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("N, K, splits", [(128, 64, None), (300, 200, None), (2048, 2048, None), (2048, 2048, 1),
+                                          (130, 1024, 5), (16384, 512, None), (258, 8192, 16)])
+def test_gemm_skinny_and_its_epilogues(M, N, K, splits):
+    """Few tokens against many weight rows, with K cut into spans whose partial tiles the last CTA adds
+    up; the same inputs twice must give the same bits (the sum does not depend on arrival order)."""
+    o = ops()
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    ref = a.float().cpu().double() @ w.float().cpu().double().t()
+    for c_dtype in (torch.bfloat16, torch.float32):
+        c = torch.full((M, N), 7.0, dtype=c_dtype, device="cuda")
+        assert o.gemm_skinny(a, w, c, o.EPILOGUE_STORE, splits)
+        torch.testing.assert_close(c.float().cpu(), ref.float().to(c_dtype).float(), **tol(c_dtype, ref))
+        c2 = torch.empty_like(c)
+        assert o.gemm_skinny(a, w, c2, o.EPILOGUE_STORE, splits)
+        assert torch.equal(c, c2)
+    res0 = torch.randn(M, N, generator=g)
+    res = res0.clone().cuda()
+    assert o.gemm_skinny(a, w, res, o.EPILOGUE_RESIDUAL_ADD, splits)
+    torch.testing.assert_close(res.cpu(), (res0.double() + ref).float(), **tol(torch.float32, ref))
+    h = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+    assert o.gemm_skinny(a, w, h, o.EPILOGUE_GATED_SILU, splits)
+    gated = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+    torch.testing.assert_close(h.float().cpu(), gated.float().to(torch.bfloat16).float(), **tol(torch.bfloat16, gated))
+    assert o.gemm_skinny_status() == 0
+    assert not o.gemm_skinny(torch.zeros(129, K, dtype=torch.bfloat16, device="cuda"), w, torch.empty(129, N, device="cuda"))
+
+
 @pytest.mark.parametrize("H, KVH, D, window", [(4, 2, 32, 0), (32, 8, 64, 0), (3, 1, 96, 0), (16, 1, 128, 0),
                                                (8, 8, 64, 0), (24, 2, 32, 0), (8, 2, 64, 100), (4, 1, 128, 33)])
 @pytest.mark.parametrize("n_splits", [1, 3, 16])
