@@ -9,10 +9,11 @@
 // tornadovm/TransformerComputeKernelsLayered.java:901-930 of the reference project.)
 //
 // Narrow outputs (few tiles of 128 rows) would leave most SMs idle, so K is also cut into
-// `k_splits` spans, one CTA each.  A span's CTA leaves its partial tile in scratch memory and
-// bumps the tile's counter; the CTA that arrives last adds the partials of all spans in span
-// order (so the sum does not depend on which CTA came last), applies the epilogue and resets
-// the counter.  Counters must be zero before the first call; every call leaves them zero.
+// `k_splits` spans (up to 8), one CTA each, and the CTAs of a tile form a thread-block cluster.
+// Each CTA leaves its partial tile in its own shared memory; after a cluster barrier every CTA
+// adds up, for its share of the tokens, the partials of all spans in span order through
+// distributed shared memory and applies the epilogue.  No scratch in global memory, no atomics:
+// the sum does not depend on timing.
 //
 // Epilogues: 0 store, 1 residual add into float32 C, 2 silu(gate) * up on interleaved rows.
 #include "tcgen05.cuh"
@@ -33,8 +34,22 @@ struct SkinnySmem {
     uint64_t acc_full;
     uint32_t tmem_base;
     int abort_flag;
-    int is_last;
 };
+
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address, in the cluster's shared window, of `local` as it sits in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t peer_shared_address(const void* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float ld_cluster_shared(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
 
 template <int EPI, typename TC>
 __device__ __forceinline__ void skinny_emit(TC* __restrict__ C, int ldc, int token, int n, int N, float v, int lane) {
@@ -51,12 +66,11 @@ __device__ __forceinline__ void skinny_emit(TC* __restrict__ C, int ldc, int tok
 template <int BT, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                   TC* __restrict__ C, int ldc, int M, int N, int K, int blocks_per_split,
-                   float* __restrict__ partial, int* __restrict__ counters) {
+                   TC* __restrict__ C, int ldc, int M, int N, int K, int blocks_per_split) {
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<SkinnySmem<BT, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, split = blockIdx.y, k_splits = gridDim.y, n_tiles = gridDim.x;
+    const int tile = blockIdx.x, split = blockIdx.y, k_splits = gridDim.y;  // the cluster is (1, k_splits, 1)
     const int n0 = tile * kRowsPerTile;
     const int kb_total = (K + BK - 1) / BK;
     const int kb_begin = split * blocks_per_split;
@@ -66,7 +80,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         mbar_init(&sm.acc_full, 1);
         sm.abort_flag = 0;
-        sm.is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -149,7 +162,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < M) skinny_emit<EPI, TC>(C, ldc, c0 + j, n, N, v[j], lane);
                 } else {
-                    float* p = partial + (((size_t)split * n_tiles + tile) * BT + c0) * kRowsPerTile + r;
+                    // the stage buffers are free once the accumulator is complete: the partial tile
+                    // [token][row] goes where the first stages of W were
+                    float* p = reinterpret_cast<float*>(sm.w) + (size_t)c0 * kRowsPerTile + r;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < M) p[(size_t)j * kRowsPerTile] = v[j];
@@ -159,25 +174,32 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     if (k_splits > 1) {
-        __threadfence();  // this CTA's partial tile is visible before its arrival is counted
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const int arrived = atomicAdd(&counters[tile], 1);
-            sm.is_last = arrived == k_splits - 1;
-        }
-        __syncthreads();
-        if (sm.is_last && warp >= 2 && !sm.abort_flag) {
-            __threadfence();
+        __syncthreads();    // the role branches have joined again: whole warps reach the cluster barrier
+        cluster_barrier();  // every span's partial tile is in its CTA's shared memory
+        if (warp >= 2) {
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane, n = n0 + r;
-            for (int token = 0; token < M; ++token) {
-                float s = 0.f;
-                for (int sp = 0; sp < k_splits; ++sp)
-                    s += __ldcg(partial + (((size_t)sp * n_tiles + tile) * BT + token) * kRowsPerTile + r);
-                skinny_emit<EPI, TC>(C, ldc, token, n, N, s, lane);
+            uint32_t peer[8];  // this thread's row of the partial tile in every span's CTA
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+                peer[sp] = peer_shared_address(reinterpret_cast<const float*>(sm.w) + r, sp < k_splits ? sp : 0);
+            // this CTA's share of the tokens, two at a time so that up to 16 remote loads are in flight
+            for (int token = split; token < M; token += 2 * k_splits) {
+                const int token2 = token + k_splits;
+                float v0[8], v1[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    v0[sp] = sp < k_splits ? ld_cluster_shared(peer[sp] + (uint32_t)token * kRowsPerTile * 4) : 0.f;
+                    v1[sp] = (sp < k_splits && token2 < M) ? ld_cluster_shared(peer[sp] + (uint32_t)token2 * kRowsPerTile * 4) : 0.f;
+                }
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) { s0 += v0[sp]; s1 += v1[sp]; }  // span order, zeros beyond k_splits
+                skinny_emit<EPI, TC>(C, ldc, token, n, N, s0, lane);
+                if (token2 < M) skinny_emit<EPI, TC>(C, ldc, token2, n, N, s1, lane);
             }
         }
-        if (sm.is_last && threadIdx.x == 0) counters[tile] = 0;
+        cluster_barrier();  // no CTA leaves while a peer may still read its shared memory
     }
     __syncthreads();
     if (warp == 1) {
@@ -188,7 +210,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <int BT, int STAGES, int EPI, typename TC>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int ldc, int M, int N, int K,
-                         int k_splits, int blocks_per_split, float* partial, int* counters, cudaStream_t stream) {
+                         int k_splits, int blocks_per_split, cudaStream_t stream) {
     const size_t smem = sizeof(SkinnySmem<BT, STAGES>) + 1024;
     static bool configured = false;
     auto kernel = gemm_skinny_kernel<BT, STAGES, EPI, TC>;
@@ -197,18 +219,37 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C, 
             return (int)cudaGetLastError();
         configured = true;
     }
-    dim3 grid((N + kRowsPerTile - 1) / kRowsPerTile, k_splits);
-    return launch_pdl(kernel, grid, dim3(kSkinnyThreads), smem, stream, mw, ma, (TC*)C, ldc, M, N, K, blocks_per_split,
-                      partial, counters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + kRowsPerTile - 1) / kRowsPerTile, k_splits);
+    cfg.blockDim = dim3(kSkinnyThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (k_splits > 1) {  // the spans of one tile are one cluster
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = k_splits;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, mw, ma, (TC*)C, ldc, M, N, K, blocks_per_split);
 }
 
 template <int BT, int STAGES>
 static int dispatch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int c_dtype, int ldc, int M, int N,
-                           int K, int epilogue, int k_splits, int bps, float* partial, int* counters, cudaStream_t st) {
-    if (epilogue == 2) return launch_skinny<BT, STAGES, 2, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
-    if (epilogue == 1) return launch_skinny<BT, STAGES, 1, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
-    if (c_dtype == kF32) return launch_skinny<BT, STAGES, 0, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
-    return launch_skinny<BT, STAGES, 0, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, partial, counters, st);
+                           int K, int epilogue, int k_splits, int bps, cudaStream_t st) {
+    if (epilogue == 2) return launch_skinny<BT, STAGES, 2, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, st);
+    if (epilogue == 1) return launch_skinny<BT, STAGES, 1, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, st);
+    if (c_dtype == kF32) return launch_skinny<BT, STAGES, 0, float>(mw, ma, C, ldc, M, N, K, k_splits, bps, st);
+    return launch_skinny<BT, STAGES, 0, __nv_bfloat16>(mw, ma, C, ldc, M, N, K, k_splits, bps, st);
 }
 
 static int token_tile(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
@@ -222,50 +263,36 @@ extern "C" int b200_gemm_skinny_status() {
     return v;
 }
 
-// How the product would be cut: spans of K (k_splits), and what the workspace must hold: floats of
-// partial tiles and ints of tile counters (zero before the first call).  Returns 0 or an error.
-extern "C" int b200_gemm_skinny_plan(int M, int N, int K, int n_sms, int* k_splits, long long* partial_floats,
-                                     int* n_counters) {
+// How many spans K is cut into for (M, N, K) on a GPU with n_sms SMs (1 .. 8).
+extern "C" int b200_gemm_skinny_splits(int M, int N, int K, int n_sms) {
     using namespace b200;
-    if (M <= 0 || M > 128 || N <= 0 || K < 8) return kErrUnsupportedSize;
+    if (M <= 0 || N <= 0 || K < 8) return 1;
     const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
     const int kb = (K + BK - 1) / BK;
+    // Measured on B200: clusters of 4 spans beat 8 (the reduction and the cluster's placement cost more
+    // than the extra CTAs win), and a span needs a few stages of work to amortise its start-up.
     int splits = 1;
-    if (tiles < n_sms) {
-        splits = n_sms / tiles;                  // one CTA per SM at most (shared memory), one wave
-        splits = splits < 1 ? 1 : splits;
-        if (splits > kb / 4) splits = kb / 4;    // at least 4 stages of work per span
-        if (splits < 1) splits = 1;
-        if (splits > 16) splits = 16;
-    }
+    if (tiles * 4 <= n_sms && kb >= 16) splits = 4;
+    else if (tiles * 2 <= n_sms && kb >= 8) splits = 2;
     const int bps = (kb + splits - 1) / splits;
-    splits = (kb + bps - 1) / bps;               // no empty span
-    *k_splits = splits;
-    *partial_floats = splits > 1 ? (long long)splits * tiles * token_tile(M) * kRowsPerTile : 0;
-    *n_counters = tiles;
-    return 0;
+    return (kb + bps - 1) / bps;                 // no empty span
 }
 
 extern "C" int b200_gemm_skinny(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                int N, int K, int epilogue, int k_splits, float* partial, long long partial_floats,
-                                int* counters, int n_counters, cudaStream_t stream) {
+                                int N, int K, int epilogue, int k_splits, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
     if (M > 128 || K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
-    const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
     const int kb = (K + BK - 1) / BK;
-    if (k_splits < 1 || k_splits > kb || k_splits > 65535) return kErrBadArgument;
+    if (k_splits < 1 || k_splits > 8 || k_splits > kb) return kErrBadArgument;
     const int bps = (kb + k_splits - 1) / k_splits;
     const int bt = token_tile(M);
-    if (k_splits > 1 && (partial == nullptr || counters == nullptr || n_counters < tiles ||
-                         partial_floats < (long long)k_splits * tiles * bt * kRowsPerTile))
-        return 10003;
     CUtensorMap mw, ma;
     if (!make_map(&mw, W, N, K, ldw, kRowsPerTile) || !make_map(&ma, A, M, K, lda, bt)) return kErrUnsupportedSize;
-    if (bt == 32) return dispatch_skinny<32, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
-    if (bt == 64) return dispatch_skinny<64, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
-    return dispatch_skinny<128, 6>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, partial, counters, stream);
+    if (bt == 32) return dispatch_skinny<32, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+    if (bt == 64) return dispatch_skinny<64, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+    return dispatch_skinny<128, 6>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
 }

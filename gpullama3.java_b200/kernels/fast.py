@@ -17,16 +17,10 @@ def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -
     M = a.shape[0]
     if M <= 16:
         return ops.gemm_decode(a, w, c, epilogue)
-    if M <= 128:
-        # wide outputs fill the GPU with one CTA per 128 weight rows; narrow ones would leave most SMs idle
-        # (and cutting K over CTAs costs more in the final sum than it wins), so up to 64 tokens they stay
-        # with the weight-streaming mma kernel, which splits K inside a CTA
-        wide = w.shape[0] >= 96 * 128
-        if (wide or M > 64) and ops.gemm_skinny(a, w, c, epilogue, 1):
-            return True
-        if M <= 64 and ops.gemm_decode(a, w, c, epilogue):
-            return True
-        return ops.gemm_skinny(a, w, c, epilogue, 1)
+    if M <= 128 and ops.gemm_skinny(a, w, c, epilogue):
+        return True
+    if M <= 64 and ops.gemm_decode(a, w, c, epilogue):
+        return True
     return ops.gemm_tcgen05(a, w, c, epilogue)
 
 

@@ -44,7 +44,7 @@ _SIGNATURES = {
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                            c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-                                                 c_int, c_int, c_int, c_void_p, ctypes.c_longlong, c_void_p, c_int]),
+                                                 c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                    c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
                                                    c_int, c_int]),
@@ -218,20 +218,6 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     return True
 
 
-_skinny_workspace: dict = {}
-
-
-def _skinny_buffers(device: torch.device, partial_floats: int, n_counters: int):
-    """Scratch of the few-token product: partial tiles (float32) and tile counters (int32, zero between
-    calls).  Kept per device and only ever grown, so that recorded decode steps keep valid addresses."""
-    ws = _skinny_workspace.get(device)
-    if ws is None or ws[0].numel() < partial_floats or ws[1].numel() < n_counters:
-        partial = torch.empty(max(partial_floats, 4 << 20), dtype=torch.float32, device=device)
-        counters = torch.zeros(max(n_counters, 4096), dtype=torch.int32, device=device)
-        ws = _skinny_workspace[device] = (partial, counters, ws)  # the old buffers stay alive for recorded graphs
-    return ws[0], ws[1]
-
-
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
                 k_splits: int | None = None) -> bool:
     """The few-token matrix product on tcgen05 tensor cores (bfloat16 operands, at most 128 tokens,
@@ -247,20 +233,21 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
     assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
     fn = _fn("b200_gemm_skinny")
-    lib = library("gemm_skinny_tcgen05")
-    splits, floats, counters = c_int(0), ctypes.c_longlong(0), c_int(0)
-    sms = torch.cuda.get_device_properties(a.device).multi_processor_count
-    _check(lib.b200_gemm_skinny_plan(M, N, K, sms, ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(counters)),
-           "gemm_skinny_plan")
-    n_splits = splits.value if k_splits is None else k_splits
-    tiles = counters.value
-    bt = 32 if M <= 32 else (64 if M <= 64 else 128)
-    need = n_splits * tiles * bt * 128 if n_splits > 1 else 0
-    partial, cnt = _skinny_buffers(a.device, need, tiles)
+    if k_splits is None:
+        k_splits = library("gemm_skinny_tcgen05").b200_gemm_skinny_splits(M, N, K, _sm_count(a.device))
     _check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), dtype_code(c.dtype), c.stride(0), M, N,
-              K, epilogue, n_splits, partial.data_ptr(), partial.numel(), cnt.data_ptr(), cnt.numel(), _stream()),
-           "gemm_skinny")
+              K, epilogue, k_splits, _stream()), "gemm_skinny")
     return True
+
+
+_sm_counts: dict = {}
+
+
+def _sm_count(device) -> int:
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 def gemm_skinny_status() -> int:
