@@ -25,6 +25,11 @@ __device__ __forceinline__ void mma_pf(float (&d)[4], uint32_t a0, uint32_t a1, 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {  // 2^x, relative error about 2^-22; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -89,7 +94,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[mt][j][i] = 0.f;
     }
-    const float sqrt_d = sqrtf((float)D);
+    const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);  // log2(e) / sqrt(d)
 
     // keys this warp needs: from the window's start of its first row to its last row's position
     const int p_first = start + row0, p_last = start + min(row0 + MT * 16, q_len) - 1;
@@ -132,49 +137,58 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, 
                     mma_pf(s[i], ql[mt][kb].z, qh[mt][kb].z, ql[mt][kb].w, qh[mt][kb].w, kf[i][kb].z, kf[i][kb].w);
                 }
             }
+            // scores stay in units of q.k; exp((s - m) / sqrt(d)) is evaluated as exp2((s - m) * scale_log2)
             float bm[2] = {-INFINITY, -INFINITY};
+            if (!full) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = base + 8 * t + 2 * i + e;
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = base + 8 * t + 2 * i + e;
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        const bool ok = full || (key <= pos[mt][r] && (window <= 0 || key > pos[mt][r] - window));
-                        const float v = ok ? s[i][2 * r + e] / sqrt_d : -INFINITY;
-                        s[i][2 * r + e] = v;
-                        bm[r] = fmaxf(bm[r], v);
+                        for (int r = 0; r < 2; ++r) {
+                            const bool ok = key <= pos[mt][r] && (window <= 0 || key > pos[mt][r] - window);
+                            if (!ok) s[i][2 * r + e] = -INFINITY;
+                        }
                     }
-                }
-            float corr[2], mn[2];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                bm[0] = fmaxf(bm[0], fmaxf(s[i][0], s[i][1]));
+                bm[1] = fmaxf(bm[1], fmaxf(s[i][2], s[i][3]));
+            }
+            float corr[2], mn[2], mn_scaled[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 1));
                 bm[r] = fmaxf(bm[r], __shfl_xor_sync(0xffffffffu, bm[r], 2));
                 mn[r] = fmaxf(m_run[mt][r], bm[r]);
                 // a row may see no key of this block (its position lies before it): nothing changes for it
-                corr[r] = mn[r] == -INFINITY ? 1.f : expf(m_run[mt][r] - mn[r]);
+                corr[r] = mn[r] == m_run[mt][r] ? 1.f : fast_exp2((m_run[mt][r] - mn[r]) * scale_log2);
                 m_run[mt][r] = mn[r];
-                l_run[mt][r] *= corr[r];
+                mn_scaled[r] = mn[r] == -INFINITY ? 0.f : mn[r] * scale_log2;  // exp2(-inf - 0) = 0 for masked keys
             }
+            // the running maximum rarely moves after the first blocks: rescale only when some row's did
+            if (!__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f)) {
+                l_run[mt][0] *= corr[0];
+                l_run[mt][1] *= corr[1];
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                o[mt][j][0] *= corr[0]; o[mt][j][1] *= corr[0];
-                o[mt][j][2] *= corr[1]; o[mt][j][3] *= corr[1];
+                for (int j = 0; j < NJ; ++j) {
+                    o[mt][j][0] *= corr[0]; o[mt][j][1] *= corr[0];
+                    o[mt][j][2] *= corr[1]; o[mt][j][3] *= corr[1];
+                }
             }
             uint32_t pa[4][2];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float p[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float mm = mn[c >> 1];
-                    p[c] = mm == -INFINITY ? 0.f : expf(s[i][c] - mm);
-                }
-                l_run[mt][0] += p[0] + p[1];
-                l_run[mt][1] += p[2] + p[3];
-                pa[i][0] = pack2(p[0], p[1]);
-                pa[i][1] = pack2(p[2], p[3]);
+                const float p0 = fast_exp2(fmaf(s[i][0], scale_log2, -mn_scaled[0]));
+                const float p1 = fast_exp2(fmaf(s[i][1], scale_log2, -mn_scaled[0]));
+                const float p2 = fast_exp2(fmaf(s[i][2], scale_log2, -mn_scaled[1]));
+                const float p3 = fast_exp2(fmaf(s[i][3], scale_log2, -mn_scaled[1]));
+                l_run[mt][0] += p0 + p1;
+                l_run[mt][1] += p2 + p3;
+                pa[i][0] = pack2(p0, p1);
+                pa[i][1] = pack2(p2, p3);
             }
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
