@@ -18,6 +18,13 @@
 //       that over the four tiles lane t ends up with the probabilities of keys 8t..8t+7 ...
 //   O[heads x d] += P V : ... which is exactly one 16-byte load of a V^T row (dim, keys 8t..8t+7).
 //
+// Fused variant (b200_attention_decode_rope): the step's own rotation and cache write are done
+// here instead of in a kernel of their own.  Each CTA rotates the queries of its heads in registers
+// (inference/InferenceCore.java:83-95); the CTA of the last span also rotates the new key, stores it
+// and the new value at the sequence's last position (:100-101) and feeds that one key to the softmax
+// directly as a partial of its own (m = score, l = 1, o = v), so the cache is only ever read for
+// positions written by earlier steps.
+//
 // Sizes: head_dim 32, 64, 96 or 128; group size (heads per kv head) <= 16.  Others are refused.
 #include "attention_decode_static.h"
 #include "common.cuh"
@@ -55,18 +62,41 @@ __device__ __forceinline__ uint4 keep_first(uint4 v, int n) {
 }
 
 // Partials in scratch: o [seq][head][split][d] floats, then ml [seq][head][split][2] floats.
-template <int KB>  // head_dim / 32
+struct RopeArgs {            // what the fused variant needs beyond the plain one
+    const float* inv_freq;   // [head_dim / 2]
+    int pairing;             // 0: (2j, 2j+1); 1: (j, j + head_dim/2)
+    int write_cache;         // 0: the layer reads a cache another layer wrote in this step (queries are still rotated)
+};
+
+// rotated element d of a head's vector x (raw, bfloat16) at position pos
+__device__ __forceinline__ float rotate_elem(const __nv_bfloat16* x, int d, int D, int pos, const float* inv_freq, int pairing) {
+    const int half = D / 2;
+    int j, d0, d1;
+    bool first;
+    if (pairing == 0) { j = d >> 1; d0 = d & ~1; d1 = d0 + 1; first = (d & 1) == 0; }
+    else { j = d < half ? d : d - half; d0 = j; d1 = j + half; first = d < half; }
+    float sn, cs;
+    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    const float v0 = __bfloat162float(x[d0]), v1 = __bfloat162float(x[d1]);
+    return first ? v0 * cs - v1 * sn : v0 * sn + v1 * cs;
+}
+
+template <int KB, bool FUSED>  // head_dim / 32; rotation and cache write of the step done here
 __global__ void __launch_bounds__(kAttnDecodeThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ kv_lens, const int* __restrict__ page_table, int table_stride,
-                        const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                        __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_heads, int n_kv_heads,
-                        int window, int n_splits) {
+                        int window, int n_splits, RopeArgs rope) {
     constexpr int D = KB * 32;
     constexpr int NJ = D / 8;  // output tiles of 8 dims
-    extern __shared__ float smem[];  // [warps][16][D] outputs, then [warps][16][2] (m, l)
+    constexpr int SLOTS = kAttnDecodeWarps + (FUSED ? 1 : 0);  // partials merged per CTA: the warps, and the new key
+    extern __shared__ float smem[];  // [SLOTS][16][D] outputs, [SLOTS][16][2] (m, l); fused: q [16][D], k [D], v [D]
     float* o_s = smem;
-    float* ml_s = smem + kAttnDecodeWarps * 16 * D;
+    float* ml_s = smem + SLOTS * 16 * D;
+    float* q_s = ml_s + SLOTS * 16 * 2;
+    float* k_s = q_s + 16 * D;
+    float* v_s = k_s + D;
 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -75,8 +105,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     pdl_wait();  // queries, the new keys and values, lengths and page tables come from earlier kernels
     const int kv_len = kv_lens[seq];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
-    const int first_block = lo / 32, last_block = (kv_len - 1) / 32;
-    const int per_split = (last_block - first_block + 1 + n_splits - 1) / n_splits;
+    // keys read from the cache: all of them, or all but the step's own when this kernel writes that one
+    const int n_cached = (FUSED && rope.write_cache) ? kv_len - 1 : kv_len;
+    const int first_block = lo / 32, last_block = n_cached > lo ? (n_cached - 1) / 32 : first_block - 1;
+    const int per_split = max(1, (last_block - first_block + 1 + n_splits - 1) / n_splits);
     const int blk_begin = first_block + split * per_split;
     const int blk_end = min(blk_begin + per_split, last_block + 1);
     const int* pages = page_table + (size_t)seq * table_stride;
@@ -91,6 +123,49 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         for (int kb = 0; kb < KB; ++kb) {
             ql[kb] = g < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
             qh[kb] = g + 8 < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        }
+        if (FUSED) {
+            // rotate in registers.  A lane holds dims 32 kb + 8 t .. + 7 of its rows: interleaved partners sit
+            // side by side; half partners (d, d + D/2) sit in blocks kb and kb + KB/2 of the same lane.
+            const int pos = kv_len - 1;
+            uint32_t* lo32 = reinterpret_cast<uint32_t*>(ql);
+            uint32_t* hi32 = reinterpret_cast<uint32_t*>(qh);
+            auto unpack = [](uint32_t w, float& a, float& b) { a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u); };
+            if (rope.pairing == 0) {
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float sn, cs;
+                        sincosf((float)pos * rope.inv_freq[(kb * 32 + t * 8) / 2 + e], &sn, &cs);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t* w = (h ? hi32 : lo32) + kb * 4 + e;
+                            float v0, v1;
+                            unpack(*w, v0, v1);
+                            *w = pack_bf16(v0 * cs - v1 * sn, v0 * sn + v1 * cs);
+                        }
+                    }
+            } else {
+#pragma unroll
+                for (int kb = 0; kb < KB / 2; ++kb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float sn[2], cs[2];
+                        sincosf((float)pos * rope.inv_freq[kb * 32 + t * 8 + 2 * e], &sn[0], &cs[0]);
+                        sincosf((float)pos * rope.inv_freq[kb * 32 + t * 8 + 2 * e + 1], &sn[1], &cs[1]);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t* wa = (h ? hi32 : lo32) + kb * 4 + e;               // dims d, d + 1
+                            uint32_t* wb = (h ? hi32 : lo32) + (kb + KB / 2) * 4 + e;    // dims d + D/2, d + D/2 + 1
+                            float a0, a1, b0, b1;
+                            unpack(*wa, a0, a1);
+                            unpack(*wb, b0, b1);
+                            *wa = pack_bf16(a0 * cs[0] - b0 * sn[0], a1 * cs[1] - b1 * sn[1]);
+                            *wb = pack_bf16(a0 * sn[0] + b0 * cs[0], a1 * sn[1] + b1 * cs[1]);
+                        }
+                    }
+            }
         }
     }
     float o[NJ][4];
@@ -139,7 +214,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = base + 8 * t + 2 * i + e;
-                const bool ok = key >= lo && key < kv_len;
+                const bool ok = key >= lo && key < n_cached;
                 s[i][e] = ok ? s[i][e] / sqrt_d : -INFINITY;
                 s[i][2 + e] = ok ? s[i][2 + e] / sqrt_d : -INFINITY;
                 bm_lo = fmaxf(bm_lo, s[i][e]);
@@ -150,7 +225,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
         bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
         const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
-        // a block always holds at least one valid key (blocks run from lo/32 to (kv_len-1)/32), so mn is finite
+        // a block always holds at least one valid key (blocks run from lo/32 to (n_cached-1)/32), so mn is finite
         const float c_lo = expf(m_lo - mn_lo), c_hi = expf(m_hi - mn_hi);
         m_lo = mn_lo;
         m_hi = mn_hi;
@@ -168,7 +243,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             pa[i][0] = pack_bf16(p0, p1);
             pa[i][1] = pack_bf16(p2, p3);
         }
-        const int n_valid = kv_len - (base + 8 * t);  // keys of this lane's V slice that exist
+        const int n_valid = n_cached - (base + 8 * t);  // keys of this lane's V slice that exist
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const uint4 v = n_valid >= 8 ? vf[j] : keep_first(vf[j], max(n_valid, 0));
@@ -196,15 +271,61 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         ml_s[(warp * 16 + g + 8) * 2] = m_hi;
         ml_s[(warp * 16 + g + 8) * 2 + 1] = l_hi;
     }
+    if (FUSED) {
+        // The step's own key and value.  The CTA of the last span stores them at the sequence's last position
+        // and adds them to the softmax as one more partial: m = q.k / sqrt(d), l = 1, o = v.
+        const bool mine = rope.write_cache && split == n_splits - 1;
+        if (mine) {
+            const int pos = kv_len - 1;
+            const __nv_bfloat16* row = q + (size_t)seq * q_row_stride;
+            const __nv_bfloat16* k_raw = row + (size_t)n_heads * D + (size_t)kvh * D;
+            const __nv_bfloat16* v_raw = k_raw + (size_t)n_kv_heads * D;
+            const size_t page_base = (size_t)pages[pos / kPageTokens] * page_stride + head_off;
+            for (int d = threadIdx.x; d < D; d += kAttnDecodeThreads) {
+                const __nv_bfloat16 kr = __float2bfloat16_rn(rotate_elem(k_raw, d, D, pos, rope.inv_freq, rope.pairing));
+                k_pool[page_base + (size_t)(pos % kPageTokens) * D + d] = kr;
+                v_pool[page_base + (size_t)d * kPageTokens + (pos % kPageTokens)] = v_raw[d];
+                k_s[d] = __bfloat162float(kr);
+                v_s[d] = __bfloat162float(v_raw[d]);
+            }
+            if (warp == 0) {  // the rotated queries, as the tensor cores see them
+                const uint32_t* lo32 = reinterpret_cast<const uint32_t*>(ql);
+                const uint32_t* hi32 = reinterpret_cast<const uint32_t*>(qh);
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int d = kb * 32 + t * 8 + 2 * e;
+                        q_s[g * D + d] = __uint_as_float(lo32[kb * 4 + e] << 16);
+                        q_s[g * D + d + 1] = __uint_as_float(lo32[kb * 4 + e] & 0xffff0000u);
+                        q_s[(g + 8) * D + d] = __uint_as_float(hi32[kb * 4 + e] << 16);
+                        q_s[(g + 8) * D + d + 1] = __uint_as_float(hi32[kb * 4 + e] & 0xffff0000u);
+                    }
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 16; idx += kAttnDecodeThreads) {
+            float sc = -INFINITY;
+            if (mine && idx < group) {
+                float dot = 0.f;
+                for (int d = 0; d < D; ++d) dot += q_s[idx * D + d] * k_s[d];
+                sc = dot / sqrt_d;
+            }
+            ml_s[(kAttnDecodeWarps * 16 + idx) * 2] = sc;
+            ml_s[(kAttnDecodeWarps * 16 + idx) * 2 + 1] = mine && idx < group ? 1.f : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads)
+            o_s[(size_t)kAttnDecodeWarps * 16 * D + idx] = mine ? v_s[idx % D] : 0.f;
+    }
     __syncthreads();
     for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads) {
         const int row = idx / D, d = idx % D;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnDecodeWarps; ++w) m = fmaxf(m, ml_s[(w * 16 + row) * 2]);
+        for (int w = 0; w < SLOTS; ++w) m = fmaxf(m, ml_s[(w * 16 + row) * 2]);
         float l = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < kAttnDecodeWarps; ++w) {
+        for (int w = 0; w < SLOTS; ++w) {
             const float mw = ml_s[(w * 16 + row) * 2];
             const float f = mw == -INFINITY ? 0.f : expf(mw - m);
             l += ml_s[(w * 16 + row) * 2 + 1] * f;
@@ -249,39 +370,81 @@ extern "C" long long b200_attention_decode_scratch_floats(int n_seqs, int n_head
     return (long long)n_seqs * n_heads * n_splits * (head_dim + 2);
 }
 
-extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens,
-                                     const int* page_table, int table_stride, const void* k_pool, const void* v_pool,
-                                     float* scratch, long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads,
-                                     int head_dim, int window, int n_splits, cudaStream_t stream) {
-    using namespace b200;
+namespace b200 {
+
+static int launch_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens, const int* page_table,
+                                   int table_stride, void* k_pool, void* v_pool, float* scratch, long long scratch_floats,
+                                   int n_seqs, int n_heads, int n_kv_heads, int head_dim, int window, int n_splits,
+                                   bool fused, RopeArgs rope, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits < 1) return kErrBadArgument;
     const int group = n_heads / n_kv_heads;
     if (group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128 || q_row_stride % 8 != 0) return kErrUnsupportedSize;
     if (n_seqs > 65535 || n_kv_heads > 65535) return kErrUnsupportedSize;
+    if (fused && rope.pairing == 1 && head_dim != 64 && head_dim != 128) return kErrUnsupportedSize;
+    if (fused && (rope.pairing < 0 || rope.pairing > 1 || rope.inv_freq == nullptr)) return kErrBadArgument;
     if (scratch_floats < b200_attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)) return 10003;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * head_dim;
     dim3 grid(n_splits, n_kv_heads, n_seqs);
-    const size_t smem = sizeof(float) * kAttnDecodeWarps * 16 * (head_dim + 2);
+    const int slots = kAttnDecodeWarps + (fused ? 1 : 0);
+    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 18 * head_dim : 0));
     auto qq = (const __nv_bfloat16*)q;
-    auto kk = (const __nv_bfloat16*)k_pool;
-    auto vv = (const __nv_bfloat16*)v_pool;
+    auto kk = (__nv_bfloat16*)k_pool;
+    auto vv = (__nv_bfloat16*)v_pool;
     auto oo = (__nv_bfloat16*)out;
     int st = 0;
-#define B200_LAUNCH(KB)                                                                                          \
-    st = launch_pdl(attention_decode_kernel<KB>, grid, dim3(kAttnDecodeThreads), smem, stream, qq, q_row_stride, oo, \
-                    kv_lens, page_table, table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits)
+#define B200_LAUNCH(KB, F)                                                                                          \
+    do {                                                                                                            \
+        auto kernel = attention_decode_kernel<KB, F>;                                                               \
+        if (smem > 48 * 1024) {                                                                                     \
+            static bool configured = false;                                                                         \
+            if (!configured) {                                                                                      \
+                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+                    return (int)cudaGetLastError();                                                                 \
+                configured = true;                                                                                  \
+            }                                                                                                       \
+        }                                                                                                           \
+        st = launch_pdl(kernel, grid, dim3(kAttnDecodeThreads), smem, stream, qq, q_row_stride, oo, kv_lens, page_table, \
+                        table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits, rope);         \
+    } while (0)
+#define B200_PICK(KB) do { if (fused) B200_LAUNCH(KB, true); else B200_LAUNCH(KB, false); } while (0)
     switch (head_dim / 32) {
-        case 1: B200_LAUNCH(1); break;
-        case 2: B200_LAUNCH(2); break;
-        case 3: B200_LAUNCH(3); break;
-        default: B200_LAUNCH(4); break;
+        case 1: B200_PICK(1); break;
+        case 2: B200_PICK(2); break;
+        case 3: B200_PICK(3); break;
+        default: B200_PICK(4); break;
     }
+#undef B200_PICK
 #undef B200_LAUNCH
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
                       (const float*)part_o, (const float*)part_ml, oo, n_splits, head_dim);
+}
+
+}  // namespace b200
+
+// Queries already rotated, keys and values of the step already in the cache.
+extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens,
+                                     const int* page_table, int table_stride, const void* k_pool, const void* v_pool,
+                                     float* scratch, long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads,
+                                     int head_dim, int window, int n_splits, cudaStream_t stream) {
+    return b200::launch_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, const_cast<void*>(k_pool),
+                                         const_cast<void*>(v_pool), scratch, scratch_floats, n_seqs, n_heads, n_kv_heads,
+                                         head_dim, window, n_splits, false, b200::RopeArgs{nullptr, 0, 0}, stream);
+}
+
+// The fused variant: `qkv` holds the step's raw projections [n_seqs, (n_heads + 2 n_kv_heads) head_dim]; queries
+// are rotated here, and with write_cache the new key (rotated) and value are stored at position kv_len - 1.
+// Rotary dimension = head_dim.  Half pairing needs head_dim 64 or 128.
+extern "C" int b200_attention_decode_rope(const void* qkv, int q_row_stride, void* out, const int* kv_lens,
+                                          const int* page_table, int table_stride, void* k_pool, void* v_pool,
+                                          float* scratch, long long scratch_floats, int n_seqs, int n_heads,
+                                          int n_kv_heads, int head_dim, int window, int n_splits, const float* inv_freq,
+                                          int pairing, int write_cache, cudaStream_t stream) {
+    return b200::launch_attention_decode(qkv, q_row_stride, out, kv_lens, page_table, table_stride, k_pool, v_pool, scratch,
+                                         scratch_floats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, true,
+                                         b200::RopeArgs{inv_freq, pairing, write_cache}, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -24,6 +24,21 @@ def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -
     return ops.gemm_tcgen05(a, w, c, epilogue)
 
 
+def try_decode_attention_with_rope(qkv, out, ctx, page_table, cache, mixer, writes_cache: bool) -> bool:
+    """A decode step's rotation, cache write and attention in one kernel, where the sizes allow."""
+    pos = mixer.position
+    if not (ctx.all_decode and ops.attention_decode_rope_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads,
+                                                                   mixer.head_dim, pos.rotary_dim, pos.pairing)):
+        return False
+    splits = ctx.extras.get("decode_splits")
+    if splits is None:
+        splits = ops.attention_decode_splits(ctx.n_seqs, mixer.n_kv_heads, ctx.max_kv_len)
+    ops.attention_decode_rope(qkv, out, ctx.kv_lens, page_table, cache.k, cache.v, pos.inverse_frequencies(qkv.device),
+                              mixer.n_heads, mixer.n_kv_heads, mixer.head_dim, pos.pairing, mixer.window or 0, splits,
+                              write_cache=writes_cache)
+    return True
+
+
 def try_attention(qkv, out, ctx, page_table, cache, mixer) -> bool:
     if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
         splits = ctx.extras.get("decode_splits")

@@ -50,6 +50,9 @@ _SIGNATURES = {
                                                    c_int, c_int]),
     "b200_attention_prefill": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_attention_decode_rope": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                        c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int,
+                                                        c_int, c_int, c_int, c_void_p, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
 }
@@ -278,6 +281,36 @@ def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resid
     while p * 2 <= want:
         p *= 2
     return p
+
+
+def attention_decode_rope_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                                    pairing: int) -> bool:
+    """Whether the decode kernel can also do the step's rotation and cache write."""
+    return (attention_decode_supported(dtype, n_heads, n_kv_heads, head_dim) and rotary_dim == head_dim
+            and (pairing == 0 or head_dim in (64, 128)))
+
+
+def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, kv_lens: torch.Tensor, page_table: torch.Tensor,
+                          k_pool: torch.Tensor, v_pool: torch.Tensor, inv_freq: torch.Tensor, n_heads: int,
+                          n_kv_heads: int, head_dim: int, pairing: int, window: int, n_splits: int,
+                          write_cache: bool = True, scratch: torch.Tensor | None = None) -> None:
+    """Decode attention that rotates the step's queries itself and, with ``write_cache``, stores the
+    step's rotated key and its value at position kv_lens[i] - 1 of sequence i.  ``qkv``: the raw
+    projections [n_seqs, (n_heads + 2 n_kv_heads) head_dim] (left untouched)."""
+    _dev(qkv, out, kv_lens, page_table, k_pool, v_pool, inv_freq)
+    n_seqs = out.shape[0]
+    assert qkv.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous() and qkv.is_contiguous()
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and inv_freq.dtype == torch.float32
+    assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    need = n_seqs * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+    if need and (scratch is None or scratch.numel() < need):
+        scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+    _check(_fn("b200_attention_decode_rope")(
+        qkv.data_ptr(), qkv.shape[1], out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
+        n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, inv_freq.data_ptr(), pairing,
+        1 if write_cache else 0, _stream()), "attention_decode_rope")
 
 
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,

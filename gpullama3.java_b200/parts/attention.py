@@ -44,15 +44,17 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True):
         qkv = self.qkv.store(x, ctx.dtype)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
-        table = ctx.page_tables[cache.group]
-        ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
-                             cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
-                             self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
-        out = torch.empty((x.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
         from ..kernels import fast
-        if not fast.try_attention(qkv, out, ctx, table, cache, self):
-            ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
-                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
+
+        table = ctx.page_tables[cache.group]
+        out = torch.empty((x.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
+        if not fast.try_decode_attention_with_rope(qkv, out, ctx, table, cache, self, writes_cache):
+            ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
+                                 cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                                 self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
+            if not fast.try_attention(qkv, out, ctx, table, cache, self):
+                ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
+                                    self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
         self.o.add_to(out, residual)
 
 

@@ -323,6 +323,47 @@ def test_attention_prefill_against_plain(H, KVH, D, window):
     torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("H, KVH, D, pairing, window", [(8, 2, 64, "half", 0), (32, 8, 64, "half", 0), (4, 1, 128, "half", 70),
+                                                        (6, 3, 32, "interleaved", 0), (3, 1, 96, "interleaved", 0),
+                                                        (16, 1, 128, "interleaved", 0)])
+@pytest.mark.parametrize("n_splits", [1, 4])
+def test_attention_decode_with_fused_rotation_and_cache_write(H, KVH, D, pairing, window, n_splits):
+    """One kernel that rotates the step's queries, stores its key and value and attends must give what
+    the rotation kernel followed by the attention kernel give: the same cache, the same output."""
+    from gpullama3.java_b200.parts.position import PAIRING_CODES
+    o = ops()
+    kv_lens = [1, 2, 33, 64, 65, 300, 517]   # lengths after the step: the new token sits at kv_len - 1
+    B = len(kv_lens)
+    k_pool, v_pool, table, _ = _paged_setup(torch.bfloat16, B, kv_lens, KVH, D, n_pages=40, seed=D + H)
+    g = torch.Generator().manual_seed(3)
+    qkv = (torch.randn(B, (H + 2 * KVH) * D, generator=g) * 2).to(torch.bfloat16).cuda()
+    inv = P.rope_inverse_frequencies(D, 5e5, None).to(torch.float32).cuda()
+    lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    pos = lens - 1
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    code = PAIRING_CODES[pairing]
+    assert o.attention_decode_rope_supported(torch.bfloat16, H, KVH, D, D, code)
+    # two steps, reference: separate kernels
+    k_ref, v_ref, q_ref = k_pool.clone(), v_pool.clone(), qkv.clone()
+    o.rope_cache_write(q_ref, pos, seq, table, inv, k_ref, v_ref, H, KVH, D, D, code)
+    want = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    o.attention_decode(q_ref, q_ref.shape[1], want, lens, table, k_ref, v_ref, H, KVH, D, window, n_splits)
+    # fused
+    k_new, v_new, raw = k_pool.clone(), v_pool.clone(), qkv.clone()
+    got = torch.empty_like(want)
+    o.attention_decode_rope(raw, got, lens, table, k_new, v_new, inv, H, KVH, D, code, window, n_splits)
+    assert torch.equal(raw, qkv)                         # the projections are left as they were
+    assert torch.equal(k_new, k_ref) and torch.equal(v_new, v_ref)
+    scale = float(want.float().abs().max())
+    torch.testing.assert_close(got.float(), want.float(), rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
+    # a layer that reads another layer's cache: nothing is stored, the cached last position is attended
+    got2 = torch.empty_like(want)
+    k2, v2 = k_ref.clone(), v_ref.clone()
+    o.attention_decode_rope(raw, got2, lens, table, k2, v2, inv, H, KVH, D, code, window, n_splits, write_cache=False)
+    assert torch.equal(k2, k_ref) and torch.equal(v2, v_ref)
+    torch.testing.assert_close(got2.float(), want.float(), rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
+
+
 def test_attention_decode_ignores_what_lies_beyond_a_sequence():
     """Slots are used again without clearing: stale or non-finite numbers after a sequence's last
     position (same page) and in pages of other sequences must not reach the output."""
