@@ -22,7 +22,6 @@ namespace b200 {
 
 constexpr int kDecodeWarps = 8;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kUnroll = 4;  // k-blocks of 32 in flight per warp
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {
     uint4 v;
@@ -42,14 +41,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 
 // MT: 16-row tiles of weight rows per CTA (ROWS = 16 * MT), or MT = 0 for 8 rows (narrow outputs, so that
 // more CTAs pull on HBM).  NT: token tiles of 8.  EPI: 0 store, 1 residual add (C float), 2 gated SiLU.
-template <int MT, int NT, int EPI, typename TC>
+template <int MT, int NT, int EPI, typename TC, int U>  // U: k-blocks of 32 in flight per warp
 __global__ void __launch_bounds__(kDecodeThreads)
 gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
                    TC* __restrict__ C, int ldc, int M, int N, int K) {
     constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
     constexpr int MTT = MT == 0 ? 1 : MT;            // tiles actually multiplied
     constexpr bool HI = MT != 0;                     // rows g + 8 of a tile exist
-    constexpr int U = (MTT * NT >= 8) ? 2 : kUnroll;  // k-blocks in flight per warp
     extern __shared__ float red_raw[];               // [warps][NT * 8][ROWS] partial sums, then [NT * 8][ROWS]
     float (*red)[NT * 8][ROWS] = reinterpret_cast<float (*)[NT * 8][ROWS]>(red_raw);
     float (*fin)[ROWS] = reinterpret_cast<float (*)[ROWS]>(red_raw + kDecodeWarps * NT * 8 * ROWS);
@@ -102,19 +100,22 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
 #pragma unroll
             for (int m = 0; m < MTT; ++m) { cl[u][m] = wl[u][m]; ch[u][m] = wh[u][m]; }
         load_weights(kb0 + kDecodeWarps * U);  // next round's weights, in flight during this round's MMAs
+        // activation fragments of the round are all requested before the first MMA needs one
+        uint4 av[U][NT];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const bool k_ok = kb0 + u < n_blocks;
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int n = 0; n < NT; ++n) {
-                const uint4 av = (a_ok[n] && k_ok) ? load_cached(a_row[n] + (kb0 + u) * 32) : make_uint4(0, 0, 0, 0);
+            for (int n = 0; n < NT; ++n)
+                av[u][n] = (a_ok[n] && kb0 + u < n_blocks) ? load_cached(a_row[n] + (kb0 + u) * 32) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
 #pragma unroll
                 for (int m = 0; m < MTT; ++m) {
-                    mma_bf16(acc[m][n], cl[u][m].x, ch[u][m].x, cl[u][m].y, ch[u][m].y, av.x, av.y);
-                    mma_bf16(acc[m][n], cl[u][m].z, ch[u][m].z, cl[u][m].w, ch[u][m].w, av.z, av.w);
+                    mma_bf16(acc[m][n], cl[u][m].x, ch[u][m].x, cl[u][m].y, ch[u][m].y, av[u][n].x, av[u][n].y);
+                    mma_bf16(acc[m][n], cl[u][m].z, ch[u][m].z, cl[u][m].w, ch[u][m].w, av[u][n].z, av[u][n].w);
                 }
-            }
-        }
     }
 
     // partial sums of the warps meet in shared memory; thread (row, token) adds them in warp order
@@ -155,12 +156,12 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     }
 }
 
-template <int MT, int NT, int EPI, typename TC>
-static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
-                      int K, cudaStream_t stream) {
+template <int MT, int NT, int EPI, typename TC, int U>
+static int launch_u(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
+                    int K, cudaStream_t stream) {
     constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
     const size_t smem = sizeof(float) * (kDecodeWarps + 1) * NT * 8 * ROWS;
-    auto kernel = gemm_decode_kernel<MT, NT, EPI, TC>;
+    auto kernel = gemm_decode_kernel<MT, NT, EPI, TC, U>;
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -171,6 +172,17 @@ static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, i
     }
     return launch_pdl(kernel, dim3((N + ROWS - 1) / ROWS), dim3(kDecodeThreads), smem, stream, a, lda, w, ldw, (TC*)C, ldc,
                       M, N, K);
+}
+
+template <int MT, int NT, int EPI, typename TC>
+static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
+                      int K, cudaStream_t stream) {
+    constexpr int MTT = MT == 0 ? 1 : MT;
+    if (MTT * NT >= 8) return launch_u<MT, NT, EPI, TC, 2>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    // 8-row CTAs of a short grid (at most two per SM) can afford twice the loads in flight; a longer grid
+    // needs the registers for a third and fourth resident CTA instead
+    if (MT == 0 && NT == 1 && N <= 2 * 148 * 8) return launch_u<MT, NT, EPI, TC, (MT == 0 && NT == 1) ? 8 : 4>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    return launch_u<MT, NT, EPI, TC, 4>(a, lda, w, ldw, C, ldc, M, N, K, stream);
 }
 
 template <int MT, int NT, typename TC>

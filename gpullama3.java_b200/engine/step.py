@@ -112,6 +112,7 @@ class DecodeGraph:
         np.concatenate(pieces, out=self.host.numpy())
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
+        self.h2d_bytes = self.host.numel() * 4
 
     def _forward(self, slots, start_pos):
         ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, slots,
@@ -163,6 +164,7 @@ class StepFunction:
         self.reuse_output = False   # True: the caller consumes the logits before the next step (no copy is made)
         self._graphs: dict[tuple, DecodeGraph] = {}
         self.graph_launches = 0     # kernel launches replayed from graphs so far
+        self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy (tokens, positions, page tables)
 
     def _decode_with_graph(self, inputs: list[SequenceInput], reuse_output: bool) -> torch.Tensor | None:
         cache = self.cache
@@ -182,6 +184,7 @@ class StepFunction:
             g = self._graphs[key] = DecodeGraph(self.model, cache, n, widths)
         replayed = g.graph is not None
         logits = g.run(slots, start, [s.tokens[0] for s in inputs])
+        self.last_h2d_bytes = g.h2d_bytes
         if replayed:
             self.graph_launches += g.n_launches
         for s in slots:
@@ -250,6 +253,7 @@ class StepFunction:
                         dest.append(out_offsets[i] + j)
                 base += len(t)
             ctx, rows_dev = build_context(model.dtype, model.device, cache, slots, start, toks, rows)
+            self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
             logits = model.forward(ctx, cache, rows_dev)
             for (_, s), t in zip(part, toks):
                 cache.commit(s.slot, len(t))
