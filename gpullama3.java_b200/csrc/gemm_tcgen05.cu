@@ -5,13 +5,14 @@
 // residual :766-784, fused SiLU gate :808-826); here a 128 x BN tile of C is accumulated in
 // tensor memory by tcgen05.mma, fed by TMA through a ring of shared-memory stages.
 //
-// One CTA computes one tile.  Roles (192 threads):
+// Persistent CTAs (one per SM) each compute a sequence of tiles.  Roles (192 threads):
 //   warp 0, one lane   producer: waits for a free stage, arms its mbarrier with the byte count and
 //                      issues two TMA loads (A box 64x128, W box 64xBN; 128-byte swizzle)
 //   warp 1, one lane   issues four tcgen05.mma (K = 16 each) per stage into the TMEM accumulator,
-//                      then tcgen05.commit onto the stage's "empty" mbarrier; after the last stage
-//                      a commit onto the "accumulator full" mbarrier.  Warp 1 also owns the TMEM
-//                      allocation (BN columns) and frees it at the end.
+//                      then tcgen05.commit onto the stage's "empty" mbarrier; after a tile's last stage
+//                      a commit onto that accumulator's "full" mbarrier.  Two accumulators (2 x BN columns
+//                      of TMEM, owned by warp 1) alternate, so the next tile's main loop runs while the
+//                      epilogue warps still read the previous tile out.
 //   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns at a time, then one of
 //                      0 store (bfloat16 or float32), 1 residual add into float32 C,
 //                      2 silu(gate) * up on interleaved gate/up columns (bfloat16 out, N/2 wide).
@@ -34,11 +35,19 @@ struct GemmSmem {
     alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t acc_full;
+    uint64_t acc_full[2];   // MMA -> epilogue: accumulator b holds a finished tile
+    uint64_t acc_empty[2];  // epilogue -> MMA: accumulator b has been read out
     uint32_t tmem_base;
     int abort_flag;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: CTA c computes tiles c, c + gridDim.x, ...; tiles are numbered with n fastest so that CTAs running at
+// the same time share rows of A and sweep W, which the L2 then serves.  Two accumulators of BN columns live in tensor
+// memory: while the epilogue warps read tile i out of one, the MMA thread already fills the other with tile i + 1.
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kGemmTcThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -46,19 +55,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, n_tiles = tiles_n * tiles_m;
     const int k_iters = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-        mbar_init(&sm.acc_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 4); }
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     }
-    if (warp == 1) {  // tensor memory for the accumulator: BN columns of 128 lanes
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(BN) : "memory");
+    if (warp == 1) {  // tensor memory for two accumulators of BN columns x 128 lanes
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -69,53 +78,85 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---- producer
-        for (int it = 0; it < k_iters; ++it) {
-            const int s = it % STAGES;
-            if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
-                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (1 << 8) | s); break;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (1 << 8) | s); ok = false; break;
+                }
+                mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+                tma_load_2d(sm.a[s], &map_a, k * BK, m0, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_w, k * BK, n0, &sm.full[s]);
             }
-            mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
-            tma_load_2d(sm.a[s], &map_a, it * BK, m0, &sm.full[s]);
-            tma_load_2d(sm.b[s], &map_w, it * BK, n0, &sm.full[s]);
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer.  Instruction descriptor: D f32, A and B bf16, both K-major, N x 128.
+        // ---- MMA issuer
         constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        int it = 0, local = 0;
         bool ok = true;
-        for (int it = 0; it < k_iters && ok; ++it) {
-            const int s = it % STAGES;
-            if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
-                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (2 << 8) | s); ok = false; break;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            // the first use of each accumulator finds it free (a fresh barrier passes a wait for parity 1)
+            if (!mbar_wait(&sm.acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (4 << 8) | buf); break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
+            const uint32_t acc = tmem + buf * BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (2 << 8) | s); ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)  // 16 elements = 32 bytes further along K: +2 in the address field
-                umma_bf16(tmem, ad + 2 * k, bd + 2 * k, idesc, (it | k) != 0);
-            umma_commit(&sm.empty[s]);  // frees the stage once these MMAs have read it
+                for (int kk = 0; kk < BK / 16; ++kk)  // 16 elements = 32 bytes further along K: +2 in the address field
+                    umma_bf16(acc, ad + 2 * kk, bd + 2 * kk, idesc, (k | kk) != 0);
+                umma_commit(&sm.empty[s]);  // frees the stage once these MMAs have read it
+            }
+            if (ok) umma_commit(&sm.acc_full[buf]);
         }
-        if (ok) umma_commit(&sm.acc_full);
     } else if (warp >= 2) {
         // ---- epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        bool ok = mbar_wait(&sm.acc_full, 0, abort_flag);
-        if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (3 << 8) | quarter); }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int row = m0 + quarter * 32 + lane;
+            bool ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (3 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= N) break;  // uniform: whole chunk beyond the matrix
                 float v[32];
-                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
                 if (row >= M) continue;
                 const int col = n0 + c0;
                 if (EPI == 2) {
                     TC* dst = C + (size_t)row * ldc + (col >> 1);
+                    if (col + 32 <= N && ((uintptr_t)dst & 15) == 0 && sizeof(TC) == 2) {
+                        uint32_t pk[8];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>((v[2 * j] / (1.0f + expf(-v[2 * j]))) * v[2 * j + 1]);
+                        for (int j = 0; j < 8; ++j) {
+                            const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                            __nv_bfloat162 h = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+                            pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        uint4* d = reinterpret_cast<uint4*>(dst);
+                        d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>((v[2 * j] / (1.0f + expf(-v[2 * j]))) * v[2 * j + 1]);
+                    }
                 } else {
                     TC* dst = C + (size_t)row * ldc + col;
                     const bool whole = col + 32 <= N && ((uintptr_t)dst & 15) == 0;
@@ -149,13 +190,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            // this warp has read its lanes of the accumulator out: once all four have, the MMA thread may reuse it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
     }
 }
 
@@ -169,7 +214,14 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
             return (int)cudaGetLastError();
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0)
+            n_sms = 148;
+    }
+    const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    dim3 grid((unsigned)(n_tiles < n_sms ? n_tiles : n_sms));
     kernel<<<grid, kGemmTcThreads, smem, stream>>>(ma, mw, (TC*)C, ldc, M, N, K);
     return launch_status();
 }
@@ -193,7 +245,6 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
-    if ((M + BM - 1) / BM > 65535) return kErrUnsupportedSize;
     constexpr int BN = 256, STAGES = 4;
     CUtensorMap ma, mw;
     if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;

@@ -1,0 +1,69 @@
+"""The layer sizes of the real models (Llama-3.2-3B and Llama-3.1-8B: head size 128, 24 or 32 heads over 8 kv
+heads, widths 3072/4096, feed-forward 8192/14336) with two layers and a short vocabulary: prompts in one step and
+then decoded tokens, in both precisions, against the plain implementation.  These sizes take the tensor-core
+kernels' other template instances (head_dim 128, groups of 3 and 4, K = 14336, prefill tiles with ragged edges)."""
+import pytest
+import torch
+
+import plain_llama as P
+from conftest import make_model_dir, plain_inputs, random_prompts
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "3B": dict(hidden_size=3072, num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192,
+               rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192}, tie_word_embeddings=True),
+    "8B": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192}, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("name", ["3B", "8B"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_layers_of_real_size(session_tmp, name, dtype):
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    cfg_json = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, vocab_size=1000, rope_theta=500000.0,
+                    rms_norm_eps=1e-5, max_position_embeddings=8192, **SHAPES[name])
+    d = make_model_dir(session_tmp, cfg_json, seed=31)   # N(0, 0.02): at these widths the scores already spread over a few units
+    cfg, w = plain_inputs(d)
+    lengths = [150, 37, 70]           # 257 tokens in the prompt step: more than two prefill tiles, a ragged edge
+    prompts = random_prompts(1000, lengths, seed=8)
+    tail = 6
+    rt = None if dtype == torch.float32 else torch.bfloat16
+    refs = [P.forward(cfg, w, p, round_to=rt) for p in prompts]
+    # Sums of 8192 and 14336 terms: round-off itself is no longer small against the tiny models' tolerances, so
+    # the yardstick here is the plain implementation's own error (float32, or rounded to bfloat16 at the places
+    # where the engine rounds) against its float64 run: on the same rows the engine may be twice (bfloat16) or
+    # four times (float32, whose noise is tiny) that far from the float64 logits, not more.
+    exact = [P.forward(cfg, w, p, dtype=torch.float64) for p in prompts]
+    scale = max(float(e.abs().max()) for e in exact)
+    factor = 4.0 if dtype == torch.float32 else 2.0
+
+    def check(got, i, rows, what):
+        g, e, r = got.cpu().double(), exact[i][rows].double(), refs[i][rows].double()
+        assert torch.isfinite(g).all(), what
+        err, noise = float((g - e).abs().max()), float((r - e).abs().max())
+        assert err <= factor * noise + 2e-5 * scale, f"{what}: max err {err:.3e}, plain noise {noise:.3e}, scale {scale:.3e}"
+        err_m, noise_m = float((g - e).abs().mean()), float((r - e).abs().mean())
+        assert err_m <= factor * noise_m + 2e-6 * scale, f"{what}: mean err {err_m:.3e}, plain noise {noise_m:.3e}"
+
+    model = load_model(d, dtype)
+    cache = model.new_cache(64 * 8)
+    step = StepFunction(model, cache)
+    slots = [cache.acquire() for _ in prompts]
+    heads = [n - tail for n in lengths]
+    out = step([SequenceInput(s, p[:h], list(range(h))) for s, p, h in zip(slots, prompts, heads)])
+    off = 0
+    for i, h in enumerate(heads):
+        check(out[off:off + h], i, slice(0, h), f"{name} prompt {i}")
+        off += h
+    for t in range(tail):
+        out = step([SequenceInput(s, [p[h + t]], [0]) for s, p, h in zip(slots, prompts, heads)])
+        for i, h in enumerate(heads):
+            check(out[i:i + 1], i, slice(h + t, h + t + 1), f"{name} decoded token {t} of {i}")
+    for s in slots:
+        cache.release(s)
