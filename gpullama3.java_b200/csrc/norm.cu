@@ -8,20 +8,85 @@
 
 namespace b200 {
 
-template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
-                               const int* __restrict__ rows, int dim, float eps) {
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&f)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float (&f)[4]);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+constexpr int kNormThreads = 256;
+constexpr int kNormKeep = 4;  // groups of 4 elements a thread keeps in registers between the two passes
+
+// VEC: rows are read and written four elements at a time (dim a multiple of 4, pointers aligned); the first
+// kNormKeep * 4 * 256 elements of a row stay in registers, so x is read once for the usual widths.
+template <typename TW, typename TO, bool VEC>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+               const int* __restrict__ rows, int dim, float eps) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
-    ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
     TO* o = out + (size_t)r * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>(to_f32<TW>(w[i]) * (scale * xr[i]));
+    float ss = 0.f;
+    if (VEC) {
+        float keep[kNormKeep][4];
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int i = (k * kNormThreads + threadIdx.x) * 4;
+            if (i < dim) {
+                load4<float>(xr + i, keep[k]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss += keep[k][e] * keep[k][e];
+            }
+        }
+        for (int i = (kNormKeep * kNormThreads + threadIdx.x) * 4; i < dim; i += kNormThreads * 4) {
+            float v[4];
+            load4<float>(xr + i, v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += v[e] * v[e];
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+#pragma unroll
+        for (int k = 0; k < kNormKeep; ++k) {
+            const int i = (k * kNormThreads + threadIdx.x) * 4;
+            if (i < dim) {
+                float wv[4], y[4];
+                load4<TW>(w + i, wv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y[e] = wv[e] * (scale * keep[k][e]);
+                store4<TO>(o + i, y);
+            }
+        }
+        for (int i = (kNormKeep * kNormThreads + threadIdx.x) * 4; i < dim; i += kNormThreads * 4) {
+            float v[4], wv[4], y[4];
+            load4<float>(xr + i, v);
+            load4<TW>(w + i, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = wv[e] * (scale * v[e]);
+            store4<TO>(o + i, y);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>(to_f32<TW>(w[i]) * (scale * xr[i]));
+    }
 }
 
 }  // namespace b200
@@ -29,9 +94,11 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
 extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
                             const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    const int threads = dim >= 1024 ? 256 : 128;
+    const bool vec = dim % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0;
     B200_DISPATCH_DTYPE(w_dtype, TW, B200_DISPATCH_DTYPE2(out_dtype, TO,
-        return b200::launch_pdl(b200::rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, (const TW*)w,
-                                (TO*)out, rows, dim, eps)));
+        return vec ? b200::launch_pdl(b200::rmsnorm_kernel<TW, TO, true>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x,
+                                      (const TW*)w, (TO*)out, rows, dim, eps)
+                   : b200::launch_pdl(b200::rmsnorm_kernel<TW, TO, false>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x,
+                                      (const TW*)w, (TO*)out, rows, dim, eps)));
     return b200::launch_status();
 }

@@ -18,6 +18,8 @@
 
 namespace b200 {
 
+constexpr int kMaxRotaryPairs = 256;  // rotary_dim <= 512
+
 template <typename T>
 __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                         const int* __restrict__ seq_ids, const int* __restrict__ page_table,
@@ -40,14 +42,18 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     }
     const size_t head_stride = (size_t)kPageTokens * head_dim;
 
+    // the angles of this position are the same for every head: one sine and cosine per frequency
+    __shared__ float sin_s[kMaxRotaryPairs], cos_s[kMaxRotaryPairs];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sin_s[j], &cos_s[j]);
+    __syncthreads();
+
     // rotated pairs of queries (in place) and keys (into the cache)
     const int n_units = (n_heads + n_kv_heads) * half;
     for (int u = threadIdx.x; u < n_units; u += blockDim.x) {
         const int h = u / half, j = u % half;
         const int i0 = pairing == 0 ? 2 * j : j;
         const int i1 = pairing == 0 ? 2 * j + 1 : j + half;
-        float s, c;
-        sincosf((float)pos * inv_freq[j], &s, &c);
+        const float s = sin_s[j], c = cos_s[j];
         if (h < n_heads) {
             T* v = row + h * head_dim;
             const float v0 = to_f32<T>(v[i0]), v1 = to_f32<T>(v[i1]);
@@ -84,6 +90,7 @@ extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions,
     if (n_tokens <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || (pairing != 0 && pairing != 1))
         return b200::kErrBadArgument;
+    if (rotary_dim / 2 > b200::kMaxRotaryPairs) return b200::kErrUnsupportedSize;
     B200_DISPATCH_DTYPE(dtype, T,
         return b200::launch_pdl(b200::rope_cache_write_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)qkv,
                                 positions, seq_ids, page_table, table_stride, inv_freq, (T*)k_pool, (T*)v_pool, n_heads,
