@@ -1,0 +1,356 @@
+// Prefill attention on tcgen05 tensor cores (bfloat16, head_dim 64): causal grouped-query attention of
+// packed prompt tokens over the paged cache, flash style.
+//
+// One CTA owns 128 consecutive query tokens of one sequence and one query head and walks over the keys
+// 0 .. position in blocks of 128 (two cache pages).  Per block:
+//     S = Q K^T          tcgen05.mma 128 x 128 x 64, both operands from shared memory, S in tensor memory
+//     P = exp2((S - m) * log2(e) / sqrt(d))   128 threads, one query row each, read S with tcgen05.ld,
+//                        write P as bfloat16 into shared memory in the layout the next MMA wants
+//     O += P V           tcgen05.mma 128 x 64 x 128, P from shared memory, V^T pages as they lie in the cache
+// with the running maximum and sum of the online softmax in registers and O in tensor memory (formulas of
+// inference/InferenceCore.java:106-145 of the reference project, online form of
+// tornadovm/TransformerComputeKernelsLayered.java:431-502).  The reference maximum of a row only moves
+// when a block's maximum exceeds it by more than 2^8 (then O and l are rescaled), which is exact and
+// saves most rescaling passes.  Q, K pages and V^T pages arrive by TMA (128-byte swizzle) through a
+// two-stage ring.  Two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
+//
+// Roles (320 threads): warp 0 lane 0 issues TMA; warp 1 lane 0 issues MMAs (warp 1 owns the 256 TMEM
+// columns: S 128, O 64); warps 2-9 are the softmax (two threads per query row) and the epilogue.  Every mbarrier wait is bounded;
+// a wait that gives up sets a status word and all roles fall through to the common exit.
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+constexpr int kFaThreads = 320;  // TMA warp, MMA warp, eight softmax warps
+constexpr int kFaRows = 128, kFaKeys = 128, kFaD = 64;
+
+__device__ int g_fa_status = 0;
+
+struct FaSmem {
+    alignas(1024) __nv_bfloat16 q[kFaRows * kFaD];         // 16 KB
+    alignas(1024) __nv_bfloat16 k[2][kFaKeys * kFaD];      // per stage: two pages of 64 keys x 64 dims
+    alignas(1024) __nv_bfloat16 v[2][2][kFaD * 64];        // per stage: two pages of 64 dims x 64 keys (V^T)
+    alignas(1024) __nv_bfloat16 p[2][kFaRows * 64];        // probabilities: keys 0-63 and 64-127 of the block
+    alignas(8) uint64_t q_full;
+    uint64_t kv_full[2], kv_empty[2];
+    uint64_t s_full, p_full, o_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    // exchange between the two threads of a row (512 bytes: the struct must stay within 113 KB): block maxima
+    // rounded to bfloat16 (any common reference close to the maximum will do), and at the end the sum
+    union { __nv_bfloat16 row_max[2][kFaRows]; float row_sum[kFaRows]; };
+};
+
+__device__ __forceinline__ void mbar_arrive_fa(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(kFaThreads, 2)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
+                            const int* __restrict__ page_table, int table_stride, int n_heads, int n_kv_heads,
+                            int window, int k_rows_total, int v_rows_total) {
+    // Two CTAs share an SM only if each stays within 113 KB, which leaves no room for an alignment pad: the
+    // dynamic shared memory of a kernel without static shared memory starts at the CTA's window, 1024-aligned;
+    // if it ever does not, the kernel records that and leaves.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(&g_fa_status, 0, 7 << 8);
+        return;
+    }
+    FaSmem& sm = *reinterpret_cast<FaSmem*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
+    const int n_tiles = (q_len + kFaRows - 1) / kFaRows;
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;  // long tiles first
+    if (tile >= n_tiles) return;
+    const int kvh = head / (n_heads / n_kv_heads);
+    const int kv_len = kv_lens[seq], start = kv_len - q_len;
+    const int q0 = tile * kFaRows;
+    const int rows_here = min(kFaRows, q_len - q0);
+    const int p_first = start + q0, p_last = start + q0 + rows_here - 1;  // positions of the first and last row
+    const int key_lo = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int blk_begin = key_lo / kFaKeys, blk_end = p_last / kFaKeys + 1;  // key blocks [begin, end)
+    const int* pages = page_table + (size_t)seq * table_stride;
+    const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 1); }
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_full, 8);
+        mbar_init(&sm.o_full, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: Q once, then per block two K pages and two V^T pages
+        mbar_expect_tx(&sm.q_full, kFaRows * kFaD * 2);
+        tma_load_2d(sm.q, &map_q, head * kFaD, tok0 + q0, &sm.q_full);
+        int it = 0;
+        for (int blk = blk_begin; blk < blk_end; ++blk, ++it) {
+            const int s = it & 1;
+            if (it >= 2 && !mbar_wait(&sm.kv_empty[s], ((it >> 1) - 1) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_fa_status, 0, (1 << 8) | s); break;
+            }
+            mbar_expect_tx(&sm.kv_full[s], 2 * (64 * kFaD * 2) + 2 * (kFaD * 64 * 2));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int lp = blk * 2 + h;  // logical page; pages the sequence does not have are read as zeros
+                const bool have = lp < n_pages_seq;
+                const int page = have ? pages[lp] : 0;
+                tma_load_2d(sm.k[s] + h * 64 * kFaD, &map_k, 0, have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * kFaD : v_rows_total, &sm.kv_full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
+        constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, kFaD);
+        bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
+        if (!ok) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, 2 << 8); }
+        int it = 0;
+        for (int blk = blk_begin; blk < blk_end && ok; ++blk, ++it) {
+            const int s = it & 1;
+            if (!mbar_wait(&sm.kv_full[s], (it >> 1) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_fa_status, 0, (3 << 8) | s); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t qd = umma_desc(sm.q), kd = umma_desc(sm.k[s]);
+#pragma unroll
+            for (int kk = 0; kk < kFaD / 16; ++kk) umma_bf16(tmem_s, qd + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
+            umma_commit(&sm.s_full);  // also means: the previous block's P V has finished
+            if (!mbar_wait(&sm.p_full, it & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_fa_status, 0, 4 << 8); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int kk = 0; kk < kFaKeys / 16; ++kk) {
+                const uint64_t pd = umma_desc(sm.p[kk / 4]) + 2 * (kk % 4);
+                const uint64_t vd = umma_desc(sm.v[s][kk / 4]) + 2 * (kk % 4);
+                umma_bf16(tmem_o, pd, vd, idesc_o, (it | kk) != 0);
+            }
+            umma_commit(&sm.kv_empty[s]);
+        }
+        if (ok) umma_commit(&sm.o_full);
+    } else if (warp >= 2) {
+        // ---- softmax and epilogue.  Eight warps: warp w reads TMEM lanes 32 (w % 4) .. + 31 (query rows); the two
+        // warps of a lane quarter split a block's 128 keys (and O's 64 dims) in halves.  The two threads of a row
+        // agree on the row's maximum through shared memory, so both take the same decisions.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int pos = start + q0 + min(r, rows_here - 1);  // rows past the end mirror the last one (never stored)
+        const float scale_log2 = 1.4426950408889634f / sqrtf((float)kFaD);
+        float m_ref = -INFINITY, l = 0.f;  // reference maximum (units of q.k); this thread's share of the running sum
+        bool ok = true;
+        int it = 0;
+        for (int blk = blk_begin; blk < blk_end; ++blk, ++it) {
+            ok = mbar_wait(&sm.s_full, it & 1, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (5 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int base = blk * kFaKeys + half * 64;  // first key of this thread's half
+            const bool masked = blk * kFaKeys + kFaKeys - 1 > p_first || (window > 0 && blk * kFaKeys < p_last - window + 1);
+            const int lo_key = window > 0 ? pos - window + 1 : 0;
+            // pass 1: the block's maximum of this row (this thread's 64 keys, then both halves together)
+            float m_blk = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float v[32];
+                tmem_ld32(tmem_s + lane_base + half * 64 + c * 32, v);
+                if (masked) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = base + c * 32 + j;
+                        if (key <= pos && key >= lo_key) m_blk = fmaxf(m_blk, v[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) m_blk = fmaxf(m_blk, fmaxf(v[j], v[j + 1]));
+                }
+            }
+            sm.row_max[half][r] = __float2bfloat16_rn(m_blk);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            m_blk = fmaxf(__bfloat162float(sm.row_max[0][r]), __bfloat162float(sm.row_max[1][r]));
+            // the reference maximum moves only when the block exceeds it by more than 2^8 after scaling
+            const bool move = m_blk > m_ref && (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > 8.f);
+            if (__any_sync(0xffffffffu, move)) {
+                const float m_new = move ? m_blk : m_ref;
+                const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
+                l *= corr;
+                if (it > 0) {  // O holds earlier blocks: rescale this row's 32 dims (whole warps take part in the TMEM access)
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_base + half * 32, o);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= corr;
+                    tmem_st32(tmem_o + lane_base + half * 32, o);
+                }
+                m_ref = m_new;
+            }
+            const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
+            // pass 2: probabilities, written as bfloat16 in the K-major 128-byte-swizzled layout of an MMA operand
+            uint8_t* row_base = reinterpret_cast<uint8_t*>(sm.p[half]) + r * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float v[32];
+                tmem_ld32(tmem_s + lane_base + half * 64 + c * 32, v);
+                uint32_t pk[16];
+                float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    float p0 = ex2(fmaf(v[j], scale_log2, -m_scaled));
+                    float p1 = ex2(fmaf(v[j + 1], scale_log2, -m_scaled));
+                    if (masked) {
+                        const int key = base + c * 32 + j;
+                        if (!(key <= pos && key >= lo_key)) p0 = 0.f;
+                        if (!(key + 1 <= pos && key + 1 >= lo_key)) p1 = 0.f;
+                    }
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    l0 += p0;
+                    l1 += p1;
+                    pk[j / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                l += l0 + l1;
+                // 32 keys = 4 chunks of 16 bytes; the chunk index is XORed with row % 8 inside its 128-byte row
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int chunk = (c * 4 + ch) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(row_base + chunk * 16) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+                }
+            }
+            // P is in shared memory (visible to the tensor cores' proxy) and S has been read: the MMA thread may go on
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_fa(&sm.p_full);
+        }
+        if (ok) {
+            ok = mbar_wait(&sm.o_full, 0, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (6 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        // the row's sum is the two halves' shares together (the barriers are reached by all 256 threads, ok or not)
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // every thread is done with the maxima that share this memory
+        if (half == 1) sm.row_sum[r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (half == 0) { l += sm.row_sum[r]; sm.row_sum[r] = l; }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float inv_l = 1.0f / sm.row_sum[r];
+            __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + r) * n_heads + head) * kFaD + half * 32;
+            float o[32];
+            tmem_ld32(tmem_o + lane_base + half * 32, o);
+            if (r < rows_here) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * j] * inv_l, o[8 * j + 1] * inv_l);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * j + 2] * inv_l, o[8 * j + 3] * inv_l);
+                    __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * j + 4] * inv_l, o[8 * j + 5] * inv_l);
+                    __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * j + 6] * inv_l, o[8 * j + 7] * inv_l);
+                    *reinterpret_cast<uint4*>(orow + 8 * j) =
+                        make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
+                                   *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(256) : "memory");
+    }
+}
+
+// 2-D bfloat16 view [rows, cols] with row stride ld elements and boxes of box_cols x box_rows, 128-byte swizzle.
+static bool make_map_2d(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace b200
+
+extern "C" int b200_attention_prefill_tc_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, b200::g_fa_status, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(b200::g_fa_status, &zero, sizeof(int));
+    return v;
+}
+
+// q: packed rows of q_row_stride elements whose first n_heads * 64 are the rotated queries (n_rows of them);
+// k_pool [n_pages][n_kv_heads][64][64], v_pool [n_pages][n_kv_heads][64][64] (values transposed).
+extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_rows, void* out, const int* cu_seqlens,
+                                         const int* kv_lens, const int* page_table, int table_stride,
+                                         const void* k_pool, const void* v_pool, int n_pages, int n_seqs, int max_q_len,
+                                         int n_heads, int n_kv_heads, int head_dim, int window, cudaStream_t stream) {
+    using namespace b200;
+    if (n_seqs <= 0 || max_q_len <= 0) return 0;
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return kErrBadArgument;
+    if (head_dim != kFaD || q_row_stride % 8 != 0 || (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15))
+        return kErrUnsupportedSize;
+    if (n_seqs > 65535 || n_heads > 65535) return kErrUnsupportedSize;
+    const long long k_rows = (long long)n_pages * n_kv_heads * 64, v_rows = (long long)n_pages * n_kv_heads * kFaD;
+    if (k_rows >= (1ll << 31) || v_rows >= (1ll << 31)) return kErrUnsupportedSize;
+    CUtensorMap mq, mk, mv;
+    if (!make_map_2d(&mq, q, n_rows, n_heads * kFaD, q_row_stride, kFaD, kFaRows) ||
+        !make_map_2d(&mk, k_pool, k_rows, kFaD, kFaD, kFaD, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, kFaD))
+        return kErrUnsupportedSize;
+    const size_t smem = sizeof(FaSmem);
+    static_assert(sizeof(FaSmem) <= 113 * 1024, "two CTAs per SM need at most 113 KB each");
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_heads, n_seqs);
+    attention_prefill_tc_kernel<<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
+                                                                   page_table, table_stride, n_heads, n_kv_heads, window,
+                                                                   (int)k_rows, (int)v_rows);
+    return launch_status();
+}

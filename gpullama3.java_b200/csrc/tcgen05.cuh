@@ -11,7 +11,7 @@
 namespace b200 {
 
 constexpr int BK = 64;  // K extent of one pipeline stage: 64 bfloat16 = one 128-byte swizzled row
-constexpr unsigned long long kWaitLimit = 200000ull;  // polls (each suspends up to ~10 us) before a wait gives up
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait on an mbarrier gives up after two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -21,20 +21,33 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase with the given parity.  Returns false when it gave up.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for the phase with the given parity.  Returns false when it gave up: after kWaitLimitNs of
+// wall time, or as soon as another role of the CTA has given up.  The poll itself is the plain try_wait
+// (it returns within a short, hardware-defined time): a suspend-time hint makes every hand-over between
+// roles cost microseconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     const uint32_t addr = smem_u32(bar);
-    for (unsigned long long i = 0; i < kWaitLimit; ++i) {
+    unsigned long long deadline = 0;
+    for (unsigned int i = 0;; ++i) {
         uint32_t done;
         asm volatile(
             "{\n.reg .pred p;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
             "selp.u32 %0, 1, 0, p;\n}"
-            : "=r"(done) : "r"(addr), "r"(parity), "r"(10000u) : "memory");
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
         if (done) return true;
-        if ((i & 15) == 15 && *abort_flag) return false;  // another role already gave up
+        if ((i & 255) == 255) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_timer_ns();
+            if (deadline == 0) deadline = now + kWaitLimitNs;
+            else if (now > deadline) return false;
+        }
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(

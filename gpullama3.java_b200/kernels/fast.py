@@ -47,6 +47,10 @@ def try_attention(qkv, out, ctx, page_table, cache, mixer) -> bool:
         ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,
                              mixer.n_kv_heads, mixer.head_dim, mixer.window or 0, splits)
         return True
+    if qkv.dtype == torch.bfloat16 and ops.attention_prefill_tc(
+            qkv, qkv.shape[1], out, ctx.cu_seqlens, ctx.kv_lens, page_table, cache.k, cache.v, ctx.n_seqs,
+            ctx.max_q_len, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim, mixer.window or 0):
+        return True
     if qkv.dtype == torch.bfloat16 and mixer.head_dim in (32, 64, 96, 128):
         ops.attention_prefill(qkv, qkv.shape[1], out, ctx.cu_seqlens, ctx.kv_lens, page_table, cache.k, cache.v,
                               ctx.n_seqs, ctx.max_q_len, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,

@@ -53,6 +53,9 @@ _SIGNATURES = {
     "b200_attention_decode_rope": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                         c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int,
                                                         c_int, c_int, c_int, c_void_p, c_int, c_int]),
+    "b200_attention_prefill_tc": ("attention_prefill_tcgen05", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                                c_int, c_int, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
 }
@@ -346,6 +349,30 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_
         q.data_ptr(), q_row_stride, out.data_ptr(), cu_seqlens.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), n_seqs, max_q_len, n_heads, n_kv_heads, head_dim,
         int(window), _stream()), "attention_prefill")
+
+
+def attention_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,
+                         kv_lens: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                         n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int) -> bool:
+    """``attention_prefill`` on tcgen05 tensor cores (head_dim 64).  Returns False, having done nothing,
+    for sizes it does not take."""
+    if head_dim != 64 or q.dtype != torch.bfloat16 or q_row_stride % 8 or (q.data_ptr() | out.data_ptr()) & 15:
+        return False
+    _dev(q, out, cu_seqlens, kv_lens, page_table, k_pool, v_pool)
+    assert out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous() and k_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+    assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    _check(_fn("b200_attention_prefill_tc")(
+        q.data_ptr(), q_row_stride, out.shape[0], out.data_ptr(), cu_seqlens.data_ptr(), kv_lens.data_ptr(),
+        page_table.data_ptr(), page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], n_seqs,
+        max_q_len, n_heads, n_kv_heads, head_dim, int(window), _stream()), "attention_prefill_tc")
+    return True
+
+
+def attention_prefill_tc_status() -> int:
+    lib = library("attention_prefill_tcgen05")
+    lib.b200_attention_prefill_tc_status.restype = c_int
+    return int(lib.b200_attention_prefill_tc_status())
 
 
 # --------------------------------------------------------------------------- sampling

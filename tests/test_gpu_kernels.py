@@ -364,6 +364,33 @@ def test_attention_decode_with_fused_rotation_and_cache_write(H, KVH, D, pairing
     torch.testing.assert_close(got2.float(), want.float(), rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
 
 
+@pytest.mark.parametrize("H, KVH, window", [(8, 2, 0), (4, 4, 0), (3, 1, 0), (4, 1, 37), (2, 1, 200), (2, 2, 129)])
+def test_attention_prefill_on_tcgen05_against_plain(H, KVH, window):
+    """The tensor-memory flash kernel (head size 64): whole prompts across several 128-row tiles and 128-key
+    blocks, chunks that continue a cached prefix, single tokens, windows; every wait inside must complete."""
+    D = 64
+    kv_lens = [1, 64, 65, 300, 129, 517, 40, 128, 700]
+    q_starts = [0, 0, 64, 101, 100, 0, 39, 0, 256]
+    k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=60, seed=H + KVH)
+    g = torch.Generator().manual_seed(1)
+    qs, refs, cu = [], [], [0]
+    for s, (n, q0) in enumerate(zip(kv_lens, q_starts)):
+        k, v = dense[s]
+        q_full = (torch.randn(n, H, D, generator=g) * 2).to(torch.bfloat16).float()
+        refs.append(P.causal_attention(q_full, k, v, window or None)[q0:])
+        qs.append(q_full[q0:])
+        cu.append(cu[-1] + n - q0)
+    q = torch.cat(qs).reshape(-1, H * D)
+    qkv = torch.cat([q, torch.randn(q.shape[0], 2 * KVH * D)], dim=1).to(torch.bfloat16).cuda().contiguous()
+    out = torch.full((q.shape[0], H * D), 9.0, dtype=torch.bfloat16, device="cuda")
+    assert ops().attention_prefill_tc(qkv, qkv.shape[1], out, torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                                      torch.tensor(kv_lens, dtype=torch.int32, device="cuda"), table, k_pool, v_pool,
+                                      len(kv_lens), max(n - q0 for n, q0 in zip(kv_lens, q_starts)), H, KVH, D, window)
+    assert ops().attention_prefill_tc_status() == 0
+    ref = torch.cat(refs).reshape(-1, H * D)
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
+
+
 def test_attention_decode_ignores_what_lies_beyond_a_sequence():
     """Slots are used again without clearing: stale or non-finite numbers after a sequence's last
     position (same page) and in pages of other sequences must not reach the output."""
