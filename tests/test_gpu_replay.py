@@ -87,3 +87,55 @@ def test_trace_run_program(setup, tmp_path):
     assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
     got = read_rows(out, rows, cfg["vocab_size"])
     _check(got, _reference(cfg, weights, few, torch.float32), torch.float32, "trace_run")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_a_step_cut_into_passes_gives_the_same_logits(setup, dtype):
+    """A step with more tokens than one pass may hold is run as several passes (chunks of each sequence
+    that continue what the earlier pass cached); wanted places of all passes come back in the order asked."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    d, cfg, weights, requests, refs = setup
+    if dtype not in refs:
+        refs[dtype] = _reference(cfg, weights, requests, dtype)
+    model = load_model(d, dtype)
+    cache = model.new_cache(64 * 16)
+    ids = list(requests)[:5]
+    wants = {r: sorted({0, len(requests[r]) // 3, len(requests[r]) - 1}) for r in ids}
+    for limits in (dict(max_pass_tokens=96, max_sequence_chunk=8192), dict(max_pass_tokens=16384, max_sequence_chunk=40)):
+        step = StepFunction(model, cache, **limits)
+        slots = {r: cache.acquire() for r in ids}
+        out = step([SequenceInput(slots[r], requests[r], wants[r]) for r in ids]).cpu()
+        off = 0
+        for r in ids:
+            n = len(wants[r])
+            assert_close_logits(out[off:off + n], refs[dtype][r][wants[r]], dtype, f"passes {limits} request {r}")
+            off += n
+        for r in ids:
+            assert cache.length(slots[r]) == len(requests[r])
+            cache.release(slots[r])
+    cache.check_invariants()
+
+
+def test_a_step_that_does_not_fit_changes_nothing(setup):
+    from gpullama3.java_b200.cache import CacheFull
+    from gpullama3.java_b200.engine.step import SequenceInput, StepError, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    d, cfg, weights, requests, refs = setup
+    model = load_model(d, torch.float32)
+    cache = model.new_cache(64 * 3)
+    step = StepFunction(model, cache)
+    a, b = cache.acquire(), cache.acquire()
+    first = step([SequenceInput(a, requests["r0"][:20], [19])]).cpu()
+    with pytest.raises(CacheFull):
+        step([SequenceInput(a, [1], [0]), SequenceInput(b, list(range(200)), [199])])     # 1 + 4 pages wanted, 3 exist
+    assert cache.length(a) == 20 and cache.length(b) == 0
+    cache.check_invariants()
+    for bad in ([SequenceInput(a, [], [])], [SequenceInput(a, [cfg["vocab_size"]], [0])], [SequenceInput(a, [1], [1])],
+                [SequenceInput(a, [1], [0]), SequenceInput(a, [2], [0])], [SequenceInput(77, [1], [0])], []):
+        with pytest.raises(StepError):
+            step(bad)
+    again = step([SequenceInput(b, requests["r0"][:20], [19])]).cpu()       # the other slot, same tokens, same logits
+    assert torch.equal(first, again)
