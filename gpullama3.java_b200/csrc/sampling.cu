@@ -10,7 +10,9 @@
 // The uniform number u of each row is an input (the host derives it from seed, request and step
 // counters), so a request's draws do not depend on which batch it sits in.  Sums that decide a
 // token are either accumulated in a fixed order or in integers, so a row always gives the same
-// token.  Equal probabilities are ordered by index in the nucleus.
+// token.  Equal probabilities are ordered by index in the nucleus.  The nucleus is found without sorting:
+// the bits of the probability at which the descending running mass crosses a target are decided
+// two at a time, each pair by one pass of masked sums over the row (two such descents: for top_p, then for the draw).
 #include <limits.h>
 #include "common.cuh"
 
@@ -58,91 +60,136 @@ argmax_rows_kernel(const float* __restrict__ logits, int ld, int* __restrict__ o
 }
 
 struct SampleShared {
-    unsigned long long hist_mass[256];
-    unsigned int hist_cnt[256];
+    unsigned long long sum_u64[3][kSampleWarps + 1];
+    unsigned int sum_u32[kSampleWarps + 1];
     float seg_sum[kSampleWarps];
     unsigned int seg_cnt[kSampleWarps];
     float red[33];
-    // results of one radix descent
-    unsigned int key;
-    unsigned long long above, mass_eq;
-    unsigned int cnt_eq;
-    int found;
     int answer;
 };
 
 constexpr double kMassScale = 1099511627776.0;  // 2^40: probabilities become integers, sums exact
 
-// Walks the candidates (p >= cutoff) in descending order of p and stops at the value where the
-// running mass first exceeds `target`.  Leaves in sh: the bits of that value, the mass strictly
-// above it, and the count and mass of the candidates equal to it.  found = 0 when the whole
-// candidate mass does not exceed target (then `above` is that whole mass).
-__device__ void radix_descent(const float* row, int V, float temperature, float zmax, float total, float cutoff,
-                              unsigned long long target, SampleShared& sh) {
+// Sums of three 64-bit values and one 32-bit value per thread over the CTA; every thread gets all of them.
+__device__ __forceinline__ void block_sum_mass(unsigned long long (&m)[3], unsigned int& c, SampleShared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) m[k] += __shfl_xor_sync(0xffffffffu, m[k], o);
+        c += __shfl_xor_sync(0xffffffffu, c, o);
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) sh.sum_u64[k][warp] = m[k];
+        sh.sum_u32[warp] = c;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long mm[3] = {sh.sum_u64[0][lane], sh.sum_u64[1][lane], sh.sum_u64[2][lane]};
+        unsigned int cc = sh.sum_u32[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) mm[k] += __shfl_xor_sync(0xffffffffu, mm[k], o);
+            cc += __shfl_xor_sync(0xffffffffu, cc, o);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 3; ++k) sh.sum_u64[k][kSampleWarps] = mm[k];
+            sh.sum_u32[kSampleWarps] = cc;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 3; ++k) m[k] = sh.sum_u64[k][kSampleWarps];
+    c = sh.sum_u32[kSampleWarps];
+}
+
+struct Crossing {
+    unsigned int key;                 // bits of the probability at which the running mass first exceeds the target
+    unsigned long long above;         // mass of the candidates with a larger probability
+    unsigned long long mass_eq;       // mass and number of the candidates with exactly that probability
+    unsigned int cnt_eq;
+    bool found;                       // false: the whole candidate mass does not exceed the target (`above` is all of it)
+};
+
+// p * 2^40 is exact in float32 (a power-of-two scale), so the integer part is the same as in double
+__device__ __forceinline__ unsigned long long mass_of(float p) { return (unsigned long long)(p * 1099511627776.0f); }
+
+// Walks the candidates (p >= cutoff) in descending order of p, without sorting: the bits of the crossing
+// probability are decided two at a time from the top, each pair with one pass of masked sums over the row
+// (probabilities are non-negative floats, so their bit patterns order like integers).  Masses are integers
+// (p * 2^40): the sums do not depend on the order of addition.  `probs` is 16-byte aligned when V % 4 == 0.
+__device__ Crossing mass_descent(const float* __restrict__ probs, int V, float cutoff, unsigned long long target,
+                                 SampleShared& sh) {
     unsigned int prefix = 0;
     unsigned long long above = 0;
-    for (int pass = 0; pass < 4; ++pass) {
-        const int shift = 24 - 8 * pass;
-        for (int b = threadIdx.x; b < 256; b += kSampleThreads) { sh.hist_mass[b] = 0; sh.hist_cnt[b] = 0; }
-        __syncthreads();
-        for (int base = 0; base < V; base += kSampleThreads) {
-            const int i = base + threadIdx.x;
-            int bin = -1;
-            unsigned long long q = 0;
-            if (i < V) {
-                const float p = expf(row[i] / temperature - zmax) / total;
-                if (p >= cutoff) {
-                    const unsigned int key = __float_as_uint(p);
-                    if (pass == 0 || (key >> (shift + 8)) == (prefix >> (shift + 8))) {
-                        bin = (key >> shift) & 255;
-                        q = (unsigned long long)((double)p * kMassScale);
-                    }
-                }
+    const bool vec = (V & 3) == 0;
+    // bits 30 .. 0 of a non-negative float: bit 30 alone first, then pairs (29,28) .. (1,0)
+    for (int lo = 30; lo >= 0; lo -= 2) {
+        const int width = lo == 30 ? 1 : 2;               // bits [lo, lo + width)
+        const unsigned int high = ~((1u << (lo + width)) - 1u);
+        const unsigned int field = (1u << width) - 1u;
+        unsigned long long m[3] = {0, 0, 0};              // mass with field value >= 3, >= 2, >= 1
+        unsigned int c = 0;
+        auto take = [&](float p) {
+            const unsigned int key = __float_as_uint(p);
+            if (p >= cutoff && (key & high) == prefix) {
+                const unsigned int f = (key >> lo) & field;
+                const unsigned long long q = mass_of(p);
+                if (f >= 3) m[0] += q;
+                if (f >= 2) m[1] += q;
+                if (f >= 1) m[2] += q;
             }
-            int all_same;
-            __match_all_sync(0xffffffffu, bin, &all_same);
-            if (all_same) {  // the common case in a flat distribution: one atomic for the warp
-                if (bin >= 0) {
+        };
+        if (vec) {
+            // four 16-byte loads are requested before the first is used: a pass is bound by the latency of L2
+            const float4* p4 = reinterpret_cast<const float4*>(probs);
+            const int n4 = V / 4;
+            for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * kSampleThreads) {
+                float4 v[4];
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-                    if ((threadIdx.x & 31) == 0) {
-                        atomicAdd(&sh.hist_mass[bin], q);
-                        atomicAdd(&sh.hist_cnt[bin], 32u);
-                    }
+                for (int k = 0; k < 4; ++k) {
+                    const int i = i0 + k * kSampleThreads;
+                    v[k] = i < n4 ? p4[i] : make_float4(-1.f, -1.f, -1.f, -1.f);  // negative: below any cutoff
                 }
-            } else if (bin >= 0) {
-                atomicAdd(&sh.hist_mass[bin], q);
-                atomicAdd(&sh.hist_cnt[bin], 1u);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { take(v[k].x); take(v[k].y); take(v[k].z); take(v[k].w); }
             }
+        } else {
+            for (int i = threadIdx.x; i < V; i += kSampleThreads) take(probs[i]);
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long cum = above;
-            int chosen = -1;
-            for (int b = 255; b >= 0; --b) {
-                if (sh.hist_cnt[b] == 0) continue;
-                if (cum + sh.hist_mass[b] > target) { chosen = b; break; }
-                cum += sh.hist_mass[b];
-            }
-            sh.above = cum;
-            sh.found = chosen >= 0;
-            if (chosen >= 0) {
-                sh.key = prefix | ((unsigned int)chosen << shift);
-                sh.mass_eq = sh.hist_mass[chosen];
-                sh.cnt_eq = sh.hist_cnt[chosen];
-            }
+        block_sum_mass(m, c, sh);
+        // field values from the top: the crossing lies in the first one whose cumulative mass exceeds the target
+        unsigned int chosen = 0;
+        unsigned long long taken = m[2];                  // everything with field >= 1 lies above field 0
+        for (unsigned int f = field; f >= 1; --f) {
+            if (above + m[3 - f] > target) { chosen = f; taken = f == field ? 0 : m[3 - f - 1]; break; }
         }
-        __syncthreads();
-        if (!sh.found) return;
-        prefix = sh.key;
-        above = sh.above;
-        __syncthreads();
+        above += taken;
+        prefix |= chosen << lo;
     }
+    unsigned long long m[3] = {0, 0, 0};
+    unsigned int c = 0;
+    for (int i = threadIdx.x; i < V; i += kSampleThreads) {
+        const float p = probs[i];
+        if (p >= cutoff && __float_as_uint(p) == prefix) { m[0] += mass_of(p); ++c; }
+    }
+    block_sum_mass(m, c, sh);
+    Crossing r;
+    r.key = prefix;
+    r.above = above;
+    r.mass_eq = m[0];
+    r.cnt_eq = c;
+    r.found = c > 0 && above + m[0] > target;
+    return r;
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ uniforms,
-                   int* __restrict__ out, int V, float temperature, float top_p) {
+                   int* __restrict__ out, int V, float temperature, float top_p, float* __restrict__ probs_scratch) {
     __shared__ SampleShared sh;
     const float* row = logits + (size_t)blockIdx.x * ld;
     const float u = uniforms[blockIdx.x];
@@ -197,20 +244,23 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
         return;
     }
 
-    // nucleus: the kept set is the shortest descending prefix of the candidates whose mass exceeds top_p
+    // nucleus: the kept set is the shortest descending prefix of the candidates whose mass exceeds top_p.
+    // The probabilities are written once to scratch (this row's V floats) and read back by every pass.
+    float* probs = probs_scratch + (size_t)blockIdx.x * V;
+    for (int i = threadIdx.x; i < V; i += kSampleThreads) probs[i] = expf(row[i] / temperature - zmax) / total;
+    __syncthreads();
     float cutoff = (1.0f - top_p) / (float)(V - 1);
     const unsigned long long target1 = (unsigned long long)((double)top_p * kMassScale);
-    radix_descent(row, V, temperature, zmax, total, cutoff, target1, sh);
+    Crossing first = mass_descent(probs, V, cutoff, target1, sh);
     unsigned long long kept_mass;
-    if (sh.found) {
-        const unsigned long long q1 = sh.cnt_eq ? sh.mass_eq / sh.cnt_eq : 0;
-        unsigned long long m = q1 ? (target1 - sh.above) / q1 + 1 : sh.cnt_eq;
-        if (m > sh.cnt_eq) m = sh.cnt_eq;
-        kept_mass = sh.above + m * q1;
+    if (first.found) {
+        const unsigned long long q1 = first.mass_eq / first.cnt_eq;
+        unsigned long long m = q1 ? (target1 - first.above) / q1 + 1 : first.cnt_eq;
+        if (m > first.cnt_eq) m = first.cnt_eq;
+        kept_mass = first.above + m * q1;
     } else {
-        kept_mass = sh.above;
+        kept_mass = first.above + first.mass_eq;
     }
-    __syncthreads();
     unsigned long long target2;
     if (kept_mass == 0) {  // no candidate passes the cutoff: take the most probable token
         cutoff = 0.f;
@@ -219,22 +269,21 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
         target2 = (unsigned long long)((double)u * (double)kept_mass);
         if (target2 >= kept_mass) target2 = kept_mass - 1;
     }
-    radix_descent(row, V, temperature, zmax, total, cutoff, target2, sh);
-    if (!sh.found) {  // cannot happen while target2 < kept mass; keep the last index as the reference's fallback
+    Crossing second = mass_descent(probs, V, cutoff, target2, sh);
+    if (!second.found) {  // cannot happen while target2 < kept mass; keep the last index as the reference's fallback
         if (threadIdx.x == 0) out[blockIdx.x] = V - 1;
         return;
     }
-    const unsigned int key2 = sh.key;
-    const unsigned long long q2 = sh.cnt_eq ? sh.mass_eq / sh.cnt_eq : 0;
-    unsigned long long m2 = q2 ? (target2 - sh.above) / q2 + 1 : 1;
-    if (m2 > sh.cnt_eq) m2 = sh.cnt_eq;
+    const unsigned int key2 = second.key;
+    const unsigned long long q2 = second.mass_eq / second.cnt_eq;
+    unsigned long long m2 = q2 ? (target2 - second.above) / q2 + 1 : 1;
+    if (m2 > second.cnt_eq) m2 = second.cnt_eq;
     if (m2 < 1) m2 = 1;
-    __syncthreads();
 
     // the m2-th token, in index order, whose probability has exactly the bits key2
     unsigned int cnt = 0;
     for (int i = seg_lo + lane; i < seg_hi; i += 32) {
-        const float p = expf(row[i] / temperature - zmax) / total;
+        const float p = probs[i];
         cnt += (p >= cutoff && __float_as_uint(p) == key2) ? 1u : 0u;
     }
 #pragma unroll
@@ -254,7 +303,7 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
             const int i = base + lane;
             bool match = false;
             if (i < seg_hi) {
-                const float p = expf(row[i] / temperature - zmax) / total;
+                const float p = probs[i];
                 match = p >= cutoff && __float_as_uint(p) == key2;
             }
             const unsigned mask = __ballot_sync(0xffffffffu, match);
@@ -282,12 +331,14 @@ extern "C" int b200_argmax_rows(const float* logits, int ld, int* out, int n_row
                             vocab);
 }
 
+// `probs_scratch`: n_rows * vocab floats of workspace, needed only for nucleus sampling (0 < top_p < 1).
 extern "C" int b200_sample_rows(const float* logits, int ld, const float* uniforms, int* out, int n_rows, int vocab,
-                                float temperature, float top_p, cudaStream_t stream) {
+                                float temperature, float top_p, float* probs_scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (vocab <= 0 || !(temperature > 0.f) || top_p < 0.f || top_p > 1.f) return b200::kErrBadArgument;
     if (vocab < 2 && top_p > 0.f && top_p < 1.f) top_p = 1.f;  // the cutoff divides by (n - 1)
+    if (top_p > 0.f && top_p < 1.f && probs_scratch == nullptr) return 10003;
     b200::sample_rows_kernel<<<n_rows, b200::kSampleThreads, 0, stream>>>(logits, ld, uniforms, out, vocab,
-                                                                          temperature, top_p);
+                                                                          temperature, top_p, probs_scratch);
     return b200::launch_status();
 }

@@ -57,7 +57,7 @@ _SIGNATURES = {
                                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                                 c_int, c_int, c_int, c_int]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
-    "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float]),
+    "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
 
 
@@ -390,6 +390,10 @@ def sample_rows(logits: torch.Tensor, uniforms: torch.Tensor, out: torch.Tensor,
     _dev(logits, uniforms, out)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     assert uniforms.dtype == torch.float32 and uniforms.numel() == logits.shape[0]
+    scratch = None
+    if 0.0 < top_p < 1.0:  # nucleus: the row's probabilities are kept in workspace between the passes
+        scratch = torch.empty(logits.shape[0] * logits.shape[1], dtype=torch.float32, device=logits.device)
     _check(_fn("b200_sample_rows")(logits.data_ptr(), logits.stride(0), uniforms.data_ptr(), out.data_ptr(),
-                                   logits.shape[0], logits.shape[1], float(temperature), float(top_p), _stream()),
+                                   logits.shape[0], logits.shape[1], float(temperature), float(top_p),
+                                   scratch.data_ptr() if scratch is not None else None, _stream()),
            "sample_rows")
