@@ -307,3 +307,158 @@ def test_schedule_mistakes_are_refused(toy_registered):
             return [ScheduleEntry(0, 0), ScheduleEntry(2, 0, writes_cache=False)]   # window differs from cache 0's
     with pytest.raises(ConfigError, match="different needs"):
         CausalLM(Bad2.from_dict(TOY), torch.float32, "cpu")
+
+
+# --------------------------------------------------------------------------- a second toy architecture
+class Top1ExpertsFeedForward(__import__("gpullama3.java_b200.parts", fromlist=["FeedForward"]).FeedForward):
+    """Toy feed-forward with routing: router logits in float32, each token goes to its best expert (a small
+    gated feed-forward), the expert's output is weighted by the router's softmax probability."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, n_experts: int):
+        self.h, self.i, self.e = hidden_size, intermediate_size, n_experts
+
+    def parameters(self):
+        p = {"router": ParamSpec((self.e, self.h))}
+        for k in range(self.e):
+            p[f"gate{k}"] = ParamSpec((self.i, self.h))
+            p[f"up{k}"] = ParamSpec((self.i, self.h))
+            p[f"down{k}"] = ParamSpec((self.h, self.i))
+        return p
+
+    def load(self, tensors, dtype, device):
+        from gpullama3.java_b200.parts import Linear
+        wd = torch.float32 if dtype == torch.float32 else torch.bfloat16
+        self.router = tensors["router"].to(device=device, dtype=torch.float32)
+        self.gate_up = [Linear(torch.stack([tensors[f"gate{k}"], tensors[f"up{k}"]], 1).reshape(2 * self.i, self.h)
+                               .to(device=device, dtype=wd).contiguous()) for k in range(self.e)]
+        self.down = [Linear(tensors[f"down{k}"].to(device=device, dtype=wd).contiguous()) for k in range(self.e)]
+
+    def forward(self, x, ctx, residual):
+        probs = torch.softmax(x.float() @ self.router.t(), dim=-1)      # router in 32-bit
+        weight, expert = probs.max(dim=-1)
+        for k in range(self.e):
+            rows = (expert == k).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            h = self.gate_up[k].gated_silu(x[rows].contiguous(), ctx.dtype)
+            y = self.down[k].store(h, torch.float32)
+            residual.index_add_(0, rows, y * weight[rows, None])
+
+
+class HalfRotaryLinearScaling(__import__("gpullama3.java_b200.parts", fromlist=["PositionEncoding"]).PositionEncoding):
+    """Toy position encoding: only the first half of a head is rotated, interleaved pairs, frequencies
+    theta^(-i/rotary_dim) divided by a constant factor."""
+
+    def __init__(self, head_dim: int, theta: float, factor: float):
+        self.rotary_dim, self.pairing = head_dim // 2, 0
+        self.theta, self.factor = theta, factor
+        self._cache = {}
+
+    def inverse_frequencies(self, device):
+        if str(device) not in self._cache:
+            f = [1.0 / (self.theta ** (i / self.rotary_dim)) / self.factor for i in range(0, self.rotary_dim, 2)]
+            self._cache[str(device)] = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
+        return self._cache[str(device)]
+
+
+@dataclass(frozen=True)
+class ToyRoutedConfig(LlamaConfig):
+    architecture = "ToyRoutedForCausalLM"
+    n_experts: int = 3
+    rope_factor: float = 4.0
+
+    def layer_specs(self):
+        base = super().layer_specs()[0]
+        pos = PartSpec("test_half_rotary", {"head_dim": self.head_dim, "theta": self.rope_theta, "factor": self.rope_factor})
+        mixer = PartSpec("attention", dict(base.mixer.args, position=pos))
+        ff = PartSpec("test_top1_experts", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
+                                            "n_experts": self.n_experts})
+        return [LayerSpec(mixer, ff, base.mixer_norm, base.feed_forward_norm) for _ in range(self.num_hidden_layers)]
+
+    def tensor_names(self):
+        names = {"embedding.table": "wte", "final_norm.weight": "ln_f", "head.weight": "head"}
+        for i in range(self.num_hidden_layers):
+            p, c = f"layers.{i}.", f"h.{i}."
+            names[p + "mixer_norm.weight"] = c + "ln1"
+            names[p + "feed_forward_norm.weight"] = c + "ln2"
+            for w in ("q", "k", "v", "o"):
+                names[p + f"mixer.{w}"] = c + w
+            names[p + "feed_forward.router"] = c + "router"
+            for k in range(self.n_experts):
+                for w in ("gate", "up", "down"):
+                    names[p + f"feed_forward.{w}{k}"] = c + f"expert{k}.{w}"
+        return names
+
+
+def plain_routed_forward(cfg, w, tokens, n_experts, rope_factor):
+    T = len(tokens)
+    H, KVH, D, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    R = D // 2
+    inv = torch.tensor([1.0 / (cfg["rope_theta"] ** (i / R)) / rope_factor for i in range(0, R, 2)], dtype=torch.float64)
+    cos, sin = P.rope_tables(torch.arange(T), inv, torch.float32)
+
+    def rot(x):   # only the first half of each head turns
+        return torch.cat([P.apply_rope(x[..., :R], cos, sin, "interleaved"), x[..., R:]], dim=-1)
+
+    x = P.embedding(w["wte"], torch.tensor(tokens))
+    for l in range(cfg["num_hidden_layers"]):
+        c = f"h.{l}."
+        xb = P.rmsnorm(x, w[c + "ln1"], eps)
+        q = rot(P.linear(xb, w[c + "q"]).view(T, H, D))
+        k = rot(P.linear(xb, w[c + "k"]).view(T, KVH, D))
+        v = P.linear(xb, w[c + "v"]).view(T, KVH, D)
+        x = x + P.linear(P.causal_attention(q, k, v).reshape(T, H * D), w[c + "o"])
+        xb = P.rmsnorm(x, w[c + "ln2"], eps)
+        probs = torch.softmax(xb @ w[c + "router"].t(), dim=-1)
+        weight, expert = probs.max(dim=-1)
+        y = torch.zeros_like(x)
+        for t in range(T):
+            e = int(expert[t])
+            h = P.swiglu(P.linear(xb[t:t + 1], w[c + f"expert{e}.gate"]), P.linear(xb[t:t + 1], w[c + f"expert{e}.up"]))
+            y[t] = weight[t] * P.linear(h, w[c + f"expert{e}.down"])[0]
+        x = x + y
+    return P.linear(P.rmsnorm(x, w["ln_f"], eps), w["head"])
+
+
+def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
+    """A feed-forward with a router and a position encoding of its own, both defined here, registered and
+    used by a toy architecture: whole prompts and token-by-token decoding against a plain restatement."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+    from gpullama3.java_b200.parts import register_feed_forward, register_position_encoding
+
+    register_feed_forward("test_top1_experts", Top1ExpertsFeedForward)
+    register_position_encoding("test_half_rotary", HalfRotaryLinearScaling)
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+    try:
+        cfg_json = dict(TINY["B"][0], architectures=["ToyRoutedForCausalLM"], num_hidden_layers=2, rope_scaling=None)
+        d = make_model_dir(tmp_path, cfg_json, seed=9, scale={".q": 6.0, ".k": 6.0, "router": 30.0})
+        cfg, w = plain_inputs(d)
+        model = load_model(d, torch.float32)
+        assert not model.graph_safe                       # the routed feed-forward did not promise graph safety
+        cache = model.new_cache(64 * 6)
+        step = StepFunction(model, cache)
+        prompts = [torch.randint(0, 384, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (90, 33)]
+        slots = [cache.acquire() for _ in prompts]
+        heads = [len(p) - 10 for p in prompts]
+        out = step([SequenceInput(s, p[:h], list(range(h))) for s, p, h in zip(slots, prompts, heads)])
+        refs = [plain_routed_forward(cfg, w, p, 3, 4.0) for p in prompts]
+        off = 0
+        for i, h in enumerate(heads):
+            assert_close_logits(out[off:off + h], refs[i][:h], torch.float32, f"routed toy prompt {i}")
+            off += h
+        for t in range(10):
+            o = step([SequenceInput(s, [p[h + t]], [0]) for s, p, h in zip(slots, prompts, heads)])
+            for i, h in enumerate(heads):
+                assert_close_logits(o[i:i + 1], refs[i][h + t:h + t + 1], torch.float32, f"routed toy decode {t}")
+        # bfloat16: the same model steps and gives finite logits close to the float32 ones
+        m16 = load_model(d, torch.bfloat16)
+        c16 = m16.new_cache(64 * 4)
+        s16 = c16.acquire()
+        o16 = StepFunction(m16, c16)([SequenceInput(s16, prompts[1], [len(prompts[1]) - 1])])
+        assert torch.isfinite(o16).all()
+        assert float((o16.cpu() - refs[1][-1:]).abs().max()) < 0.15 * float(refs[1].abs().max())
+    finally:
+        unregister("feed_forward", "test_top1_experts")
+        unregister("position", "test_half_rotary")
+        unregister_architecture("ToyRoutedForCausalLM")
