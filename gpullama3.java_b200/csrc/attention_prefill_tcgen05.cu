@@ -1,4 +1,4 @@
-// Prefill attention on tcgen05 tensor cores (bfloat16, head_dim 64): causal grouped-query attention of
+// Prefill attention on tcgen05 tensor cores (bfloat16, head_dim 64 or 128): causal grouped-query attention of
 // packed prompt tokens over the paged cache, flash style.
 //
 // One CTA owns 128 consecutive query tokens of one sequence and one query head and walks over the keys
@@ -12,24 +12,27 @@
 // tornadovm/TransformerComputeKernelsLayered.java:431-502).  The reference maximum of a row only moves
 // when a block's maximum exceeds it by more than 2^8 (then O and l are rescaled), which is exact and
 // saves most rescaling passes.  Q, K pages and V^T pages arrive by TMA (128-byte swizzle) through a
-// two-stage ring.  Two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
+// two-stage ring.  With head_dim 64 two CTAs fit on an SM, so one CTA's softmax overlaps the other's MMAs.
 //
 // Roles (320 threads): warp 0 lane 0 issues TMA; warp 1 lane 0 issues MMAs (warp 1 owns the 256 TMEM
-// columns: S 128, O 64); warps 2-9 are the softmax (two threads per query row) and the epilogue.  Every mbarrier wait is bounded;
+// columns: S 128, O head_dim); warps 2-9 are the softmax (two threads per query row) and the epilogue.  Every mbarrier wait is bounded;
 // a wait that gives up sets a status word and all roles fall through to the common exit.
 #include "tcgen05.cuh"
 
 namespace b200 {
 
 constexpr int kFaThreads = 320;  // TMA warp, MMA warp, eight softmax warps
-constexpr int kFaRows = 128, kFaKeys = 128, kFaD = 64;
+constexpr int kFaRows = 128, kFaKeys = 128;
 
 __device__ int g_fa_status = 0;
 
+// Operand tiles are stored as "atoms" of 64 elements (128 bytes, one swizzle span) along the contraction:
+// Q and K as D/64 atoms of 128 rows, V^T as one atom of D rows per page, P as two atoms of 128 rows.
+template <int D>
 struct FaSmem {
-    alignas(1024) __nv_bfloat16 q[kFaRows * kFaD];         // 16 KB
-    alignas(1024) __nv_bfloat16 k[2][kFaKeys * kFaD];      // per stage: two pages of 64 keys x 64 dims
-    alignas(1024) __nv_bfloat16 v[2][2][kFaD * 64];        // per stage: two pages of 64 dims x 64 keys (V^T)
+    alignas(1024) __nv_bfloat16 q[kFaRows * D];            // D/64 atoms [128 rows x 64 dims]
+    alignas(1024) __nv_bfloat16 k[2][kFaKeys * D];         // per stage: D/64 atoms [128 keys x 64 dims] (two pages each)
+    alignas(1024) __nv_bfloat16 v[2][2][D * 64];           // per stage and page: [D dims x 64 keys] (V^T as cached)
     alignas(1024) __nv_bfloat16 p[2][kFaRows * 64];        // probabilities: keys 0-63 and 64-127 of the block
     alignas(8) uint64_t q_full;
     uint64_t kv_full[2], kv_empty[2];
@@ -65,7 +68,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(kFaThreads, 2)
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, D == 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
@@ -79,7 +83,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (threadIdx.x == 0) atomicCAS(&g_fa_status, 0, 7 << 8);
         return;
     }
-    FaSmem& sm = *reinterpret_cast<FaSmem*>(smem_raw);
+    FaSmem<D>& sm = *reinterpret_cast<FaSmem<D>*>(smem_raw);
+    constexpr int kAtoms = D / 64;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = blockIdx.z, head = blockIdx.y;
     const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
@@ -115,33 +120,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;  // S: 128 columns, O: D columns
     volatile int* abort_flag = &sm.abort_flag;
 
     if (warp == 0 && lane == 0) {
         // ---- producer: Q once, then per block two K pages and two V^T pages
-        mbar_expect_tx(&sm.q_full, kFaRows * kFaD * 2);
-        tma_load_2d(sm.q, &map_q, head * kFaD, tok0 + q0, &sm.q_full);
+        mbar_expect_tx(&sm.q_full, kFaRows * D * 2);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) tma_load_2d(sm.q + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0, &sm.q_full);
         int it = 0;
         for (int blk = blk_begin; blk < blk_end; ++blk, ++it) {
             const int s = it & 1;
             if (it >= 2 && !mbar_wait(&sm.kv_empty[s], ((it >> 1) - 1) & 1, abort_flag)) {
                 *abort_flag = 1; atomicCAS(&g_fa_status, 0, (1 << 8) | s); break;
             }
-            mbar_expect_tx(&sm.kv_full[s], 2 * (64 * kFaD * 2) + 2 * (kFaD * 64 * 2));
+            mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int lp = blk * 2 + h;  // logical page; pages the sequence does not have are read as zeros
                 const bool have = lp < n_pages_seq;
                 const int page = have ? pages[lp] : 0;
-                tma_load_2d(sm.k[s] + h * 64 * kFaD, &map_k, 0, have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
-                tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * kFaD : v_rows_total, &sm.kv_full[s]);
+#pragma unroll
+                for (int a = 0; a < kAtoms; ++a)  // keys 64 h .. of atom a (dims 64 a ..)
+                    tma_load_2d(sm.k[s] + a * kFaKeys * 64 + h * 64 * 64, &map_k, a * 64,
+                                have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
+                tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer
         constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
-        constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, kFaD);
+        constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, D);
         bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
         if (!ok) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, 2 << 8); }
         int it = 0;
@@ -151,9 +160,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 *abort_flag = 1; atomicCAS(&g_fa_status, 0, (3 << 8) | s); ok = false; break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t qd = umma_desc(sm.q), kd = umma_desc(sm.k[s]);
 #pragma unroll
-            for (int kk = 0; kk < kFaD / 16; ++kk) umma_bf16(tmem_s, qd + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint64_t qd = umma_desc(sm.q + (kk / 4) * kFaRows * 64) + 2 * (kk % 4);
+                const uint64_t kd = umma_desc(sm.k[s] + (kk / 4) * kFaKeys * 64) + 2 * (kk % 4);
+                umma_bf16(tmem_s, qd, kd, idesc_s, kk != 0);
+            }
             umma_commit(&sm.s_full);  // also means: the previous block's P V has finished
             if (!mbar_wait(&sm.p_full, it & 1, abort_flag)) {
                 *abort_flag = 1; atomicCAS(&g_fa_status, 0, 4 << 8); ok = false; break;
@@ -176,7 +188,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos = start + q0 + min(r, rows_here - 1);  // rows past the end mirror the last one (never stored)
-        const float scale_log2 = 1.4426950408889634f / sqrtf((float)kFaD);
+        const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);
         float m_ref = -INFINITY, l = 0.f;  // reference maximum (units of q.k); this thread's share of the running sum
         bool ok = true;
         int it = 0;
@@ -215,12 +227,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const float m_new = move ? m_blk : m_ref;
                 const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
                 l *= corr;
-                if (it > 0) {  // O holds earlier blocks: rescale this row's 32 dims (whole warps take part in the TMEM access)
-                    float o[32];
-                    tmem_ld32(tmem_o + lane_base + half * 32, o);
+                if (it > 0) {  // O holds earlier blocks: rescale this row's half of the dims (whole warps take part)
+#pragma unroll 1
+                    for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_base + c0, o);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] *= corr;
-                    tmem_st32(tmem_o + lane_base + half * 32, o);
+                        for (int j = 0; j < 32; ++j) o[j] *= corr;
+                        tmem_st32(tmem_o + lane_base + c0, o);
+                    }
                 }
                 m_ref = m_new;
             }
@@ -275,19 +290,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv_l = 1.0f / sm.row_sum[r];
-            __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + r) * n_heads + head) * kFaD + half * 32;
-            float o[32];
-            tmem_ld32(tmem_o + lane_base + half * 32, o);
-            if (r < rows_here) {
+            __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + r) * n_heads + head) * D;
+#pragma unroll 1
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 32) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_base + c0, o);
+                if (r < rows_here) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * j] * inv_l, o[8 * j + 1] * inv_l);
-                    __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * j + 2] * inv_l, o[8 * j + 3] * inv_l);
-                    __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * j + 4] * inv_l, o[8 * j + 5] * inv_l);
-                    __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * j + 6] * inv_l, o[8 * j + 7] * inv_l);
-                    *reinterpret_cast<uint4*>(orow + 8 * j) =
-                        make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
-                                   *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                    for (int j = 0; j < 4; ++j) {
+                        __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * j] * inv_l, o[8 * j + 1] * inv_l);
+                        __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * j + 2] * inv_l, o[8 * j + 3] * inv_l);
+                        __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * j + 4] * inv_l, o[8 * j + 5] * inv_l);
+                        __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * j + 6] * inv_l, o[8 * j + 7] * inv_l);
+                        *reinterpret_cast<uint4*>(orow + c0 + 8 * j) =
+                            make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
+                                       *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                    }
                 }
             }
         }
@@ -322,8 +340,30 @@ extern "C" int b200_attention_prefill_tc_status() {
     return v;
 }
 
-// q: packed rows of q_row_stride elements whose first n_heads * 64 are the rotated queries (n_rows of them);
-// k_pool [n_pages][n_kv_heads][64][64], v_pool [n_pages][n_kv_heads][64][64] (values transposed).
+namespace b200 {
+template <int D>
+static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* cu_seqlens,
+                     const int* kv_lens, const int* page_table, int table_stride, int n_seqs, int max_q_len, int n_heads,
+                     int n_kv_heads, int window, int k_rows, int v_rows, cudaStream_t stream) {
+    static_assert(D != 64 || sizeof(FaSmem<64>) <= 113 * 1024, "two CTAs per SM need at most 113 KB each");
+    const size_t smem = sizeof(FaSmem<D>);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_heads, n_seqs);
+    attention_prefill_tc_kernel<D><<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
+                                                                      page_table, table_stride, n_heads, n_kv_heads, window,
+                                                                      k_rows, v_rows);
+    return launch_status();
+}
+}  // namespace b200
+
+// q: packed rows of q_row_stride elements whose first n_heads * head_dim are the rotated queries (n_rows of them);
+// k_pool [n_pages][n_kv_heads][64][head_dim], v_pool [n_pages][n_kv_heads][head_dim][64] (values transposed).
+// head_dim 64 or 128.
 extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_rows, void* out, const int* cu_seqlens,
                                          const int* kv_lens, const int* page_table, int table_stride,
                                          const void* k_pool, const void* v_pool, int n_pages, int n_seqs, int max_q_len,
@@ -331,26 +371,19 @@ extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_
     using namespace b200;
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return kErrBadArgument;
-    if (head_dim != kFaD || q_row_stride % 8 != 0 || (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15))
+    if ((head_dim != 64 && head_dim != 128) || q_row_stride % 8 != 0 ||
+        (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15))
         return kErrUnsupportedSize;
     if (n_seqs > 65535 || n_heads > 65535) return kErrUnsupportedSize;
-    const long long k_rows = (long long)n_pages * n_kv_heads * 64, v_rows = (long long)n_pages * n_kv_heads * kFaD;
+    const long long k_rows = (long long)n_pages * n_kv_heads * 64, v_rows = (long long)n_pages * n_kv_heads * head_dim;
     if (k_rows >= (1ll << 31) || v_rows >= (1ll << 31)) return kErrUnsupportedSize;
     CUtensorMap mq, mk, mv;
-    if (!make_map_2d(&mq, q, n_rows, n_heads * kFaD, q_row_stride, kFaD, kFaRows) ||
-        !make_map_2d(&mk, k_pool, k_rows, kFaD, kFaD, kFaD, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, kFaD))
+    if (!make_map_2d(&mq, q, n_rows, n_heads * head_dim, q_row_stride, 64, kFaRows) ||
+        !make_map_2d(&mk, k_pool, k_rows, head_dim, head_dim, 64, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, head_dim))
         return kErrUnsupportedSize;
-    const size_t smem = sizeof(FaSmem);
-    static_assert(sizeof(FaSmem) <= 113 * 1024, "two CTAs per SM need at most 113 KB each");
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return (int)cudaGetLastError();
-        configured = true;
-    }
-    dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_heads, n_seqs);
-    attention_prefill_tc_kernel<<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
-                                                                   page_table, table_stride, n_heads, n_kv_heads, window,
-                                                                   (int)k_rows, (int)v_rows);
-    return launch_status();
+    if (head_dim == 64)
+        return launch_fa<64>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
+                             n_kv_heads, window, (int)k_rows, (int)v_rows, stream);
+    return launch_fa<128>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
+                          n_kv_heads, window, (int)k_rows, (int)v_rows, stream);
 }

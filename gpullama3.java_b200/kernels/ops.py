@@ -354,9 +354,9 @@ def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_
 def attention_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,
                          kv_lens: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                          n_seqs: int, max_q_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int) -> bool:
-    """``attention_prefill`` on tcgen05 tensor cores (head_dim 64).  Returns False, having done nothing,
-    for sizes it does not take."""
-    if head_dim != 64 or q.dtype != torch.bfloat16 or q_row_stride % 8 or (q.data_ptr() | out.data_ptr()) & 15:
+    """``attention_prefill`` on tcgen05 tensor cores (head_dim 64 or 128).  Returns False, having done
+    nothing, for sizes it does not take."""
+    if head_dim not in (64, 128) or q.dtype != torch.bfloat16 or q_row_stride % 8 or (q.data_ptr() | out.data_ptr()) & 15:
         return False
     _dev(q, out, cu_seqlens, kv_lens, page_table, k_pool, v_pool)
     assert out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous() and k_pool.is_contiguous()

@@ -364,11 +364,11 @@ def test_attention_decode_with_fused_rotation_and_cache_write(H, KVH, D, pairing
     torch.testing.assert_close(got2.float(), want.float(), rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("H, KVH, window", [(8, 2, 0), (4, 4, 0), (3, 1, 0), (4, 1, 37), (2, 1, 200), (2, 2, 129)])
-def test_attention_prefill_on_tcgen05_against_plain(H, KVH, window):
-    """The tensor-memory flash kernel (head size 64): whole prompts across several 128-row tiles and 128-key
-    blocks, chunks that continue a cached prefix, single tokens, windows; every wait inside must complete."""
-    D = 64
+def test_attention_prefill_on_tcgen05_against_plain(H, KVH, window, D):
+    """The tensor-memory flash kernel (head sizes 64 and 128): whole prompts across several 128-row tiles and
+    128-key blocks, chunks that continue a cached prefix, single tokens, windows; every wait inside must complete."""
     kv_lens = [1, 64, 65, 300, 129, 517, 40, 128, 700]
     q_starts = [0, 0, 64, 101, 100, 0, 39, 0, 256]
     k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=60, seed=H + KVH)
