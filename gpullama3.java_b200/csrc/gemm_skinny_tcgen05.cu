@@ -36,21 +36,6 @@ struct SkinnySmem {
     int abort_flag;
 };
 
-__device__ __forceinline__ void cluster_barrier() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address, in the cluster's shared window, of `local` as it sits in the CTA of rank `rank`.
-__device__ __forceinline__ uint32_t peer_shared_address(const void* local, uint32_t rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    return remote;
-}
-__device__ __forceinline__ float ld_cluster_shared(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
-}
-
 template <int EPI, typename TC>
 __device__ __forceinline__ void skinny_emit(TC* __restrict__ C, int ldc, int token, int n, int N, float v, int lane) {
     if (EPI == 2) {
@@ -175,22 +160,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     if (k_splits > 1) {
         __syncthreads();    // the role branches have joined again: whole warps reach the cluster barrier
-        cluster_barrier();  // every span's partial tile is in its CTA's shared memory
+        cluster_sync_all();  // every span's partial tile is in its CTA's shared memory
         if (warp >= 2) {
             const int quarter = warp & 3;
             const int r = quarter * 32 + lane, n = n0 + r;
             uint32_t peer[8];  // this thread's row of the partial tile in every span's CTA
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp)
-                peer[sp] = peer_shared_address(reinterpret_cast<const float*>(sm.w) + r, sp < k_splits ? sp : 0);
+                peer[sp] = cluster_peer_address(reinterpret_cast<const float*>(sm.w) + r, sp < k_splits ? sp : 0);
             // this CTA's share of the tokens, two at a time so that up to 16 remote loads are in flight
             for (int token = split; token < M; token += 2 * k_splits) {
                 const int token2 = token + k_splits;
                 float v0[8], v1[8];
 #pragma unroll
                 for (int sp = 0; sp < 8; ++sp) {
-                    v0[sp] = sp < k_splits ? ld_cluster_shared(peer[sp] + (uint32_t)token * kRowsPerTile * 4) : 0.f;
-                    v1[sp] = (sp < k_splits && token2 < M) ? ld_cluster_shared(peer[sp] + (uint32_t)token2 * kRowsPerTile * 4) : 0.f;
+                    v0[sp] = sp < k_splits ? cluster_load_f32(peer[sp] + (uint32_t)token * kRowsPerTile * 4) : 0.f;
+                    v1[sp] = (sp < k_splits && token2 < M) ? cluster_load_f32(peer[sp] + (uint32_t)token2 * kRowsPerTile * 4) : 0.f;
                 }
                 float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -199,7 +184,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 if (token2 < M) skinny_emit<EPI, TC>(C, ldc, token2, n, N, s1, lane);
             }
         }
-        cluster_barrier();  // no CTA leaves while a peer may still read its shared memory
+        cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
     }
     __syncthreads();
     if (warp == 1) {

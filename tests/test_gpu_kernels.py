@@ -276,7 +276,7 @@ def test_gemm_skinny_and_its_epilogues(M, N, K, splits):
 
 @pytest.mark.parametrize("H, KVH, D, window", [(4, 2, 32, 0), (32, 8, 64, 0), (3, 1, 96, 0), (16, 1, 128, 0),
                                                (8, 8, 64, 0), (24, 2, 32, 0), (8, 2, 64, 100), (4, 1, 128, 33)])
-@pytest.mark.parametrize("n_splits", [1, 3, 16])
+@pytest.mark.parametrize("n_splits", [1, 2, 3, 8, 16])
 def test_attention_decode_against_plain(H, KVH, D, window, n_splits):
     kv_lens = [1, 31, 32, 33, 64, 65, 300, 517]
     k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=40, seed=D + H)
@@ -326,7 +326,7 @@ def test_attention_prefill_against_plain(H, KVH, D, window):
 @pytest.mark.parametrize("H, KVH, D, pairing, window", [(8, 2, 64, "half", 0), (32, 8, 64, "half", 0), (4, 1, 128, "half", 70),
                                                         (6, 3, 32, "interleaved", 0), (3, 1, 96, "interleaved", 0),
                                                         (16, 1, 128, "interleaved", 0)])
-@pytest.mark.parametrize("n_splits", [1, 4])
+@pytest.mark.parametrize("n_splits", [1, 4, 16])
 def test_attention_decode_with_fused_rotation_and_cache_write(H, KVH, D, pairing, window, n_splits):
     """One kernel that rotates the step's queries, stores its key and value and attends must give what
     the rotation kernel followed by the attention kernel give: the same cache, the same output."""
