@@ -375,7 +375,7 @@ namespace b200 {
 static int launch_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens, const int* page_table,
                                    int table_stride, void* k_pool, void* v_pool, float* scratch, long long scratch_floats,
                                    int n_seqs, int n_heads, int n_kv_heads, int head_dim, int window, int n_splits,
-                                   bool fused, RopeArgs rope, cudaStream_t stream) {
+                                   bool fused, RopeArgs rope, bool early_start, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_splits < 1) return kErrBadArgument;
     const int group = n_heads / n_kv_heads;
@@ -405,8 +405,9 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
                 configured = true;                                                                                  \
             }                                                                                                       \
         }                                                                                                           \
-        st = launch_pdl(kernel, grid, dim3(kAttnDecodeThreads), smem, stream, qq, q_row_stride, oo, kv_lens, page_table, \
-                        table_stride, kk, vv, part_o, part_ml, n_heads, n_kv_heads, window, n_splits, rope);         \
+        st = launch_pdl_cluster(kernel, grid, dim3(kAttnDecodeThreads), smem, stream, dim3(1, 1, 1), early_start, qq,   \
+                                q_row_stride, oo, kv_lens, page_table, table_stride, kk, vv, part_o, part_ml, n_heads,  \
+                                n_kv_heads, window, n_splits, rope);                                                 \
     } while (0)
 #define B200_PICK(KB) do { if (fused) B200_LAUNCH(KB, true); else B200_LAUNCH(KB, false); } while (0)
     switch (head_dim / 32) {
@@ -424,14 +425,15 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
 
 }  // namespace b200
 
-// Queries already rotated, keys and values of the step already in the cache.
+// Queries already rotated, keys and values of the step already in the cache.  early_start: whether the kernel
+// may be scheduled while its predecessor on the stream still runs (0 for a long kernel that fills the GPU).
 extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens,
                                      const int* page_table, int table_stride, const void* k_pool, const void* v_pool,
                                      float* scratch, long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads,
-                                     int head_dim, int window, int n_splits, cudaStream_t stream) {
+                                     int head_dim, int window, int n_splits, int early_start, cudaStream_t stream) {
     return b200::launch_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, const_cast<void*>(k_pool),
                                          const_cast<void*>(v_pool), scratch, scratch_floats, n_seqs, n_heads, n_kv_heads,
-                                         head_dim, window, n_splits, false, b200::RopeArgs{nullptr, 0, 0}, stream);
+                                         head_dim, window, n_splits, false, b200::RopeArgs{nullptr, 0, 0}, early_start != 0, stream);
 }
 
 // The fused variant: `qkv` holds the step's raw projections [n_seqs, (n_heads + 2 n_kv_heads) head_dim]; queries
@@ -441,10 +443,10 @@ extern "C" int b200_attention_decode_rope(const void* qkv, int q_row_stride, voi
                                           const int* page_table, int table_stride, void* k_pool, void* v_pool,
                                           float* scratch, long long scratch_floats, int n_seqs, int n_heads,
                                           int n_kv_heads, int head_dim, int window, int n_splits, const float* inv_freq,
-                                          int pairing, int write_cache, cudaStream_t stream) {
+                                          int pairing, int write_cache, int early_start, cudaStream_t stream) {
     return b200::launch_attention_decode(qkv, q_row_stride, out, kv_lens, page_table, table_stride, k_pool, v_pool, scratch,
                                          scratch_floats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, true,
-                                         b200::RopeArgs{inv_freq, pairing, write_cache}, stream);
+                                         b200::RopeArgs{inv_freq, pairing, write_cache}, early_start != 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -484,5 +486,5 @@ extern "C" int b200_attention_decode_static(const void* q, int q_row_stride, voi
         g_static_scratch_address[device] = scratch;
     }
     return b200_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, k_pool, v_pool, scratch,
-                                 kStaticScratchFloats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, stream);
+                                 kStaticScratchFloats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, 1, stream);
 }

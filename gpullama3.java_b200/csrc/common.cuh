@@ -91,10 +91,13 @@ inline bool pdl_enabled() {
     return on == 1;
 }
 
-// The same, with the CTAs grouped into thread-block clusters of `cluster` (1, 1, 1: no clusters).
+// The general form: CTAs grouped into thread-block clusters of `cluster` (1, 1, 1: no clusters), and
+// `early_start` false for a kernel that should find the GPU empty.  A long kernel whose grid just fills the
+// SMs is such a kernel: started early, its CTAs settle wherever the predecessor's CTAs leave room, unevenly, and
+// the SMs that got more of them finish late.
 template <typename... KArgs, typename... Args>
 inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              dim3 cluster, Args... args) {
+                              dim3 cluster, bool early_start, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -109,7 +112,7 @@ inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
         attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
-    if (pdl_enabled()) {
+    if (pdl_enabled() && early_start) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
@@ -121,7 +124,7 @@ inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    return launch_pdl_cluster(kernel, grid, block, smem, stream, dim3(1, 1, 1), args...);
+    return launch_pdl_cluster(kernel, grid, block, smem, stream, dim3(1, 1, 1), true, args...);
 }
 
 // Thread-block clusters: barrier over all threads of the cluster, and reads of a peer CTA's shared memory.

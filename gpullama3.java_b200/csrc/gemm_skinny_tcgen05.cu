@@ -3,8 +3,9 @@
 // With so few tokens the product is a stream of W from HBM, so the roles of the operands are
 // swapped against the prefill kernel: 128 weight rows are the M side of the tensor-core tile and
 // the tokens are its N side (BT = 32, 64 or 128 columns of tensor memory).  TMA brings a
-// 128 x 64 slice of W and a BT x 64 slice of A per stage through a deep ring (24 KB per stage,
-// 8 stages in flight), one thread issues tcgen05.mma, four warps read the accumulator back.
+// 128 x 64 slice of W and a BT x 64 slice of A per stage through a ring (24 KB per stage at 64 tokens;
+// 8 stages and one CTA per SM, or 4 stages and two), one thread issues tcgen05.mma, four warps read
+// the accumulator back.
 // (The reference does these products one output row per work-group,
 // tornadovm/TransformerComputeKernelsLayered.java:901-930 of the reference project.)
 //
@@ -49,7 +50,7 @@ __device__ __forceinline__ void skinny_emit(TC* __restrict__ C, int ldc, int tok
 }
 
 template <int BT, int STAGES, int EPI, typename TC>
-__global__ void __launch_bounds__(kSkinnyThreads, 1)
+__global__ void __launch_bounds__(kSkinnyThreads, STAGES <= 4 ? 2 : 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                    TC* __restrict__ C, int ldc, int M, int N, int K, int blocks_per_split) {
     extern __shared__ uint8_t smem_raw[];
@@ -103,6 +104,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // ---- MMA issuer: 128 weight rows x BT tokens
         constexpr uint32_t idesc = umma_idesc_bf16(kRowsPerTile, BT);
         bool ok = true;
+        pdl_wait();  // no stage can fill before the predecessor has ended (A comes from it): sleep, do not poll
+
         for (int it = 0; it < k_iters; ++it) {
             const int s = it % STAGES;
             if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
@@ -142,13 +145,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0.f;
                 }
-                if (k_splits == 1) {
+                if (k_splits == 1 && EPI == 2) {
+                    // lanes 2i, 2i+1 hold a gate row and its up row: one exchange per token pair gives the even
+                    // lane the up value of the even token and the odd lane the gate value of the odd token
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float got = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[j + 1], 1);
+                        const float gate = odd ? got : v[j], up = odd ? v[j + 1] : got;
+                        const int token = c0 + j + (odd ? 1 : 0);
+                        if (token < M && (n | 1) < N)
+                            C[(size_t)token * ldc + (n >> 1)] = from_f32<TC>(gate * __frcp_rn(1.0f + __expf(-gate)) * up);
+                    }
+                } else if (k_splits == 1) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < M) skinny_emit<EPI, TC>(C, ldc, c0 + j, n, N, v[j], lane);
                 } else {
                     // the stage buffers are free once the accumulator is complete: the partial tile
-                    // [token][row] goes where the first stages of W were
+                    // [token][row] goes where the first stages of W were (and, with a shallow ring and
+                    // 128 tokens, on into the stages of A, which follow W without a gap)
+                    using Smem = SkinnySmem<BT, STAGES>;
+                    static_assert(offsetof(Smem, a) == sizeof(sm.w), "A follows W");
+                    static_assert((size_t)BT * kRowsPerTile * 4 <= sizeof(sm.w) + sizeof(sm.a), "partial tile fits");
                     float* p = reinterpret_cast<float*>(sm.w) + (size_t)c0 * kRowsPerTile + r;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -239,6 +258,17 @@ static int dispatch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, void* C
 
 static int token_tile(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
+static int sm_count() {  // of the current device
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cached[dev];
+}
+
 }  // namespace b200
 
 extern "C" int b200_gemm_skinny_status() {
@@ -254,11 +284,13 @@ extern "C" int b200_gemm_skinny_splits(int M, int N, int K, int n_sms) {
     if (M <= 0 || N <= 0 || K < 8) return 1;
     const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
     const int kb = (K + BK - 1) / BK;
-    // Measured on B200: clusters of 4 spans beat 8 (the reduction and the cluster's placement cost more
-    // than the extra CTAs win), and a span needs a few stages of work to amortise its start-up.
+    // Measured on B200 (two CTAs of the shallow ring per SM): narrow outputs want as many spans as keep the
+    // grid within two CTAs per SM, up to 8, each span with at least 4 stages of work; an output that fills
+    // half the SMs with its tiles alone is not cut.
     int splits = 1;
-    if (tiles * 4 <= n_sms && kb >= 16) splits = 4;
-    else if (tiles * 2 <= n_sms && kb >= 8) splits = 2;
+    if (tiles * 2 <= n_sms)
+        for (int s = 8; s >= 2; s /= 2)
+            if (tiles * s <= 2 * n_sms && kb >= 4 * s) { splits = s; break; }
     const int bps = (kb + splits - 1) / splits;
     return (kb + bps - 1) / bps;                 // no empty span
 }
@@ -277,7 +309,20 @@ extern "C" int b200_gemm_skinny(const void* A, int lda, const void* W, int ldw, 
     const int bt = token_tile(M);
     CUtensorMap mw, ma;
     if (!make_map(&mw, W, N, K, ldw, kRowsPerTile) || !make_map(&ma, A, M, K, lda, bt)) return kErrUnsupportedSize;
-    if (bt == 32) return dispatch_skinny<32, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
-    if (bt == 64) return dispatch_skinny<64, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+    // Two ring depths.  Deep (one CTA per SM, 8 stages): a grid of one wave without K spans, where a second
+    // resident CTA would have nothing to do.  Shallow (half the stages, two CTAs per SM): every other grid;
+    // clusters of spans fill the SMs twice over, and in a grid of many waves one CTA's start-up and epilogue
+    // hide behind its neighbour's stream.
+    const int tiles = (N + kRowsPerTile - 1) / kRowsPerTile;
+    const bool shallow = k_splits > 1 || tiles > sm_count();
+    if (bt == 32) {
+        if (shallow) return dispatch_skinny<32, 4>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+        return dispatch_skinny<32, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+    }
+    if (bt == 64) {
+        if (shallow) return dispatch_skinny<64, 4>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+        return dispatch_skinny<64, 8>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
+    }
+    if (shallow) return dispatch_skinny<128, 3>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
     return dispatch_skinny<128, 6>(mw, ma, C, c_dtype, ldc, M, N, K, epilogue, k_splits, bps, stream);
 }

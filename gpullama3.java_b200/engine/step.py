@@ -104,7 +104,8 @@ class DecodeGraph:
         self.logits: torch.Tensor | None = None
         self.n_launches = 0
         kv_heads = [g.need.n_kv_heads for g in cache.kv_groups] or [1]
-        self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), max(widths, default=1) * PAGE_TOKENS)
+        self.kv_capacity = max(widths, default=1) * PAGE_TOKENS
+        self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), self.kv_capacity)
 
     def refresh(self, slots, start_pos, tokens) -> None:
         pieces, _, _ = _pack(self.cache, slots, start_pos, [[t] for t in tokens], list(range(self.n)), self.widths)
@@ -118,6 +119,7 @@ class DecodeGraph:
         ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, slots,
                                   start_pos, [1] * self.n)
         ctx.extras["decode_splits"] = self.splits
+        ctx.extras["decode_kv_capacity"] = self.kv_capacity
         return self.model.forward(ctx, self.cache, rows)
 
     def run(self, slots, start_pos, tokens) -> torch.Tensor:

@@ -47,12 +47,12 @@ _SIGNATURES = {
                                                  c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                    c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_int,
-                                                   c_int, c_int]),
+                                                   c_int, c_int, c_int]),
     "b200_attention_prefill": ("attention_prefill", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_attention_decode_rope": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                         c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int,
-                                                        c_int, c_int, c_int, c_void_p, c_int, c_int]),
+                                                        c_int, c_int, c_int, c_void_p, c_int, c_int, c_int]),
     "b200_attention_prefill_tc": ("attention_prefill_tcgen05", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                                 c_int, c_int, c_int, c_int]),
@@ -72,7 +72,14 @@ def _fn(name: str):
             raise KernelBuildError(f"{name} is not exported by the {lib_name} kernel library") from e
         f.argtypes = list(argtypes) + [c_void_p]
         f.restype = c_int
-        _functions[name] = f
+        n_args = len(f.argtypes)
+
+        def checked(*args, _f=f, _n=n_args, _name=name):
+            if len(args) != _n:  # ctypes lets extra arguments through, which shifts the stream pointer
+                raise TypeError(f"{_name} takes {_n} arguments, got {len(args)}")
+            return _f(*args)
+
+        f = _functions[name] = checked
     return f
 
 
@@ -286,6 +293,15 @@ def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resid
     return p
 
 
+def attention_decode_early_start(n_seqs: int, n_kv_heads: int, max_kv_len: int, n_splits: int) -> bool:
+    """Whether the decode attention may be scheduled while the kernel before it still runs.  A grid
+    that fills the GPU with long spans (48 blocks of 32 keys or more) should find it empty instead:
+    started early, its CTAs settle unevenly among the predecessor's and the fullest SMs finish late
+    (batch 64 at 4,096 keys: 203 against 142 us per layer)."""
+    blocks_per_span = (max_kv_len + 31) // 32 // max(1, n_splits)
+    return not (n_seqs * n_kv_heads * n_splits >= 256 and blocks_per_span >= 48)
+
+
 def attention_decode_rope_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
                                     pairing: int) -> bool:
     """Whether the decode kernel can also do the step's rotation and cache write."""
@@ -296,7 +312,8 @@ def attention_decode_rope_supported(dtype: torch.dtype, n_heads: int, n_kv_heads
 def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, kv_lens: torch.Tensor, page_table: torch.Tensor,
                           k_pool: torch.Tensor, v_pool: torch.Tensor, inv_freq: torch.Tensor, n_heads: int,
                           n_kv_heads: int, head_dim: int, pairing: int, window: int, n_splits: int,
-                          write_cache: bool = True, scratch: torch.Tensor | None = None) -> None:
+                          write_cache: bool = True, scratch: torch.Tensor | None = None,
+                          early_start: bool = True) -> None:
     """Decode attention that rotates the step's queries itself and, with ``write_cache``, stores the
     step's rotated key and its value at position kv_lens[i] - 1 of sequence i.  ``qkv``: the raw
     projections [n_seqs, (n_heads + 2 n_kv_heads) head_dim] (left untouched)."""
@@ -313,15 +330,16 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, kv_lens: torch.T
         qkv.data_ptr(), qkv.shape[1], out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
         n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, inv_freq.data_ptr(), pairing,
-        1 if write_cache else 0, _stream()), "attention_decode_rope")
+        1 if write_cache else 0, 1 if early_start else 0, _stream()), "attention_decode_rope")
 
 
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,
                      page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, n_heads: int,
                      n_kv_heads: int, head_dim: int, window: int, n_splits: int,
-                     scratch: torch.Tensor | None = None) -> None:
+                     scratch: torch.Tensor | None = None, early_start: bool = True) -> None:
     """One query token per sequence (row i of q belongs to sequence i) over kv_lens[i] cached keys.
-    ``scratch``: float32 workspace for the spans' partial results (allocated here when absent)."""
+    ``scratch``: float32 workspace for the spans' partial results (allocated here when absent).
+    ``early_start``: see ``attention_decode_early_start``."""
     _dev(q, out, kv_lens, page_table, k_pool, v_pool)
     n_seqs = out.shape[0]
     assert q.dtype == out.dtype == k_pool.dtype == torch.bfloat16 and out.is_contiguous()
@@ -333,7 +351,8 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_l
     _check(_fn("b200_attention_decode")(
         q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
-        n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, _stream()), "attention_decode")
+        n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, 1 if early_start else 0, _stream()),
+        "attention_decode")
 
 
 def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,
