@@ -318,6 +318,349 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The pair kernel (head_dim 64, no window): one CTA owns 256 consecutive query tokens as two tiles of 128
+// and keeps both in flight.  Each tile has its own S and O in tensor memory and its own warpgroup of
+// softmax threads, ONE thread per query row: the thread reads its row of S (128 scores) into registers in
+// one go, so the maximum, the exponentials and the sum need no exchange between threads and no second
+// read.  While the softmax of one tile runs, the tensor cores form the other tile's scores and outputs
+// (order of issue: S0 S1 | PV0 S0' | PV1 S1' | ...), and every K and V block that is loaded serves both
+// tiles.  The grid is one CTA per SM; each takes (pair, head, sequence) units from a counter, longest first.  The probabilities never touch shared memory: the thread writes its row of P as bfloat16 pairs into
+// tensor memory and O += P V takes its A operand from there.  One CTA per SM (tensor memory, 512 columns:
+// 2 x 128 of S, 2 x 64 of O, 2 x 64 of P; shared memory: Q 32 KB, three stages of K and V 96 KB).
+constexpr int kPairStages = 3;
+
+template <int D>
+struct PairSmem {
+    alignas(1024) __nv_bfloat16 q[2][kFaRows * D];
+    alignas(1024) __nv_bfloat16 k[kPairStages][kFaKeys * D];
+    alignas(1024) __nv_bfloat16 v[kPairStages][2][D * 64];
+    alignas(8) uint64_t q_full;
+    uint64_t kv_full[kPairStages], kv_empty[kPairStages];
+    uint64_t s_full[2], p_full[2], o_full[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int unit;  // the unit of work the CTA is on
+};
+
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+// Completes the loads issued before it; the registers are operands so that no use of them can move above it.
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tie32(uint32_t (&r)[32]) {
+    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                      "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                      "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                      "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
+
+// 16 registers (32 bfloat16) of this thread's row into 16 consecutive columns of tensor memory
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] B[smem]: A's row i lies in lane i, its K elements as bfloat16 pairs along the columns
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, int accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ unsigned int g_pair_next_unit;  // work counter of the launch in flight (zeroed on the stream before it)
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                              const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
+                              const int* __restrict__ page_table, int table_stride, int n_heads, int n_kv_heads,
+                              int k_rows_total, int v_rows_total, int n_seqs, int n_pairs) {
+    static_assert(D == 64, "the pair kernel is laid out for head_dim 64");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    PairSmem<D>& sm = *reinterpret_cast<PairSmem<D>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < kPairStages; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 1); }
+        for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_full[t], 4); mbar_init(&sm.o_full[t], 1); }
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;  // tile t: S in columns 128 t, O in 256 + 64 t, P (bfloat16 pairs) in 384 + 64 t
+    volatile int* abort_flag = &sm.abort_flag;
+
+    // The CTA stays and takes one unit of work after another from a counter: a unit is (pair of tiles, head,
+    // sequence), the pairs with the most keys first, so that the SMs finish together.  The barriers are never
+    // set up again: every role counts the phases each barrier has been through (the same numbers everywhere,
+    // they follow from the units alone).
+    const int total_units = n_pairs * n_heads * n_seqs;
+    int units_done = 0;            // phases of q_full
+    int kv_base = 0;               // K/V blocks of earlier units: block g uses stage g % stages, phase g / stages
+    int tile_blocks[2] = {0, 0};   // phases of s_full[t] and p_full[t]
+    int tile_units[2] = {0, 0};    // phases of o_full[t]
+    int kv_ready = 0;  // MMA thread: blocks (counted over all units) whose K and V are known to have landed
+
+    for (;;) {
+        __syncthreads();  // the unit before is finished everywhere: tensor memory, Q and the unit number are free
+        if (threadIdx.x == 0) sm.unit = (int)atomicAdd(&g_pair_next_unit, 1u);
+        __syncthreads();
+        const int unit = sm.unit;
+        if (unit >= total_units || *abort_flag) break;
+        const int pair = n_pairs - 1 - unit / (n_heads * n_seqs);
+        const int seq = (unit % (n_heads * n_seqs)) / n_heads, head = unit % n_heads;
+        const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
+        const int q0 = pair * 2 * kFaRows;
+        if (q0 >= q_len) continue;  // this sequence has no such rows
+        const int kvh = head / (n_heads / n_kv_heads);
+        const int kv_len = kv_lens[seq], start = kv_len - q_len;
+        // tile t: rows q0 + 128 t .. ; its key blocks are 0 .. nb[t] - 1 (causal), nb[1] = 0 when the tile has no rows
+        const int rows0 = min(kFaRows, q_len - q0), rows1 = max(0, min(kFaRows, q_len - q0 - kFaRows));
+        const int nb0 = (start + q0 + rows0 - 1) / kFaKeys + 1;
+        const int nb1 = rows1 > 0 ? (start + q0 + kFaRows + rows1 - 1) / kFaKeys + 1 : 0;
+        const int nb = max(nb0, nb1);
+
+        if (warp == 0 && lane == 0) {
+            // ---- producer: both Q tiles, then per block two K pages and two V^T pages
+            const int* pages = page_table + (size_t)seq * table_stride;
+            const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
+            mbar_expect_tx(&sm.q_full, (rows1 > 0 ? 2 : 1) * kFaRows * D * 2);
+            tma_load_2d(sm.q[0], &map_q, head * D, tok0 + q0, &sm.q_full);
+            if (rows1 > 0) tma_load_2d(sm.q[1], &map_q, head * D, tok0 + q0 + kFaRows, &sm.q_full);
+            for (int j = 0; j < nb; ++j) {
+                const int g = kv_base + j, s = g % kPairStages;
+                if (g >= kPairStages && !mbar_wait(&sm.kv_empty[s], ((g / kPairStages) - 1) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_fa_status, 0, (11 << 8) | s); break;
+                }
+                mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int lp = j * 2 + h;  // logical page; pages the sequence does not have are read as zeros
+                    const bool have = lp < n_pages_seq;
+                    const int page = have ? pages[lp] : 0;
+                    tma_load_2d(sm.k[s] + h * 64 * 64, &map_k, 0, have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
+                    tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
+            constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, D);
+            // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
+            uint64_t q_desc[2], k_desc[kPairStages], v_desc[kPairStages][2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) q_desc[t] = umma_desc(sm.q[t]);
+#pragma unroll
+            for (int s = 0; s < kPairStages; ++s) {
+                k_desc[s] = umma_desc(sm.k[s]);
+                v_desc[s][0] = umma_desc(sm.v[s][0]);
+                v_desc[s][1] = umma_desc(sm.v[s][1]);
+            }
+            bool ok = mbar_wait(&sm.q_full, units_done & 1, abort_flag);
+            if (!ok) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, 12 << 8); }
+            auto need_block = [&](int j) {
+                while (ok && kv_ready <= kv_base + j) {
+                    const int s = kv_ready % kPairStages;
+                    if (!mbar_wait(&sm.kv_full[s], (kv_ready / kPairStages) & 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (13 << 8) | s); ok = false;
+                    } else {
+                        ++kv_ready;
+                    }
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            };
+            auto scores = [&](int t, int j) {  // S_t = Q_t K_j^T
+                const uint64_t qd = q_desc[t], kd = k_desc[(kv_base + j) % kPairStages];
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 128 * t, qd + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
+                umma_commit(&sm.s_full[t]);  // also means: this tile's earlier P V products have finished
+            };
+            auto outputs = [&](int t, int j) {  // O_t += P_t V_j
+                const int s = (kv_base + j) % kPairStages;
+#pragma unroll
+                for (int kk = 0; kk < kFaKeys / 16; ++kk)  // 16 keys = 8 columns of P
+                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + 384 + 64 * t + 8 * kk, v_desc[s][kk / 4] + 2 * (kk % 4),
+                                     idesc_o, (j | kk) != 0);
+            };
+            if (ok) {
+                need_block(0);
+                if (ok) { scores(0, 0); if (nb1 > 0) scores(1, 0); }
+            }
+            for (int j = 0; j < nb && ok; ++j) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const int nbt = t == 0 ? nb0 : nb1;
+                    if (j >= nbt || !ok) continue;
+                    if (!mbar_wait(&sm.p_full[t], (tile_blocks[t] + j) & 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; continue;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    outputs(t, j);
+                    if (j + 1 < nbt) {
+                        need_block(j + 1);
+                        if (ok) scores(t, j + 1);
+                    } else {
+                        umma_commit(&sm.o_full[t]);
+                    }
+                }
+                if (ok) umma_commit(&sm.kv_empty[(kv_base + j) % kPairStages]);  // every product reading block j is issued
+            }
+        } else if (warp >= 2) {
+            // ---- softmax and epilogue: warpgroup t = (warp - 2) / 4 serves tile t, thread = query row = TMEM lane
+            const int t = (warp - 2) >> 2, quarter = warp & 3;
+            const int r = quarter * 32 + lane;
+            const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+            const int rows_t = t == 0 ? rows0 : rows1, nbt = t == 0 ? nb0 : nb1;
+            const int p_first = start + q0 + kFaRows * t;
+            const int pos = p_first + min(r, max(rows_t, 1) - 1);  // rows past the end mirror the last one (never stored)
+            const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+            const uint32_t tmem_s = tmem + 128 * t, tmem_o = tmem + 256 + D * t, tmem_p = tmem + 384 + 64 * t;
+            float m_ref = -INFINITY, l = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nbt; ++j) {
+                ok = mbar_wait(&sm.s_full[t], (tile_blocks[t] + j) & 1, abort_flag);
+                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (15 << 8) | (t * 4 + quarter)); }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t sr[4][32];  // this row's 128 scores
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + lane_base + c * 32, sr[c]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tie32(sr[c]);
+                const int base = j * kFaKeys;
+                const bool masked = base + kFaKeys - 1 > p_first;  // the block reaches beyond the tile's first row
+                float m_blk = -INFINITY;
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (base + c * 32 + i <= pos) m_blk = fmaxf(m_blk, __uint_as_float(sr[c][i]));
+                } else {
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            m4[c] = fmaxf(m4[c], fmaxf(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])));
+                    m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                }
+                // the reference maximum moves only when the block exceeds it by more than 2^8 after scaling
+                const bool move = m_blk > m_ref && (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > 8.f);
+                if (__any_sync(0xffffffffu, move)) {
+                    const float m_new = move ? m_blk : m_ref;
+                    const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
+                    l *= corr;
+                    if (j > 0) {  // O holds earlier blocks: rescale this row (whole warps take part in the TMEM access)
+#pragma unroll 1
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            float o[32];
+                            tmem_ld32(tmem_o + lane_base + c0, o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] *= corr;
+                            tmem_st32(tmem_o + lane_base + c0, o);
+                        }
+                    }
+                    m_ref = m_new;
+                }
+                const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
+                // probabilities as bfloat16 pairs into this row's lane of P: key k of the block in column k / 2
+                float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float p0 = ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled));
+                        float p1 = ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, -m_scaled));
+                        if (masked) {
+                            const int key = base + c * 32 + i;
+                            if (key > pos) p0 = 0.f;
+                            if (key + 1 > pos) p1 = 0.f;
+                        }
+                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                        l4[c] += p0 + p1;
+                        pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    tmem_st16(tmem_p + lane_base + 16 * c, pk);
+                }
+                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                // P is in tensor memory and S has been read: the MMA thread may go on
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_fa(&sm.p_full[t]);
+            }
+            if (ok && nbt > 0) {
+                ok = mbar_wait(&sm.o_full[t], tile_units[t] & 1, abort_flag);
+                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (16 << 8) | (t * 4 + quarter)); }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float inv_l = 1.0f / l;
+                    __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + kFaRows * t + r) * n_heads + head) * D;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        float o[32];
+                        tmem_ld32(tmem_o + lane_base + c0, o);
+                        if (r < rows_t) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * i] * inv_l, o[8 * i + 1] * inv_l);
+                                __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
+                                __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
+                                __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
+                                *reinterpret_cast<uint4*>(orow + c0 + 8 * i) =
+                                    make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
+                                               *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                            }
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        // the same bookkeeping in every thread
+        ++units_done;
+        kv_base += nb;
+        tile_blocks[0] += nb0;
+        tile_blocks[1] += nb1;
+        tile_units[0] += 1;
+        tile_units[1] += nb1 > 0 ? 1 : 0;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(512) : "memory");
+    }
+}
+
 // 2-D bfloat16 view [rows, cols] with row stride ld elements and boxes of box_cols x box_rows, 128-byte swizzle.
 static bool make_map_2d(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, int box_cols, int box_rows) {
     EncodeTiledFn fn = encode_fn();
@@ -361,6 +704,36 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
 }
 }  // namespace b200
 
+namespace b200 {
+static int launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* cu_seqlens,
+                       const int* kv_lens, const int* page_table, int table_stride, int n_seqs, int max_q_len, int n_heads,
+                       int n_kv_heads, int k_rows, int v_rows, cudaStream_t stream) {
+    const size_t smem = sizeof(PairSmem<64>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_pair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    const int n_pairs = (max_q_len + 2 * kFaRows - 1) / (2 * kFaRows);
+    const long long units = (long long)n_pairs * n_heads * n_seqs;
+    if (units >= (1ll << 31)) return kErrUnsupportedSize;
+    int dev = 0, n_sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    static unsigned int* counter[64] = {};
+    if (e == cudaSuccess && (dev < 0 || dev >= 64)) return kErrBadArgument;
+    if (e == cudaSuccess && counter[dev] == nullptr) e = cudaGetSymbolAddress((void**)&counter[dev], g_pair_next_unit);
+    if (e == cudaSuccess) e = cudaMemsetAsync(counter[dev], 0, sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return (int)e;
+    const int grid = (int)(units < n_sms ? units : n_sms);  // one CTA per SM; each takes units until none are left
+    attention_prefill_pair_kernel<64><<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
+                                                                         page_table, table_stride, n_heads, n_kv_heads,
+                                                                         k_rows, v_rows, n_seqs, n_pairs);
+    return launch_status();
+}
+}  // namespace b200
+
 // q: packed rows of q_row_stride elements whose first n_heads * head_dim are the rotated queries (n_rows of them);
 // k_pool [n_pages][n_kv_heads][64][head_dim], v_pool [n_pages][n_kv_heads][head_dim][64] (values transposed).
 // head_dim 64 or 128.
@@ -381,6 +754,10 @@ extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_
     if (!make_map_2d(&mq, q, n_rows, n_heads * head_dim, q_row_stride, 64, kFaRows) ||
         !make_map_2d(&mk, k_pool, k_rows, head_dim, head_dim, 64, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, head_dim))
         return kErrUnsupportedSize;
+    // tiles in pairs when there are enough pairs to give every SM one (fewer: the single-tile kernel fills more SMs)
+    if (head_dim == 64 && window <= 0 && (long long)((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows)) * n_heads * n_seqs >= 148)
+        return launch_pair(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
+                           n_kv_heads, (int)k_rows, (int)v_rows, stream);
     if (head_dim == 64)
         return launch_fa<64>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
                              n_kv_heads, window, (int)k_rows, (int)v_rows, stream);

@@ -391,6 +391,36 @@ def test_attention_prefill_on_tcgen05_against_plain(H, KVH, window, D):
     torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
 
 
+def test_attention_prefill_pairs_of_tiles_against_plain():
+    """With enough work the head-size-64 kernel takes query tiles in pairs, one CTA per SM walking through many
+    (pair, head, sequence) units: long and short sequences, a tile pair whose second tile is empty or partial,
+    prefixes that are no multiple of the block, more units than SMs so that every CTA handles several."""
+    H, KVH, D = 16, 4, 64
+    kv_lens = [1500, 129, 128, 257, 700, 64, 1, 385]
+    q_starts = [0, 0, 0, 1, 300, 63, 0, 130]
+    k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=70, seed=11)
+    g = torch.Generator().manual_seed(5)
+    qs, refs, cu = [], [], [0]
+    for s, (n, q0) in enumerate(zip(kv_lens, q_starts)):
+        k, v = dense[s]
+        q_full = (torch.randn(n, H, D, generator=g) * 2).to(torch.bfloat16).float()
+        refs.append(P.causal_attention(q_full, k, v, None)[q0:])
+        qs.append(q_full[q0:])
+        cu.append(cu[-1] + n - q0)
+    q = torch.cat(qs).reshape(-1, H * D)
+    qkv = torch.cat([q, torch.randn(q.shape[0], 2 * KVH * D)], dim=1).to(torch.bfloat16).cuda().contiguous()
+    out = torch.full((q.shape[0], H * D), 9.0, dtype=torch.bfloat16, device="cuda")
+    max_q = max(n - q0 for n, q0 in zip(kv_lens, q_starts))
+    assert -(-max_q // 256) * H * len(kv_lens) >= 148 * 4
+    for _ in range(2):  # the second launch starts from the work counter the first one left
+        assert ops().attention_prefill_tc(qkv, qkv.shape[1], out, torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                                          torch.tensor(kv_lens, dtype=torch.int32, device="cuda"), table, k_pool, v_pool,
+                                          len(kv_lens), max_q, H, KVH, D, 0)
+    assert ops().attention_prefill_tc_status() == 0
+    ref = torch.cat(refs).reshape(-1, H * D)
+    torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
+
+
 def test_attention_decode_ignores_what_lies_beyond_a_sequence():
     """Slots are used again without clearing: stale or non-finite numbers after a sequence's last
     position (same page) and in pages of other sequences must not reach the output."""
