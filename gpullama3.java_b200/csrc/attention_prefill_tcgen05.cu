@@ -324,11 +324,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // softmax threads, ONE thread per query row: the thread reads its row of S (128 scores) into registers in
 // one go, so the maximum, the exponentials and the sum need no exchange between threads and no second
 // read.  While the softmax of one tile runs, the tensor cores form the other tile's scores and outputs
-// (order of issue: S0 S1 | PV0 S0' | PV1 S1' | ...), and every K and V block that is loaded serves both
+// (a tile's next scores are issued as soon as its threads hold the current ones), and every K and V block serves both
 // tiles.  The grid is one CTA per SM; each takes (pair, head, sequence) units from a counter, longest first.  The probabilities never touch shared memory: the thread writes its row of P as bfloat16 pairs into
 // tensor memory and O += P V takes its A operand from there.  One CTA per SM (tensor memory, 512 columns:
-// 2 x 128 of S, 2 x 64 of O, 2 x 64 of P; shared memory: Q 32 KB, three stages of K and V 96 KB).
-constexpr int kPairStages = 3;
+// 2 x 128 of S, 2 x 64 of O, 2 x 64 of P; shared memory: Q 32 KB, four stages of K and V 128 KB).
+constexpr int kPairStages = 4;
+constexpr int kPairThreads = 352;                       // TMA warp, MMA warp of tile 0, eight softmax warps, MMA warp of tile 1
+constexpr int kPairMmaWarp1 = kPairThreads / 32 - 1;
 
 template <int D>
 struct PairSmem {
@@ -337,7 +339,8 @@ struct PairSmem {
     alignas(1024) __nv_bfloat16 v[kPairStages][2][D * 64];
     alignas(8) uint64_t q_full;
     uint64_t kv_full[kPairStages], kv_empty[kPairStages];
-    uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+    uint64_t exp_turn[2];  // the two tiles' softmax threads take turns at the exponentials
     uint32_t tmem_base;
     int abort_flag;
     int unit;  // the unit of work the CTA is on
@@ -363,6 +366,31 @@ __device__ __forceinline__ void tie32(uint32_t (&r)[32]) {
                  :: "memory");
 }
 
+// arithmetic on pairs of floats in one instruction, and the maximum of three
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a), "f"(b));
+    return v;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // 16 registers (32 bfloat16) of this thread's row into 16 consecutive columns of tensor memory
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile(
@@ -382,7 +410,7 @@ __device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_
 __device__ unsigned int g_pair_next_unit;  // work counter of the launch in flight (zeroed on the stream before it)
 
 template <int D>
-__global__ void __launch_bounds__(kFaThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                               const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
@@ -395,8 +423,11 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        for (int s = 0; s < kPairStages; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 1); }
-        for (int t = 0; t < 2; ++t) { mbar_init(&sm.s_full[t], 1); mbar_init(&sm.p_full[t], 4); mbar_init(&sm.o_full[t], 1); }
+        for (int s = 0; s < kPairStages; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 2); }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&sm.s_full[t], 1); mbar_init(&sm.s_free[t], 4); mbar_init(&sm.p_full[t], 4); mbar_init(&sm.pv_done[t], 1);
+            mbar_init(&sm.exp_turn[t], 4);
+        }
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -412,6 +443,10 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;  // tile t: S in columns 128 t, O in 256 + 64 t, P (bfloat16 pairs) in 384 + 64 t
     volatile int* abort_flag = &sm.abort_flag;
+    // The exponentials of a block keep the special-function units busy; reading S, the maximum and the hand-over
+    // do not.  So the two tiles' softmax threads alternate: a tile computes its exponentials only while it holds
+    // the turn, and the other tile's remaining work runs meanwhile.  Tile 0 has the first turn.
+    if (warp >= 6 && warp < 10 && lane == 0) mbar_arrive_fa(&sm.exp_turn[0]);
 
     // The CTA stays and takes one unit of work after another from a counter: a unit is (pair of tiles, head,
     // sequence), the pairs with the most keys first, so that the SMs finish together.  The barriers are never
@@ -420,9 +455,8 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     const int total_units = n_pairs * n_heads * n_seqs;
     int units_done = 0;            // phases of q_full
     int kv_base = 0;               // K/V blocks of earlier units: block g uses stage g % stages, phase g / stages
-    int tile_blocks[2] = {0, 0};   // phases of s_full[t] and p_full[t]
-    int tile_units[2] = {0, 0};    // phases of o_full[t]
-    int kv_ready = 0;  // MMA thread: blocks (counted over all units) whose K and V are known to have landed
+    int tile_blocks[2] = {0, 0};   // phases of s_full[t], s_free[t], p_full[t] and pv_done[t]
+    int kv_ready = 0;  // MMA threads: blocks (counted over all units) whose K and V this thread knows to have landed
 
     for (;;) {
         __syncthreads();  // the unit before is finished everywhere: tensor memory, Q and the unit number are free
@@ -465,22 +499,21 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
                 }
             }
-        } else if (warp == 1 && lane == 0) {
-            // ---- MMA issuer
+        } else if ((warp == 1 || warp == kPairMmaWarp1) && lane == 0) {
+            // ---- MMA issuers, one thread per tile (t = 0: warp 1, t = 1: the last warp).  A tile's next scores
+            // S(i+1) only need its S columns free, which its softmax threads report as soon as they hold block
+            // i's scores in registers (s_free); its outputs O += P(i) V(i) need the probabilities (p_full).  So
+            // per block the thread issues S(i+1), then PV(i): the tensor cores form the next scores while the
+            // softmax of the current ones runs, and the two tiles' threads keep the pipe fed between them.
+            const int t = warp == 1 ? 0 : 1;
+            const int nbt = t == 0 ? nb0 : nb1, nb_other = t == 0 ? nb1 : nb0;
             constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
             constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, D);
-            // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
-            uint64_t q_desc[2], k_desc[kPairStages], v_desc[kPairStages][2];
-#pragma unroll
-            for (int t = 0; t < 2; ++t) q_desc[t] = umma_desc(sm.q[t]);
-#pragma unroll
-            for (int s = 0; s < kPairStages; ++s) {
-                k_desc[s] = umma_desc(sm.k[s]);
-                v_desc[s][0] = umma_desc(sm.v[s][0]);
-                v_desc[s][1] = umma_desc(sm.v[s][1]);
+            bool ok = nbt > 0;
+            kv_ready = max(kv_ready, kv_base);  // blocks of earlier units this tile never read are not waited for now
+            if (ok && !mbar_wait(&sm.q_full, units_done & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_fa_status, 0, 12 << 8); ok = false;
             }
-            bool ok = mbar_wait(&sm.q_full, units_done & 1, abort_flag);
-            if (!ok) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, 12 << 8); }
             auto need_block = [&](int j) {
                 while (ok && kv_ready <= kv_base + j) {
                     const int s = kv_ready % kPairStages;
@@ -492,43 +525,43 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             };
-            auto scores = [&](int t, int j) {  // S_t = Q_t K_j^T
-                const uint64_t qd = q_desc[t], kd = k_desc[(kv_base + j) % kPairStages];
+            // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
+            const uint64_t q_desc = umma_desc(sm.q[t]);
+            auto scores = [&](int j) {  // S = Q K_j^T
+                const uint64_t kd = umma_desc(sm.k[(kv_base + j) % kPairStages]);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 128 * t, qd + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
-                umma_commit(&sm.s_full[t]);  // also means: this tile's earlier P V products have finished
-            };
-            auto outputs = [&](int t, int j) {  // O_t += P_t V_j
-                const int s = (kv_base + j) % kPairStages;
-#pragma unroll
-                for (int kk = 0; kk < kFaKeys / 16; ++kk)  // 16 keys = 8 columns of P
-                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + 384 + 64 * t + 8 * kk, v_desc[s][kk / 4] + 2 * (kk % 4),
-                                     idesc_o, (j | kk) != 0);
+                for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 128 * t, q_desc + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
+                umma_commit(&sm.s_full[t]);
             };
             if (ok) {
                 need_block(0);
-                if (ok) { scores(0, 0); if (nb1 > 0) scores(1, 0); }
+                if (ok) scores(0);
             }
-            for (int j = 0; j < nb && ok; ++j) {
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    const int nbt = t == 0 ? nb0 : nb1;
-                    if (j >= nbt || !ok) continue;
-                    if (!mbar_wait(&sm.p_full[t], (tile_blocks[t] + j) & 1, abort_flag)) {
-                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; continue;
+            for (int i = 0; i < nbt && ok; ++i) {
+                if (i + 1 < nbt) {
+                    if (!mbar_wait(&sm.s_free[t], (tile_blocks[t] + i) & 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (17 << 8) | t); ok = false; break;
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    outputs(t, j);
-                    if (j + 1 < nbt) {
-                        need_block(j + 1);
-                        if (ok) scores(t, j + 1);
-                    } else {
-                        umma_commit(&sm.o_full[t]);
-                    }
+                    need_block(i + 1);
+                    if (!ok) break;
+                    scores(i + 1);
                 }
-                if (ok) umma_commit(&sm.kv_empty[(kv_base + j) % kPairStages]);  // every product reading block j is issued
+                if (!mbar_wait(&sm.p_full[t], (tile_blocks[t] + i) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int s = (kv_base + i) % kPairStages;
+                const uint64_t vd0 = umma_desc(sm.v[s][0]), vd1 = umma_desc(sm.v[s][1]);
+#pragma unroll
+                for (int kk = 0; kk < kFaKeys / 16; ++kk)  // O += P V_i; 16 keys = 8 columns of P
+                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + 384 + 64 * t + 8 * kk, (kk < 4 ? vd0 : vd1) + 2 * (kk % 4),
+                                     idesc_o, (i | kk) != 0);
+                umma_commit(&sm.pv_done[t]);
+                // a stage is free after two arrivals: one from each tile that reads the block, two from a lone reader
+                umma_commit(&sm.kv_empty[s]);
+                if (i >= nb_other) umma_commit(&sm.kv_empty[s]);
             }
-        } else if (warp >= 2) {
+        } else if (warp >= 2 && warp < kPairMmaWarp1) {
             // ---- softmax and epilogue: warpgroup t = (warp - 2) / 4 serves tile t, thread = query row = TMEM lane
             const int t = (warp - 2) >> 2, quarter = warp & 3;
             const int r = quarter * 32 + lane;
@@ -552,6 +585,10 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tie32(sr[c]);
+                // the scores are in registers: the next block's scores may be formed
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_fa(&sm.s_free[t]);
                 const int base = j * kFaKeys;
                 const bool masked = base + kFaKeys - 1 > p_first;  // the block reaches beyond the tile's first row
                 float m_blk = -INFINITY;
@@ -567,8 +604,16 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; i += 2)
-                            m4[c] = fmaxf(m4[c], fmaxf(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])));
+                            m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
                     m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                }
+                // the block before must have left P and O alone before either is touched (it has, long ago, as a rule)
+                if (j > 0) {
+                    ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + j - 1) & 1, abort_flag);
+                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (18 << 8) | (t * 4 + quarter)); }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
                 // the reference maximum moves only when the block exceeds it by more than 2^8 after scaling
                 const bool move = m_blk > m_ref && (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > 8.f);
@@ -589,35 +634,66 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     m_ref = m_new;
                 }
                 const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
+                ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
+                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (19 << 8) | (t * 4 + quarter)); }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
                 // probabilities as bfloat16 pairs into this row's lane of P: key k of the block in column k / 2
                 float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (masked) {  // the few blocks on the diagonal: every key is compared with the row's position
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t pk[16];
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float p0 = ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled));
-                        float p1 = ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, -m_scaled));
-                        if (masked) {
+                        for (int i = 0; i < 32; i += 2) {
                             const int key = base + c * 32 + i;
-                            if (key > pos) p0 = 0.f;
-                            if (key + 1 > pos) p1 = 0.f;
+                            const float p0 = key <= pos ? ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled)) : 0.f;
+                            const float p1 = key + 1 <= pos ? ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, -m_scaled)) : 0.f;
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            l4[c] += p0 + p1;
+                            pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
                         }
-                        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                        l4[c] += p0 + p1;
-                        pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                        tmem_st16(tmem_p + lane_base + 16 * c, pk);
                     }
-                    tmem_st16(tmem_p + lane_base + 16 * c, pk);
+                } else {       // two keys per multiply-add and per addition
+                    const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-m_scaled, -m_scaled);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[16];
+                        unsigned long long sum2 = pack2(0.f, 0.f);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            float x0, x1;
+                            unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, shift2), x0, x1);
+                            const float p0 = ex2(x0), p1 = ex2(x1);
+                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                            sum2 = add2(sum2, pack2(p0, p1));
+                            pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        float s0, s1;
+                        unpack2(sum2, s0, s1);
+                        l4[c] = s0 + s1;
+                        tmem_st16(tmem_p + lane_base + 16 * c, pk);
+                    }
                 }
                 l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);  // the other tile's turn
                 // P is in tensor memory and S has been read: the MMA thread may go on
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_fa(&sm.p_full[t]);
             }
+            for (int j = nbt; j < nb && ok; ++j) {  // rounds in which only the other tile has a block: pass the turn on
+                ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
+                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (20 << 8) | (t * 4 + quarter)); }
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);
+            }
             if (ok && nbt > 0) {
-                ok = mbar_wait(&sm.o_full[t], tile_units[t] & 1, abort_flag);
+                ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + nbt - 1) & 1, abort_flag);
                 if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (16 << 8) | (t * 4 + quarter)); }
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                 if (ok) {
@@ -650,8 +726,6 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
         kv_base += nb;
         tile_blocks[0] += nb0;
         tile_blocks[1] += nb1;
-        tile_units[0] += 1;
-        tile_units[1] += nb1 > 0 ? 1 : 0;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -727,7 +801,7 @@ static int launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (e == cudaSuccess) e = cudaMemsetAsync(counter[dev], 0, sizeof(unsigned int), stream);
     if (e != cudaSuccess) return (int)e;
     const int grid = (int)(units < n_sms ? units : n_sms);  // one CTA per SM; each takes units until none are left
-    attention_prefill_pair_kernel<64><<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
+    attention_prefill_pair_kernel<64><<<grid, kPairThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
                                                                          page_table, table_stride, n_heads, n_kv_heads,
                                                                          k_rows, v_rows, n_seqs, n_pairs);
     return launch_status();
