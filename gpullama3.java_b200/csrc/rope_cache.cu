@@ -81,6 +81,118 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     }
 }
 
+// The same for many tokens (prompts): one CTA takes kRopeTile consecutive tokens, moves 16 bytes per access,
+// and writes the values of a run of tokens that lies aligned in one page as whole 32-byte pieces of the
+// transposed rows instead of one element at a time.  Needs rotary_dim == head_dim and vectors that do not
+// straddle a pair's halves; the launcher falls back to the kernel above otherwise.
+constexpr int kRopeTile = 16;
+constexpr int kRopeThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kRopeThreads)
+rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                              const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
+                              T* __restrict__ k_pool, T* __restrict__ v_pool, int n_tokens, int n_heads, int n_kv_heads,
+                              int head_dim, int pairing, int write_cache) {
+    constexpr int VEC = 16 / (int)sizeof(T);
+    extern __shared__ __align__(16) unsigned char rope_smem[];
+    const int half = head_dim / 2;
+    float* sin_s = reinterpret_cast<float*>(rope_smem);              // [tile][half]
+    float* cos_s = sin_s + kRopeTile * half;                         // [tile][half]
+    T* v_s = reinterpret_cast<T*>(cos_s + kRopeTile * half);         // [tile][kv_dim]
+    __shared__ int pos_s[kRopeTile], page_s[kRopeTile];
+    __shared__ int aligned_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * kRopeTile, n_here = min(kRopeTile, n_tokens - t0);
+    const int q_dim = n_heads * head_dim, kv_dim = n_kv_heads * head_dim, row_len = q_dim + 2 * kv_dim;
+    if (threadIdx.x < kRopeTile) {
+        const int i = threadIdx.x;
+        const int pos = i < n_here ? positions[t0 + i] : 0;
+        pos_s[i] = pos;
+        page_s[i] = (i < n_here && write_cache) ? page_table[(size_t)seq_ids[t0 + i] * table_stride + pos / kPageTokens] : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {  // a full tile of one page, positions pos0 .. pos0 + 15 with pos0 a multiple of 16?
+        bool aligned = n_here == kRopeTile && (pos_s[0] % kRopeTile) == 0;
+        for (int i = 1; i < kRopeTile && aligned; ++i) aligned = pos_s[i] == pos_s[0] + i && page_s[i] == page_s[0];
+        aligned_s = aligned ? 1 : 0;
+    }
+    for (int u = threadIdx.x; u < n_here * half; u += kRopeThreads)
+        sincosf((float)pos_s[u / half] * inv_freq[u % half], &sin_s[u], &cos_s[u]);
+    // values of the tile into shared memory, 16 bytes at a time
+    if (write_cache) {
+        const int vecs = kv_dim / VEC;
+        for (int u = threadIdx.x; u < n_here * vecs; u += kRopeThreads) {
+            const int i = u / vecs, v = u % vecs;
+            *reinterpret_cast<uint4*>(v_s + (size_t)i * kv_dim + v * VEC) =
+                *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + i) * row_len + q_dim + kv_dim + v * VEC);
+        }
+    }
+    __syncthreads();
+
+    // queries (in place) and keys (into the cache): a unit is one vector of a head and, for the half pairing, its partner
+    const int vec_per_head = pairing == 0 ? head_dim / VEC : half / VEC;
+    const int units_per_token = (n_heads + (write_cache ? n_kv_heads : 0)) * vec_per_head;
+    const size_t head_stride = (size_t)kPageTokens * head_dim;
+    for (int u = threadIdx.x; u < n_here * units_per_token; u += kRopeThreads) {
+        const int i = u / units_per_token, w = u % units_per_token;
+        const int h = w / vec_per_head, v = w % vec_per_head;
+        T* src = qkv + (size_t)(t0 + i) * row_len + (size_t)h * head_dim;  // query heads, then key heads: contiguous
+        T* dst = src;
+        if (h >= n_heads)
+            dst = k_pool + ((size_t)page_s[i] * n_kv_heads * kPageTokens + (pos_s[i] % kPageTokens)) * head_dim +
+                  (size_t)(h - n_heads) * head_stride;
+        const float* sn = sin_s + i * half;
+        const float* cs = cos_s + i * half;
+        if (pairing == 0) {
+            uint4 raw = *reinterpret_cast<const uint4*>(src + v * VEC);
+            T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int k = 0; k < VEC; k += 2) {
+                const int j = (v * VEC + k) / 2;
+                const float v0 = to_f32<T>(e[k]), v1 = to_f32<T>(e[k + 1]);
+                e[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
+                e[k + 1] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
+            }
+            *reinterpret_cast<uint4*>(dst + v * VEC) = raw;
+        } else {
+            uint4 lo = *reinterpret_cast<const uint4*>(src + v * VEC), hi = *reinterpret_cast<const uint4*>(src + half + v * VEC);
+            T* a = reinterpret_cast<T*>(&lo);
+            T* b = reinterpret_cast<T*>(&hi);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                const int j = v * VEC + k;
+                const float v0 = to_f32<T>(a[k]), v1 = to_f32<T>(b[k]);
+                a[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
+                b[k] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
+            }
+            *reinterpret_cast<uint4*>(dst + v * VEC) = lo;
+            *reinterpret_cast<uint4*>(dst + half + v * VEC) = hi;
+        }
+    }
+    if (!write_cache) return;
+    // values, transposed: row (kv head, dim) of the page gets the tile's positions
+    if (aligned_s) {
+        const size_t base = (size_t)page_s[0] * n_kv_heads * head_stride + (pos_s[0] % kPageTokens);
+        for (int u = threadIdx.x; u < kv_dim; u += kRopeThreads) {
+            const int g = u / head_dim, d = u % head_dim;
+            alignas(16) T run[kRopeTile];
+#pragma unroll
+            for (int i = 0; i < kRopeTile; ++i) run[i] = v_s[(size_t)i * kv_dim + u];
+            uint4* dst = reinterpret_cast<uint4*>(v_pool + base + g * head_stride + (size_t)d * kPageTokens);
+#pragma unroll
+            for (int q = 0; q < (int)(kRopeTile * sizeof(T) / 16); ++q) dst[q] = reinterpret_cast<const uint4*>(run)[q];
+        }
+    } else {
+        for (int u = threadIdx.x; u < n_here * kv_dim; u += kRopeThreads) {
+            const int i = u / kv_dim, w = u % kv_dim, g = w / head_dim, d = w % head_dim;
+            v_pool[(size_t)page_s[i] * n_kv_heads * head_stride + g * head_stride + (size_t)d * kPageTokens +
+                   (pos_s[i] % kPageTokens)] = v_s[u];
+        }
+    }
+}
+
 }  // namespace b200
 
 extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions, const int* seq_ids,
@@ -91,6 +203,22 @@ extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions,
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || (pairing != 0 && pairing != 1))
         return b200::kErrBadArgument;
     if (rotary_dim / 2 > b200::kMaxRotaryPairs) return b200::kErrUnsupportedSize;
+    // prompts: tiles of tokens with 16-byte accesses, when the sizes fit its vectors and its shared memory
+    {
+        const int vec = dtype == b200::kF32 ? 4 : 8, esize = dtype == b200::kF32 ? 4 : 2;
+        const long long kv_dim = (long long)n_kv_heads * head_dim, row = (long long)(n_heads + 2 * n_kv_heads) * head_dim;
+        const long long smem = (long long)b200::kRopeTile * head_dim * 4 + (long long)b200::kRopeTile * kv_dim * esize;
+        const bool fits = rotary_dim == head_dim && (pairing == 0 ? head_dim % vec == 0 : (head_dim / 2) % vec == 0) &&
+                          row % vec == 0 && kv_dim % vec == 0 && smem <= 48 * 1024 &&
+                          (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+        if (n_tokens >= 4 * b200::kRopeTile && fits) {
+            const int grid = (n_tokens + b200::kRopeTile - 1) / b200::kRopeTile;
+            B200_DISPATCH_DTYPE(dtype, T,
+                return b200::launch_pdl(b200::rope_cache_write_tiled_kernel<T>, dim3(grid), dim3(b200::kRopeThreads),
+                                        (size_t)smem, stream, (T*)qkv, positions, seq_ids, page_table, table_stride, inv_freq,
+                                        (T*)k_pool, (T*)v_pool, n_tokens, n_heads, n_kv_heads, head_dim, pairing, write_cache));
+        }
+    }
     B200_DISPATCH_DTYPE(dtype, T,
         return b200::launch_pdl(b200::rope_cache_write_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)qkv,
                                 positions, seq_ids, page_table, table_stride, inv_freq, (T*)k_pool, (T*)v_pool, n_heads,

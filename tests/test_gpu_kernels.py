@@ -163,6 +163,46 @@ def test_rope_and_cache_write(dtype, pairing, H, KVH, D, rotary):
     assert int((k_pool.float().abs().sum(dim=(1, 3)) > 0).sum()) == T   # no other cache row was touched
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing, H, KVH, D", [("half", 8, 2, 64), ("interleaved", 3, 1, 96), ("half", 4, 4, 128),
+                                                ("interleaved", 6, 2, 32)])
+def test_rope_and_cache_write_for_prompts(dtype, pairing, H, KVH, D):
+    """Many tokens go through the kernel that takes 16 tokens per CTA: a prompt from position 0 (tiles that lie
+    aligned in their pages), a prompt whose tokens start at an odd offset of the batch, a chunk that continues at
+    position 101 and crosses pages, a single token, and a last tile that is not full."""
+    from gpullama3.java_b200.parts.position import PAIRING_CODES
+
+    runs = [(0, 0, 200), (1, 0, 77), (2, 101, 150), (3, 4000, 1), (1, 77, 30)]   # (sequence, first position, tokens)
+    positions = [p0 + i for _, p0, n in runs for i in range(n)]
+    seq_ids = [s for s, _, n in runs for _ in range(n)]
+    T = len(positions)
+    assert T >= 64 and T % 16 != 0
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(T, (H + 2 * KVH) * D, generator=g).to(dtype)
+    inv = P.rope_inverse_frequencies(D, 5e5, None)
+    n_pages = 4 * 64
+    table = torch.randperm(n_pages, generator=g).to(torch.int32).reshape(4, 64)
+    k_pool = torch.zeros(n_pages, KVH, 64, D, dtype=dtype, device="cuda")
+    v_pool = torch.zeros(n_pages, KVH, D, 64, dtype=dtype, device="cuda")
+    buf = qkv.clone().cuda()
+    ops().rope_cache_write(buf, torch.tensor(positions, dtype=torch.int32, device="cuda"),
+                           torch.tensor(seq_ids, dtype=torch.int32, device="cuda"), table.cuda(),
+                           inv.to(torch.float32).cuda(), k_pool, v_pool, H, KVH, D, D, PAIRING_CODES[pairing])
+    x = qkv.float()
+    q, k, v = x[:, :H * D].reshape(T, H, D), x[:, H * D:(H + KVH) * D].reshape(T, KVH, D), x[:, (H + KVH) * D:].reshape(T, KVH, D)
+    cos, sin = P.rope_tables(torch.tensor(positions), inv, torch.float32)
+    q, k = P.apply_rope(q, cos, sin, pairing), P.apply_rope(k, cos, sin, pairing)
+    t = tol(dtype, x)
+    torch.testing.assert_close(buf[:, :H * D].float().cpu(), q.reshape(T, H * D).to(dtype).float(), **t)
+    assert torch.equal(buf[:, H * D:].cpu(), qkv[:, H * D:])          # raw keys and values stay as they were
+    pages = table[torch.tensor(seq_ids), torch.tensor(positions) // 64].long()
+    slots = torch.tensor(positions) % 64
+    torch.testing.assert_close(k_pool.cpu()[pages, :, slots].float(), k.to(dtype).float(), **t)
+    assert torch.equal(v_pool.cpu()[pages, :, :, slots].float(), v)
+    assert int((k_pool.float().abs().sum(dim=(1, 3)) > 0).sum()) == T   # no other cache row was touched
+    assert int((v_pool.float().abs().sum(dim=(1, 2)) > 0).sum()) == T
+
+
 @pytest.mark.parametrize("a_dtype, w_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                               (torch.bfloat16, torch.float32)])
 @pytest.mark.parametrize("M, N, K", [(1, 40, 24), (7, 130, 100), (65, 64, 17), (200, 258, 1030)])
