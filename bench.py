@@ -298,7 +298,7 @@ def main() -> int:
         e_val, e_ms = time_e2e(engine, args.batch, args.context, args.steps, args.warmup)
         e2e = {"value": round(e_val, 1), "unit": "tokens/s", "ms_per_step": round(e_ms, 3),
                "h2d_bytes_per_step": int(engine.step_fn.last_h2d_bytes) if hasattr(engine.step_fn, "last_h2d_bytes") else None,
-               "d2h_bytes_per_step": 4 * args.batch}
+               "d2h_bytes_per_step": int(getattr(engine.step_fn, "last_d2h_bytes", 0)) or 4 * args.batch}
         log(f"e2e b{args.batch}: {e_ms:.3f} ms/step, {e_val:.0f} tok/s")
     clocks.stop()
 

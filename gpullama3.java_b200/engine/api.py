@@ -29,6 +29,18 @@ def _resolve_dtype(dtype) -> torch.dtype:
         raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
 
 
+class _LoopStep:
+    """The step function as the generation loop uses it: the loop samples from a step's logits before it runs
+    the next step, so the logits need not be copied; decode steps may come back as drawn tokens directly."""
+
+    def __init__(self, step_fn: StepFunction):
+        self.step_fn = step_fn
+        self.decode_and_sample = step_fn.decode_and_sample
+
+    def __call__(self, inputs):
+        return self.step_fn(inputs, reuse_output=True)
+
+
 class Engine:
     def __init__(self, model, *, max_tokens: int = 32768, max_batch: int = 64, max_length: int | None = None):
         if not torch.cuda.is_available() or model.device.type != "cuda":
@@ -38,8 +50,8 @@ class Engine:
         self.cache = model.new_cache(max_tokens, max_slots=max(max_batch, 1))
         self.step_fn = StepFunction(model, self.cache)
         self.max_length = max_length if max_length is not None else self.cache.n_pages * 64
-        # the generation loop samples from a step's logits before it runs the next step
-        self.generator = Generator(lambda inputs: self.step_fn(inputs, reuse_output=True), self.cache, Sampler, max_batch=max_batch, max_length=self.max_length)
+        self.generator = Generator(_LoopStep(self.step_fn), self.cache, Sampler, max_batch=max_batch,
+                                   max_length=self.max_length)
 
     # ---- construction
     @classmethod

@@ -113,9 +113,10 @@ class Generator:
         inputs = [SequenceInput(slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in live]
         logits = self.step_fn(inputs)
         metrics.prompt_tokens += sum(len(prompts[i]) for i in live)
+        tokens = sampler.sample(logits, [ids[i] for i in live], [len(results[i].tokens) for i in live])
+        fused = getattr(self.step_fn, "decode_and_sample", None)  # step and draw as one recorded launch, if offered
         first = True
         while live:
-            tokens = sampler.sample(logits, [ids[i] for i in live], [len(results[i].tokens) for i in live])
             if first:
                 metrics.prefill_seconds += time.perf_counter() - t0
                 t0 = time.perf_counter()
@@ -139,6 +140,9 @@ class Generator:
             if not live:
                 break
             inputs = [SequenceInput(slots[i], [results[i].tokens[-1]], [0]) for i in live]
-            logits = self.step_fn(inputs)
+            requests, draws = [ids[i] for i in live], [len(results[i].tokens) for i in live]
+            tokens = fused(inputs, sampler, requests, draws) if fused is not None else None
+            if tokens is None:
+                tokens = sampler.sample(self.step_fn(inputs), requests, draws)
             metrics.decode_steps += 1
         metrics.decode_seconds += time.perf_counter() - t0

@@ -90,47 +90,87 @@ class DecodeGraph:
     replayed for every token (tornadovm/TornadoVMMasterPlan.java:149-175 of the reference
     project)."""
 
-    def __init__(self, model, cache: SequenceCache, n_seqs: int, widths: list[int]):
+    def __init__(self, model, cache: SequenceCache, n_seqs: int, widths: list[int], sampler=None):
         from ..kernels import ops
 
         self.model, self.cache, self.n, self.widths = model, cache, n_seqs, list(widths)
+        self.sampler = sampler                        # its launches are recorded after the model's, if given
+        self.draws = sampler is not None and sampler.uniforms([0], [0]) is not None
         self.sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs, n_seqs] + [n_seqs * w for w in widths]
         self.table_shapes = [(n_seqs, w) for w in widths]
-        total = sum(self.sizes)
+        self.table_offsets, off = [], sum(self.sizes[:7])
+        for w in widths:
+            self.table_offsets.append(off)
+            off += n_seqs * w
+        self.uniform_offset = off                     # float32 numbers of the draws, after the integers
+        total = off + (n_seqs if self.draws else 0)
         self.host = torch.empty(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
         self.dev = torch.empty(total, dtype=torch.int32, device=model.device)
-        self.copied = torch.cuda.Event()
+        self.tokens_dev = torch.empty(n_seqs, dtype=torch.int32, device=model.device) if sampler is not None else None
+        self.tokens_host = torch.empty(n_seqs, dtype=torch.int32).pin_memory() if sampler is not None else None
+        self.done = torch.cuda.Event()                # the last run of this step, copies included
+        self.pending = False
         self.graph: torch.cuda.CUDAGraph | None = None
         self.logits: torch.Tensor | None = None
         self.n_launches = 0
+        self.h2d_bytes = total * 4
+        self.d2h_bytes = n_seqs * 4 if sampler is not None else 0
+        self.last_slots: list[int] | None = None
+        self.last_pos: list[int] | None = None
         kv_heads = [g.need.n_kv_heads for g in cache.kv_groups] or [1]
         self.kv_capacity = max(widths, default=1) * PAGE_TOKENS
         self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), self.kv_capacity)
 
-    def refresh(self, slots, start_pos, tokens) -> None:
-        pieces, _, _ = _pack(self.cache, slots, start_pos, [[t] for t in tokens], list(range(self.n)), self.widths)
-        self.copied.synchronize()  # the previous step's copy must have left the staging buffer
-        np.concatenate(pieces, out=self.host.numpy())
-        self.dev.copy_(self.host, non_blocking=True)
-        self.copied.record()
-        self.h2d_bytes = self.host.numel() * 4
+    def refresh(self, slots, start_pos, tokens, uniforms=None) -> None:
+        """Fill the staging buffer for this step.  A step that continues the one before (same slots, every
+        position one further) only rewrites what moved: tokens, positions, lengths, and the table row of a
+        sequence that has just entered a new page."""
+        if self.pending:
+            self.done.synchronize()  # the run before must have read the staging buffer
+            self.pending = False
+        n, h = self.n, self.host_np
+        if self.last_slots == slots and all(p == q + 1 for p, q in zip(start_pos, self.last_pos)):
+            h[0:n] = tokens
+            h[n:2 * n] = start_pos
+            h[4 * n + 1:5 * n + 1] = h[n:2 * n] + 1
+            for i, p in enumerate(start_pos):
+                if p % PAGE_TOKENS == 0:
+                    for gi, (off, w) in enumerate(zip(self.table_offsets, self.widths)):
+                        row = self.cache.page_rows(gi, [slots[i]])[0]
+                        dst = h[off + i * w: off + (i + 1) * w]
+                        dst[:len(row)] = np.maximum(np.asarray(row, dtype=np.int32), 0)
+        else:
+            pieces, _, _ = _pack(self.cache, slots, start_pos, [[t] for t in tokens], list(range(n)), self.widths)
+            np.concatenate(pieces, out=h[:self.uniform_offset])
+        if self.draws:
+            h[self.uniform_offset:self.uniform_offset + n] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
+        self.last_slots, self.last_pos = list(slots), list(start_pos)
 
-    def _forward(self, slots, start_pos):
+    def _launches(self, slots, start_pos):
+        """The step as it is issued and as it is recorded: staging buffer in, model, draw, tokens out."""
+        self.dev.copy_(self.host, non_blocking=True)
         ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, slots,
                                   start_pos, [1] * self.n)
         ctx.extras["decode_splits"] = self.splits
         ctx.extras["decode_kv_capacity"] = self.kv_capacity
-        return self.model.forward(ctx, self.cache, rows)
+        logits = self.model.forward(ctx, self.cache, rows)
+        if self.sampler is not None:
+            u = self.dev[self.uniform_offset:self.uniform_offset + self.n].view(torch.float32) if self.draws else None
+            self.sampler.sample_into(logits, u, self.tokens_dev)
+            self.tokens_host.copy_(self.tokens_dev, non_blocking=True)
+        return logits
 
-    def run(self, slots, start_pos, tokens) -> torch.Tensor:
+    def run(self, slots, start_pos, tokens, uniforms=None) -> torch.Tensor:
         from ..kernels import ops
 
-        self.refresh(slots, start_pos, tokens)
+        self.refresh(slots, start_pos, tokens, uniforms)
         if self.graph is None:
             # the first step runs as ordinary launches (this also loads every kernel library the step
             # needs); the same launch sequence is then recorded, without running, for later steps
-            out = self._forward(slots, start_pos)
+            out = self._launches(slots, start_pos)
             torch.cuda.synchronize()
+            first_tokens = self.tokens_host.clone() if self.sampler is not None else None
             before = ops.launch_count()
             graph = torch.cuda.CUDAGraph()
             import gc
@@ -138,15 +178,26 @@ class DecodeGraph:
             gc.disable()  # a collection while recording could free device or pinned memory, which is not allowed then
             try:
                 with torch.cuda.graph(graph):
-                    self.logits = self._forward(slots, start_pos)
+                    self.logits = self._launches(slots, start_pos)
             finally:
                 if gc_was_on:
                     gc.enable()
             self.n_launches = ops.launch_count() - before
             self.graph = graph
+            if first_tokens is not None:
+                self.tokens_host.copy_(first_tokens)
             return out
         self.graph.replay()
+        self.done.record()
+        self.pending = True
         return self.logits
+
+    def sampled(self) -> list[int]:
+        """The tokens drawn by the last run (waits for it)."""
+        if self.pending:
+            self.done.synchronize()
+            self.pending = False
+        return self.tokens_host.tolist()
 
 
 class StepFunction:
@@ -167,12 +218,11 @@ class StepFunction:
         self._graphs: dict[tuple, DecodeGraph] = {}
         self.graph_launches = 0     # kernel launches replayed from graphs so far
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy (tokens, positions, page tables)
+        self.last_d2h_bytes = 0     # bytes of the last step's copy of drawn tokens to the host (decode_and_sample)
 
-    def _decode_with_graph(self, inputs: list[SequenceInput], reuse_output: bool) -> torch.Tensor | None:
+    def _graph_for(self, slots: list[int], start: list[int], sampler=None) -> DecodeGraph:
+        """The recorded step that fits these sequences: table widths are powers of two of at least 4 pages."""
         cache = self.cache
-        n = len(inputs)
-        slots = [s.slot for s in inputs]
-        start = [cache.length(s) for s in slots]
         widths = []
         for gi in range(len(cache.kv_groups)):
             need = max(len(r) for r in cache.page_rows(gi, slots))
@@ -180,10 +230,41 @@ class StepFunction:
             while w < need:
                 w *= 2
             widths.append(w)
-        key = (n, tuple(widths))
+        key = (len(slots), tuple(widths), sampler.launch_key() if sampler is not None else None)
         g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[key] = DecodeGraph(self.model, cache, n, widths)
+            g = self._graphs[key] = DecodeGraph(self.model, cache, len(slots), widths, sampler)
+        return g
+
+    def decode_and_sample(self, inputs: list[SequenceInput], sampler, requests: list[int], draws: list[int]):
+        """One token per sequence in, one drawn token per sequence out (host integers), as ONE recorded launch:
+        staging copy, model, the sampler's kernels and the copy of the tokens back.  Returns None when the step
+        cannot be served that way (graphs off, a part that is not graph-safe, too many sequences); the caller
+        then takes the step and the sampler separately."""
+        if not (self.use_graphs and len(inputs) <= self.max_graph_batch and all(len(s.tokens) == 1 for s in inputs)
+                and hasattr(sampler, "sample_into")):
+            return None
+        self._validate(inputs)
+        cache = self.cache
+        cache.reserve([(s.slot, 1) for s in inputs])
+        slots = [s.slot for s in inputs]
+        start = [cache.length(s) for s in slots]
+        g = self._graph_for(slots, start, sampler)
+        replayed = g.graph is not None
+        g.run(slots, start, [s.tokens[0] for s in inputs], sampler.uniforms(requests, draws))
+        self.last_h2d_bytes, self.last_d2h_bytes = g.h2d_bytes, g.d2h_bytes
+        if replayed:
+            self.graph_launches += g.n_launches
+        for s in slots:
+            cache.commit(s, 1)
+        return g.sampled()
+
+    def _decode_with_graph(self, inputs: list[SequenceInput], reuse_output: bool) -> torch.Tensor | None:
+        cache = self.cache
+        n = len(inputs)
+        slots = [s.slot for s in inputs]
+        start = [cache.length(s) for s in slots]
+        g = self._graph_for(slots, start)
         replayed = g.graph is not None
         logits = g.run(slots, start, [s.tokens[0] for s in inputs])
         self.last_h2d_bytes = g.h2d_bytes

@@ -71,3 +71,21 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, requests: list[int], draws: list[int]) -> list[int]:
         return self.sample_device(logits, requests, draws).tolist()
+
+    # --- for a step function that records the draw together with the model's launches ----------------------
+    def launch_key(self):
+        """What the recorded launches depend on: a step recorded for one key serves every sampler with it."""
+        return ("greedy",) if self.params.greedy else ("sample", float(self.params.temperature), float(self.params.top_p))
+
+    def uniforms(self, requests: list[int], draws: list[int]) -> list[float] | None:
+        """The host-side input of one step's draws (none for greedy)."""
+        if self.params.greedy:
+            return None
+        return [uniform(self.params.seed, r, d) for r, d in zip(requests, draws)]
+
+    def sample_into(self, logits: torch.Tensor, uniforms: torch.Tensor | None, out: torch.Tensor) -> None:
+        """The kernel launches of ``sample_device`` with every buffer given (nothing is copied or synchronised)."""
+        if self.params.greedy:
+            ops.argmax_rows(logits, out)
+        else:
+            ops.sample_rows(logits, uniforms, out, self.params.temperature, self.params.top_p)

@@ -89,6 +89,28 @@ def test_temperature_sampling_follows_the_uniform_numbers(session_tmp):
     assert all(len(x) == 8 and all(0 <= t < cfg["vocab_size"] for t in x) for x in nucleus)
 
 
+@pytest.mark.parametrize("sampling", [dict(), dict(temperature=0.7, seed=3), dict(temperature=0.9, top_p=0.8, seed=4)],
+                         ids=["greedy", "temperature", "nucleus"])
+def test_step_and_draw_recorded_together_give_the_tokens_of_step_then_draw(session_tmp, sampling):
+    """Decode steps normally run as one recorded launch that ends with the sampler's kernels and the copy of the
+    tokens to the host; with that path switched off the loop runs the step, then the sampler.  Same tokens, and
+    the recorded path is really taken (it reports the bytes it copied back)."""
+    from gpullama3.java_b200.engine.api import Engine
+
+    cfg_json, norm_std = TINY["A"]
+    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0})
+    cfg, _ = plain_inputs(d)
+    prompts = random_prompts(cfg["vocab_size"], [3, 70, 9, 33], seed=6)
+    engine = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
+    together = engine.generate(prompts, max_new_tokens=70, stop_ids=(), **sampling)   # crosses a page boundary
+    assert engine.step_fn.last_d2h_bytes > 0
+    apart_engine = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
+    apart_engine.generator.step_fn.decode_and_sample = lambda *a, **k: None
+    apart = apart_engine.generate(prompts, max_new_tokens=70, stop_ids=(), **sampling)
+    assert apart_engine.step_fn.last_d2h_bytes == 0
+    assert together == apart
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_long_decoding_and_first_tokens(session_tmp, dtype):
     """One token a step from the very first token on, for 330 positions (five page boundaries), and
