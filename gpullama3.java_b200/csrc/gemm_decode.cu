@@ -16,6 +16,12 @@
 //
 // Sizes: K a multiple of 32, rows 16-byte aligned; any N; M <= 64.  Other shapes are refused
 // (kErrUnsupportedSize) and the caller takes the plain kernel.
+//
+// A norm between two products can be split between them (b200_gemm_decode_linked, M <= 16): RMSNorm of a row
+// x is w * x * r with r = rsqrt(mean(x^2) + eps) (inference/InferenceCore.java:47-56), and r, one number per
+// row, commutes with the next product.  The product that completes x (residual epilogue) also writes
+// bfloat16(x * w) and, per CTA, the sum of squares of the x it holds; the next product multiplies its
+// sums by r, which it gets by adding the partial sums in CTA order.  No kernel in between, no atomics.
 #include "common.cuh"
 
 namespace b200 {
@@ -41,10 +47,25 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 
 // MT: 16-row tiles of weight rows per CTA (ROWS = 16 * MT), or MT = 0 for 8 rows (narrow outputs, so that
 // more CTAs pull on HBM).  NT: token tiles of 8.  EPI: 0 store, 1 residual add (C float), 2 gated SiLU.
-template <int MT, int NT, int EPI, typename TC, int U>  // U: k-blocks of 32 in flight per warp
+struct NormLink {
+    // this product's rows of A are x * w of a norm: multiply the sums of row t by rsqrt(sum_i in_partials[t][i] / dim + eps)
+    const float* in_partials;   // [M][n_in] or null
+    int n_in;
+    float eps;
+    int dim;
+    // this product completes a residual row x (epilogue 1): also write bfloat16(x * w) and this CTA's sum of x^2
+    const void* out_weight;     // [N] norm weights, or null
+    int out_weight_f32;         // their type: 1 float32, 0 bfloat16
+    __nv_bfloat16* out_act;     // [M][ld_out_act]
+    int ld_out_act;
+    float* out_partials;        // [M][gridDim.x]
+};
+
+// LINK: the product is a half of a split norm (the plain product is compiled without any of that)
+template <int MT, int NT, int EPI, typename TC, int U, bool LINK>  // U: k-blocks of 32 in flight per warp
 __global__ void __launch_bounds__(kDecodeThreads)
 gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
-                   TC* __restrict__ C, int ldc, int M, int N, int K) {
+                   TC* __restrict__ C, int ldc, int M, int N, int K, NormLink link) {
     constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
     constexpr int MTT = MT == 0 ? 1 : MT;            // tiles actually multiplied
     constexpr bool HI = MT != 0;                     // rows g + 8 of a tile exist
@@ -118,6 +139,20 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
                 }
     }
 
+    // the norm's factor of each row: warp w adds the partial sums of squares of rows w and w + 8 in a fixed order
+    __shared__ float row_factor[16];
+    if (LINK && NT <= 2 && link.in_partials != nullptr) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const int token = warp + 8 * n;
+            float sum = 0.f;
+            if (token < M)
+                for (int col = lane; col < link.n_in; col += 32) sum += link.in_partials[(size_t)token * link.n_in + col];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (lane == 0) row_factor[token] = rsqrtf(sum / (float)link.dim + link.eps);
+        }
+    }
     // partial sums of the warps meet in shared memory; thread (row, token) adds them in warp order
 #pragma unroll
     for (int m = 0; m < MTT; ++m)
@@ -136,12 +171,30 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < kDecodeWarps; ++w) s += red[w][token][row];
+        if (LINK && NT <= 2 && link.in_partials != nullptr) s *= row_factor[token];
+        float square = 0.f;
         if (EPI == 2) {
             fin[token][row] = s;
         } else if (token < M && row0 + row < N) {
             TC* c = C + (size_t)token * ldc + row0 + row;
-            if (EPI == 1) *c = from_f32<TC>(to_f32<TC>(*c) + s);
-            else *c = from_f32<TC>(s);
+            if (EPI == 1) {
+                const float x = to_f32<TC>(*c) + s;
+                *c = from_f32<TC>(x);
+                if (LINK && NT <= 2 && link.out_weight != nullptr) {
+                    const float w = link.out_weight_f32 ? reinterpret_cast<const float*>(link.out_weight)[row0 + row]
+                                                        : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(link.out_weight)[row0 + row]);
+                    link.out_act[(size_t)token * link.ld_out_act + row0 + row] = __float2bfloat16_rn(x * w);
+                    square = x * x;
+                }
+            } else {
+                *c = from_f32<TC>(s);
+            }
+        }
+        if (LINK && EPI == 1 && NT <= 2 && link.out_weight != nullptr) {
+            // the ROWS threads of a token are neighbours in a warp: their squares are added in a fixed tree
+#pragma unroll
+            for (int off = ROWS / 2; off > 0; off >>= 1) square += __shfl_xor_sync(0xffffffffu, square, off);
+            if (row == 0 && token < M) link.out_partials[(size_t)token * gridDim.x + blockIdx.x] = square;
         }
     }
     if (EPI == 2) {
@@ -156,12 +209,12 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     }
 }
 
-template <int MT, int NT, int EPI, typename TC, int U>
+template <int MT, int NT, int EPI, typename TC, int U, bool LINK>
 static int launch_u(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
-                    int K, cudaStream_t stream) {
+                    int K, const NormLink& link, cudaStream_t stream) {
     constexpr int ROWS = MT == 0 ? 8 : 16 * MT;
     const size_t smem = sizeof(float) * (kDecodeWarps + 1) * NT * 8 * ROWS;
-    auto kernel = gemm_decode_kernel<MT, NT, EPI, TC, U>;
+    auto kernel = gemm_decode_kernel<MT, NT, EPI, TC, U, LINK>;
     if (smem > 48 * 1024) {
         static bool configured = false;
         if (!configured) {
@@ -171,46 +224,61 @@ static int launch_u(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int
         }
     }
     return launch_pdl(kernel, dim3((N + ROWS - 1) / ROWS), dim3(kDecodeThreads), smem, stream, a, lda, w, ldw, (TC*)C, ldc,
-                      M, N, K);
+                      M, N, K, link);
 }
 
 template <int MT, int NT, int EPI, typename TC>
 static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, void* C, int ldc, int M, int N,
-                      int K, cudaStream_t stream) {
+                      int K, const NormLink& link, cudaStream_t stream) {
     constexpr int MTT = MT == 0 ? 1 : MT;
-    if (MTT * NT >= 8) return launch_u<MT, NT, EPI, TC, 2>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    constexpr bool kCanLink = NT <= 2;
+    const bool linked = kCanLink && (link.in_partials != nullptr || link.out_weight != nullptr);
+#define B200_U(UU)                                                                                                  \
+    do {                                                                                                            \
+        if (linked) return launch_u<MT, NT, EPI, TC, UU, kCanLink>(a, lda, w, ldw, C, ldc, M, N, K, link, stream);   \
+        return launch_u<MT, NT, EPI, TC, UU, false>(a, lda, w, ldw, C, ldc, M, N, K, link, stream);                  \
+    } while (0)
+    if (MTT * NT >= 8) B200_U(2);
     // 8-row CTAs of a short grid (at most two per SM) can afford twice the loads in flight; a longer grid
     // needs the registers for a third and fourth resident CTA instead
-    if (MT == 0 && NT == 1 && N <= 2 * 148 * 8) return launch_u<MT, NT, EPI, TC, (MT == 0 && NT == 1) ? 8 : 4>(a, lda, w, ldw, C, ldc, M, N, K, stream);
-    return launch_u<MT, NT, EPI, TC, 4>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    if (MT == 0 && NT == 1 && N <= 2 * 148 * 8) B200_U(((MT == 0 && NT == 1) ? 8 : 4));
+    B200_U(4);
+#undef B200_U
 }
 
 template <int MT, int NT, typename TC>
 static int launch_epi(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epi,
-                      cudaStream_t stream) {
+                      const NormLink& link, cudaStream_t stream) {
     auto a = (const __nv_bfloat16*)A;
     auto w = (const __nv_bfloat16*)W;
-    if (epi == 0) return launch_one<MT, NT, 0, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
-    if (epi == 1) return launch_one<MT, NT, 1, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
-    return launch_one<MT, NT, 2, TC>(a, lda, w, ldw, C, ldc, M, N, K, stream);
+    if (epi == 0) return launch_one<MT, NT, 0, TC>(a, lda, w, ldw, C, ldc, M, N, K, link, stream);
+    if (epi == 1) return launch_one<MT, NT, 1, TC>(a, lda, w, ldw, C, ldc, M, N, K, link, stream);
+    return launch_one<MT, NT, 2, TC>(a, lda, w, ldw, C, ldc, M, N, K, link, stream);
 }
 
 }  // namespace b200
 
-// A, W bfloat16; C bfloat16 or float32 (c_dtype); epilogue 0 store, 1 residual add (C float32), 2 gated SiLU.
-extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                int N, int K, int epilogue, cudaStream_t stream) {
-    using namespace b200;
+namespace b200 {
+
+static bool decode_narrow(int N) { return N <= 4096; }  // few rows: fewer per CTA so that enough CTAs stream weights
+static int decode_rows_per_cta(int M, int N) {
+    const bool narrow = decode_narrow(N);
+    if (M <= 16) return narrow ? 8 : 16;
+    return narrow ? 16 : 32;
+}
+
+static int gemm_decode_launch(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N,
+                              int K, int epilogue, const NormLink& link, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K < 32 || K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0) return kErrUnsupportedSize;
     if (((uintptr_t)A | (uintptr_t)W) & 15) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && (N & 1)))
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
-    const bool narrow = N <= 4096;  // few rows: fewer per CTA so that enough CTAs stream weights
-#define B200_GO(MT, NT)                                                                                       \
-    return c_dtype == kF32 ? launch_epi<MT, NT, float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)     \
-                           : launch_epi<MT, NT, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream)
+    const bool narrow = decode_narrow(N);
+#define B200_GO(MT, NT)                                                                                             \
+    return c_dtype == kF32 ? launch_epi<MT, NT, float>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, link, stream)     \
+                           : launch_epi<MT, NT, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, link, stream)
     if (M <= 8) { if (narrow) { B200_GO(0, 1); } else { B200_GO(1, 1); } }
     if (M <= 16) { if (narrow) { B200_GO(0, 2); } else { B200_GO(1, 2); } }
     // more tokens: every weight fragment meets 4 or 8 token tiles; wide outputs take 32 rows per CTA so
@@ -218,4 +286,47 @@ extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, 
     if (M <= 32) { if (narrow) { B200_GO(1, 4); } else { B200_GO(2, 4); } }
     if (narrow) { B200_GO(1, 8); } else { B200_GO(2, 8); }
 #undef B200_GO
+}
+
+}  // namespace b200
+
+// A, W bfloat16; C bfloat16 or float32 (c_dtype); epilogue 0 store, 1 residual add (C float32), 2 gated SiLU.
+extern "C" int b200_gemm_decode(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
+                                int N, int K, int epilogue, cudaStream_t stream) {
+    return b200::gemm_decode_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, b200::NormLink{}, stream);
+}
+
+// How many CTAs, hence partial sums per row, the product (M, N) runs with.
+extern "C" int b200_gemm_decode_ctas(int M, int N) {
+    if (M <= 0 || N <= 0) return 0;
+    const int rows = b200::decode_rows_per_cta(M, N);
+    return (N + rows - 1) / rows;
+}
+
+// The same product as one half, or both halves, of a split norm (M <= 16).
+//   in_partials [M][n_in] (or null): A holds x * w of the norm; every sum of row t is multiplied by
+//       rsqrt(sum(in_partials[t]) / norm_dim + eps) before the epilogue.
+//   out_weight [N] (or null; epilogue 1 only): after the residual add, bfloat16(x * out_weight) goes to
+//       out_act [M][ld_out_act] and this CTA's sum of x^2 per row to out_partials [M][b200_gemm_decode_ctas(M, N)].
+extern "C" int b200_gemm_decode_linked(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
+                                       int N, int K, int epilogue, const float* in_partials, int n_in, float eps,
+                                       int norm_dim, const void* out_weight, int out_weight_dtype, void* out_act,
+                                       int ld_out_act, float* out_partials, cudaStream_t stream) {
+    using namespace b200;
+    if (M > 16) return kErrUnsupportedSize;
+    if (in_partials != nullptr && (n_in <= 0 || norm_dim <= 0)) return kErrBadArgument;
+    if (out_weight != nullptr && (epilogue != 1 || out_act == nullptr || out_partials == nullptr || ld_out_act < N ||
+                                  (out_weight_dtype != kF32 && out_weight_dtype != kBF16)))
+        return kErrBadArgument;
+    NormLink link{};
+    link.in_partials = in_partials;
+    link.n_in = n_in;
+    link.eps = eps;
+    link.dim = norm_dim;
+    link.out_weight = out_weight;
+    link.out_weight_f32 = out_weight_dtype == kF32 ? 1 : 0;
+    link.out_act = (__nv_bfloat16*)out_act;
+    link.ld_out_act = ld_out_act;
+    link.out_partials = out_partials;
+    return gemm_decode_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, link, stream);
 }

@@ -145,9 +145,19 @@ class CausalLM:
         if not self.loaded:
             raise WeightError("the model has no weights yet (load_folder / load_random / load_tensors)")
         residual = self.embedding.forward(ctx.tokens)  # float32 [T, hidden]
-        for entry in self.schedule:
+        # a block may leave the first norm of the block that runs next to that block's first product
+        # (parts/base.py, ScaledRows); blocks that do not offer this are called the plain way
+        handed = None
+        for k, entry in enumerate(self.schedule):
             view = cache.view(entry.cache) if entry.cache is not None else None
-            self.blocks[entry.layer].forward(residual, ctx, view, entry.writes_cache)
+            block = self.blocks[entry.layer]
+            if block.takes_scaled_rows(ctx):
+                nxt = self.blocks[self.schedule[k + 1].layer] if k + 1 < len(self.schedule) else None
+                then = nxt.first_norm() if nxt is not None and nxt.takes_scaled_rows(ctx) else None
+                handed = block.forward(residual, ctx, view, entry.writes_cache, x_in=handed, then_norm=then)
+            else:
+                block.forward(residual, ctx, view, entry.writes_cache)
+                handed = None
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         x = self.final_norm.forward(residual, ctx.dtype, rows=logit_rows)

@@ -41,6 +41,9 @@ _SIGNATURES = {
                                            c_int, c_int, c_int, c_int]),
     "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_int]),
+    "b200_gemm_decode_linked": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
+                                                c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                            c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -211,6 +214,52 @@ def gemm_decode(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int
     _check(_fn("b200_gemm_decode")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_decode")
     return True
+
+
+def gemm_decode_links(n_rows: int, w: torch.Tensor) -> bool:
+    """Whether ``gemm_decode_linked`` takes a product of ``n_rows`` bfloat16 rows with ``w``."""
+    return (w.dtype == torch.bfloat16 and n_rows <= 16 and w.shape[1] % 32 == 0 and w.stride(1) == 1
+            and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_decode_partials(n_rows: int, n_out: int) -> int:
+    """How many partial sums of squares per row the residual product [n_rows, n_out] leaves."""
+    lib = library("gemm_decode")
+    return int(lib.b200_gemm_decode_ctas(n_rows, n_out))
+
+
+def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, *, row_factors=None,
+                       emit=None) -> None:
+    """``gemm_decode`` as one half, or both, of an RMSNorm split between two products (at most 16 rows).
+
+    ``row_factors = (partials [M, P] float32, eps, dim)``: the rows of ``a`` are x * w of a norm; every
+    sum of row t is multiplied by rsqrt(sum(partials[t]) / dim + eps) before the epilogue.
+    ``emit = (norm_weight [N], act [M, N] bfloat16, partials [M, gemm_decode_partials(M, N)] float32)``
+    (residual epilogue only): after c += a w^T, act = bfloat16(c * norm_weight) and partials hold each
+    CTA's sum of c^2 per row."""
+    M, K = a.shape
+    N = w.shape[0]
+    _dev(a, w, c)
+    assert a.dtype == torch.bfloat16 and gemm_decode_links(M, w) and a.stride(1) == 1 and a.stride(0) % 8 == 0
+    assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M and a.data_ptr() % 16 == 0
+    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    in_p, n_in, eps, dim = None, 0, 0.0, 0
+    if row_factors is not None:
+        part, eps, dim = row_factors
+        assert part.dtype == torch.float32 and part.is_contiguous() and part.shape[0] == M
+        in_p, n_in = part.data_ptr(), part.shape[1]
+    out_w, out_w_dtype, out_act, ld_act, out_p = None, 0, None, 0, None
+    if emit is not None:
+        nw, act, part_out = emit
+        assert epilogue == EPILOGUE_RESIDUAL_ADD and nw.numel() == N and nw.is_contiguous()
+        assert act.dtype == torch.bfloat16 and act.shape == (M, N) and act.stride(1) == 1
+        assert part_out.dtype == torch.float32 and part_out.is_contiguous()
+        assert tuple(part_out.shape) == (M, gemm_decode_partials(M, N))
+        out_w, out_w_dtype, out_act, ld_act, out_p = nw.data_ptr(), dtype_code(nw.dtype), act.data_ptr(), act.stride(0), part_out.data_ptr()
+    _check(_fn("b200_gemm_decode_linked")(
+        a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), dtype_code(c.dtype), c.stride(0), M, N, K,
+        epilogue, in_p, n_in, float(eps), int(dim), out_w, out_w_dtype, out_act, ld_act, out_p, _stream()),
+        "gemm_decode_linked")
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:

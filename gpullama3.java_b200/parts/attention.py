@@ -42,7 +42,10 @@ class GroupedQueryAttention(Mixer):
         self.qkv = Linear(torch.cat([q.to(common), k.to(common), v.to(common)], dim=0).contiguous())
         self.o = Linear(o.to(torch.float32 if dtype == torch.float32 else o.dtype).contiguous())
 
-    def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True):
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return ctx.all_decode and self.qkv.links_with(ctx.n_tokens, ctx.dtype)
+
+    def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True, then_norm=None):
         qkv = self.qkv.store(x, ctx.dtype)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
         from ..kernels import fast
 
@@ -55,7 +58,7 @@ class GroupedQueryAttention(Mixer):
             if not fast.try_attention(qkv, out, ctx, table, cache, self):
                 ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
                                     self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
-        self.o.add_to(out, residual)
+        return self.o.add_to(out, residual, then_norm)
 
 
 register_mixer("attention", GroupedQueryAttention)

@@ -45,6 +45,27 @@ class StepContext:
     extras: dict = field(default_factory=dict)  # scratch a part may keep for the duration of a step
 
 
+@dataclass
+class ScaledRows:
+    """Rows of an RMSNorm that is split between the product before it and the product after it: ``data`` holds
+    x * weight (rounded to the run dtype) and row t still lacks its factor rsqrt(sum(partials[t]) / dim + eps).
+    A part that says so (``takes_scaled_rows``) accepts this in place of normalised rows and lets its first
+    product apply the factor; a part whose last product adds into the residual stream may be asked to leave
+    the next norm in this form (``then_norm``).  Decode steps save two kernel launches per layer that way."""
+    data: torch.Tensor       # [T, dim]
+    partials: torch.Tensor   # float32 [T, P]
+    eps: float
+    dim: int
+
+    @property
+    def shape(self):
+        return self.data.shape
+
+    @property
+    def device(self):
+        return self.data.device
+
+
 class Part:
     """Common face of all parts."""
 
@@ -67,6 +88,11 @@ class Norm(Part):
         """x: float32 residual stream [T, dim] -> normalised rows in ``out_dtype``; ``rows`` picks rows."""
         raise NotImplementedError
 
+    def row_factor_form(self):
+        """(weight [dim], eps, dim) if the norm is weight * x * f(row) with f = rsqrt(mean(x^2) + eps), so that
+        it can be split between two products (see ScaledRows); None otherwise."""
+        return None
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer.  The attention mixer asks for the rotary description."""
@@ -86,14 +112,25 @@ class Mixer(Part):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache, residual: torch.Tensor, writes_cache: bool = True) -> None:
         """x: normalised input [T, hidden] in the run dtype.  Adds the mixer's output to the float32
-        ``residual`` [T, hidden] in place.  ``cache`` is the KVView/StateView of this run's entry."""
+        ``residual`` [T, hidden] in place.  ``cache`` is the KVView/StateView of this run's entry.
+
+        A mixer whose ``takes_scaled_rows(ctx)`` is true is also called with ``x`` a ScaledRows and with the
+        keyword ``then_norm`` (a Norm or None); it returns the ScaledRows of that norm over the updated
+        residual, or None if it left the norm to the caller."""
         raise NotImplementedError
+
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return False
 
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
-        """Adds the feed-forward output of x [T, hidden] to ``residual`` in place."""
+        """Adds the feed-forward output of x [T, hidden] to ``residual`` in place.  With
+        ``takes_scaled_rows(ctx)`` true: ``x`` may be a ScaledRows, ``then_norm`` as for a mixer."""
         raise NotImplementedError
+
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return False
 
 
 class Block(Part):
@@ -108,7 +145,17 @@ class Block(Part):
                 "feed_forward_norm": self.feed_forward_norm}
 
     def forward(self, residual: torch.Tensor, ctx: StepContext, cache, writes_cache: bool = True) -> None:
+        """Runs the layer on the float32 ``residual`` in place.  A block whose ``takes_scaled_rows(ctx)`` is
+        true is also called with ``x_in`` (the ScaledRows of its first norm, or None) and ``then_norm`` (the
+        first norm of the block that runs next, or None) and returns that norm's ScaledRows or None."""
         raise NotImplementedError
+
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return False
+
+    def first_norm(self) -> Norm | None:
+        """The norm the block applies to the residual stream before anything else, if it starts that way."""
+        return None
 
 
 class PartRegistryError(KeyError):

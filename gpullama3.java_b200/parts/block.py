@@ -10,9 +10,31 @@ class PreNormBlock(Block):
     def graph_safe(self):
         return all(p.graph_safe for p in self.children().values())
 
-    def forward(self, residual, ctx: StepContext, cache, writes_cache=True):
-        self.mixer.forward(self.mixer_norm.forward(residual, ctx.dtype), ctx, cache, residual, writes_cache)
-        self.feed_forward.forward(self.feed_forward_norm.forward(residual, ctx.dtype), ctx, residual)
+    def first_norm(self):
+        return self.mixer_norm
+
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return self.mixer.takes_scaled_rows(ctx) and self.mixer_norm.row_factor_form() is not None
+
+    def forward(self, residual, ctx: StepContext, cache, writes_cache=True, x_in=None, then_norm=None):
+        """In a decode step the two norms need not be kernels of their own: the product that completes the
+        residual stream before a norm (the mixer's, or the previous block's, last product) leaves the norm's
+        rows one factor short, and the product after it applies the factor (ScaledRows).  Parts that do not
+        offer this are called the plain way."""
+        x = x_in if x_in is not None else self.mixer_norm.forward(residual, ctx.dtype)
+        h = None
+        if self.mixer.takes_scaled_rows(ctx):
+            ffn_links = self.feed_forward.takes_scaled_rows(ctx)
+            h = self.mixer.forward(x, ctx, cache, residual, writes_cache,
+                                   then_norm=self.feed_forward_norm if ffn_links else None)
+        else:
+            self.mixer.forward(x, ctx, cache, residual, writes_cache)
+        if h is None:
+            h = self.feed_forward_norm.forward(residual, ctx.dtype)
+        if self.feed_forward.takes_scaled_rows(ctx):
+            return self.feed_forward.forward(h, ctx, residual, then_norm=then_norm)
+        self.feed_forward.forward(h, ctx, residual)
+        return None
 
 
 register_block("pre_norm", PreNormBlock)

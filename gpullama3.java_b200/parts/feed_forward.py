@@ -32,9 +32,12 @@ class SwiGLUFeedForward(FeedForward):
         self.gate_up = Linear(fused.contiguous())
         self.down = Linear(down.to(torch.float32 if dtype == torch.float32 else down.dtype).contiguous())
 
-    def forward(self, x, ctx: StepContext, residual):
+    def takes_scaled_rows(self, ctx: StepContext) -> bool:
+        return ctx.all_decode and self.gate_up.links_with(ctx.n_tokens, ctx.dtype)
+
+    def forward(self, x, ctx: StepContext, residual, then_norm=None):
         h = self.gate_up.gated_silu(x, ctx.dtype)  # [T, intermediate]
-        self.down.add_to(h, residual)
+        return self.down.add_to(h, residual, then_norm)
 
 
 register_feed_forward("swiglu", SwiGLUFeedForward)

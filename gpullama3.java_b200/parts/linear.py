@@ -8,6 +8,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .base import ScaledRows
 
 
 class Linear:
@@ -16,12 +17,19 @@ class Linear:
         self.weight = weight
         self.out_features, self.in_features = weight.shape
 
-    def _run(self, a: torch.Tensor, c: torch.Tensor, epilogue: int) -> None:
+    def _run(self, a, c: torch.Tensor, epilogue: int) -> None:
         from ..kernels import fast
 
+        if isinstance(a, ScaledRows):  # only handed to a product that said it links (links_with)
+            ops.gemm_decode_linked(a.data, self.weight, c, epilogue, row_factors=(a.partials, a.eps, a.dim))
+            return
         if fast.try_gemm(a, self.weight, c, epilogue):
             return
         ops.gemm_generic(a, self.weight, c, epilogue)
+
+    def links_with(self, n_rows: int, dtype: torch.dtype) -> bool:
+        """Whether this product can be one half of a split norm for ``n_rows`` rows of ``dtype``."""
+        return dtype == torch.bfloat16 and ops.gemm_decode_links(n_rows, self.weight)
 
     def store(self, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """a @ W.T as a new [T, out] tensor."""
@@ -29,9 +37,20 @@ class Linear:
         self._run(a, c, ops.EPILOGUE_STORE)
         return c
 
-    def add_to(self, a: torch.Tensor, residual: torch.Tensor) -> None:
-        """residual += a @ W.T, the sum kept in float32."""
+    def add_to(self, a: torch.Tensor, residual: torch.Tensor, then_norm=None) -> ScaledRows | None:
+        """residual += a @ W.T, the sum kept in float32.  With ``then_norm`` (a norm that has a row-factor form)
+        and a product that links, the same kernel also leaves that norm of the new residual as ScaledRows."""
+        form = then_norm.row_factor_form() if then_norm is not None else None
+        if (form is not None and a.dtype == torch.bfloat16 and self.links_with(a.shape[0], a.dtype)
+                and form[2] == self.out_features and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0):
+            weight, eps, dim = form
+            n = a.shape[0]
+            act = torch.empty((n, dim), dtype=torch.bfloat16, device=a.device)
+            partials = torch.empty((n, ops.gemm_decode_partials(n, self.out_features)), dtype=torch.float32, device=a.device)
+            ops.gemm_decode_linked(a, self.weight, residual, ops.EPILOGUE_RESIDUAL_ADD, emit=(weight, act, partials))
+            return ScaledRows(act, partials, eps, dim)
         self._run(a, residual, ops.EPILOGUE_RESIDUAL_ADD)
+        return None
 
     def gated_silu(self, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """W holds gate and up rows interleaved; returns silu(gate) * up as [T, out/2]."""

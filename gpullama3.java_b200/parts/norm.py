@@ -25,6 +25,9 @@ class RMSNorm(Norm):
         keep = torch.float32 if (dtype == torch.float32 or w.dtype == torch.float32) else torch.bfloat16
         self.weight = w.to(device=device, dtype=keep).contiguous()
 
+    def row_factor_form(self):
+        return self.weight, self.eps, self.dim
+
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.dim), dtype=out_dtype, device=x.device)

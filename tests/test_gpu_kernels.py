@@ -255,6 +255,64 @@ def test_gemm_decode_and_its_epilogues(M, N, K):
     assert not o.gemm_decode(a.float(), w, c)
 
 
+@pytest.mark.parametrize("M", [1, 8, 13, 16])
+@pytest.mark.parametrize("hidden, K, N2", [(544, 96, 96), (2400, 64, 50), (4128, 32, 40)])
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32], ids=["w16", "w32"])
+def test_gemm_decode_halves_of_a_split_norm(M, hidden, K, N2, w_dtype):
+    """RMSNorm between two products without a kernel of its own: the residual product also leaves x * w and
+    per-CTA sums of x^2 (68, 300 and 258 partial sums per row here: under and over the 256 a warp asks for
+    up front, 8 and 16 rows per CTA), the next product applies rsqrt(mean(x^2) + eps) to its sums.  Checked
+    half by half and end to end against the norm followed by the product."""
+    o = ops()
+    eps = 1e-5
+    g = torch.Generator().manual_seed(M + hidden)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(hidden, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    x0 = torch.randn(M, hidden, generator=g)
+    nw = (1.0 + 0.2 * torch.randn(hidden, generator=g)).to(w_dtype)
+    x_ref = x0.double() + a.float().cpu().double() @ w1.float().cpu().double().t()
+    res = x0.clone().cuda()
+    act = torch.empty(M, hidden, dtype=torch.bfloat16, device="cuda")
+    P_out = o.gemm_decode_partials(M, hidden)
+    assert P_out == {544: 68, 2400: 300, 4128: 258}[hidden]
+    partials = torch.full((M, P_out), 99.0, device="cuda")
+    o.gemm_decode_linked(a, w1, res, o.EPILOGUE_RESIDUAL_ADD, emit=(nw.cuda(), act, partials))
+    torch.testing.assert_close(res.cpu(), x_ref.float(), **tol(torch.float32, x_ref))
+    x = res.cpu().double()                                            # what the kernel itself holds
+    torch.testing.assert_close(act.float().cpu(), (x * nw.double()).float().to(torch.bfloat16).float(), rtol=2.0 ** -7, atol=1e-6)
+    torch.testing.assert_close(partials.sum(dim=1).cpu().double(), (x * x).sum(dim=1), rtol=1e-5, atol=0)
+    # second half against what it is given: act (already rounded) and the factor of the partial sums
+    w2 = (torch.randn(N2, hidden, generator=g) / math.sqrt(hidden)).to(torch.bfloat16).cuda()
+    r = torch.rsqrt(partials.sum(dim=1).cpu().double() / hidden + eps).reshape(M, 1)
+    want = (act.float().cpu().double() @ w2.float().cpu().double().t()) * r
+    for c_dtype in (torch.bfloat16, torch.float32):
+        c = torch.empty(M, N2, dtype=c_dtype, device="cuda")
+        o.gemm_decode_linked(act, w2, c, o.EPILOGUE_STORE, row_factors=(partials, eps, hidden))
+        torch.testing.assert_close(c.float().cpu(), want.float().to(c_dtype).float(), **tol(c_dtype, want))
+    h = torch.empty(M, N2 // 2, dtype=torch.bfloat16, device="cuda")
+    o.gemm_decode_linked(act, w2, h, o.EPILOGUE_GATED_SILU, row_factors=(partials, eps, hidden))
+    gated = P.swiglu(want[:, 0::2], want[:, 1::2])
+    torch.testing.assert_close(h.float().cpu(), gated.float().to(torch.bfloat16).float(), **tol(torch.bfloat16, gated))
+    # and against the norm as a kernel of its own followed by the product.  Both ways round the product's input to
+    # bfloat16 once, at different places (x w r against x w): per term a relative 2^-9 at most, so two sums of
+    # `hidden` such terms differ by about 2^-9 of the result's size; 2^-7 of the largest result bounds 96 of them
+    normed = torch.empty(M, hidden, dtype=torch.bfloat16, device="cuda")
+    o.rmsnorm(res, nw.cuda(), normed, eps)
+    apart = torch.empty(M, N2, dtype=torch.float32, device="cuda")
+    assert o.gemm_decode(normed, w2, apart, o.EPILOGUE_STORE)
+    assert float((c.float() - apart).abs().max()) <= 2.0 ** -7 * float(apart.abs().max())
+    exact = P.rmsnorm(x.float(), nw.float(), eps).double() @ w2.float().cpu().double().t()
+    assert float((c.float().cpu() - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max())
+    # both halves in one call: the residual product of a second layer
+    res2 = torch.zeros(M, N2, device="cuda")
+    act2 = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
+    part2 = torch.empty(M, o.gemm_decode_partials(M, N2), device="cuda")
+    o.gemm_decode_linked(act, w2, res2, o.EPILOGUE_RESIDUAL_ADD, row_factors=(partials, eps, hidden),
+                         emit=(torch.ones(N2, dtype=w_dtype, device="cuda"), act2, part2))
+    torch.testing.assert_close(res2.cpu(), want.float(), **tol(torch.bfloat16, want))
+    torch.testing.assert_close(part2.sum(dim=1).cpu().double(), (res2.cpu().double() ** 2).sum(dim=1), rtol=1e-5, atol=0)
+
+
 @pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 512), (1, 8, 8), (100, 300, 72), (129, 257, 200),
                                      (300, 1030, 2048), (2048, 512, 1024), (65, 3072, 2048)])
 def test_gemm_tcgen05_and_its_epilogues(M, N, K):

@@ -116,6 +116,42 @@ class _Dummy:
         self.dtype = dtype
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_block_with_its_norms_left_to_the_products_around_them(tmp_path, name):
+    """In a decode step the pre-norm block hands each norm to the products before and after it (ScaledRows).
+    With that switched off in every part the same step runs the norm kernels; both give the same logits up to
+    the rounding of a bfloat16 run, the launches differ by the two norms per layer, and a prompt step, which
+    does not take that path, is not affected."""
+    from gpullama3.java_b200.engine.api import Engine, SequenceInput
+    from gpullama3.java_b200.kernels import ops
+
+    cfg_json, norm_std = TINY[name]
+    d = make_model_dir(tmp_path, cfg_json, seed=31, norm_std=norm_std)
+    cfg, w = plain_inputs(d)
+    engines = [Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 8, max_batch=4) for _ in range(2)]
+    for e in engines:
+        e.step_fn.use_graphs = False          # launches are counted as they are issued
+    for block in engines[1].model.blocks:
+        for part in (block, block.mixer, block.feed_forward):
+            part.takes_scaled_rows = lambda ctx: False
+    prompts = [[5, 9, 3], [7] * 40, [1, 2]]
+    outs, launches = [], []
+    for e in engines:
+        slots = [e.cache.acquire() for _ in prompts]
+        first = e.step([SequenceInput(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        before = ops.launch_count()
+        second = e.step([SequenceInput(s, [11 + i], [0]) for i, s in enumerate(slots)])
+        launches.append(ops.launch_count() - before)
+        outs.append((first.float().cpu(), second.float().cpu()))
+    assert torch.equal(outs[0][0], outs[1][0])
+    n_layers = cfg["num_hidden_layers"]
+    assert launches[1] - launches[0] == 2 * n_layers - 1   # every norm but the first layer's first one
+    for i, p in enumerate(prompts):
+        ref = P.forward(cfg, w, p + [11 + i], round_to=torch.bfloat16)[-1]
+        assert_close_logits(outs[0][1][i], ref, torch.bfloat16)
+        assert_close_logits(outs[1][1][i], ref, torch.bfloat16)
+
+
 def test_embedding_and_tied_head_share_memory():
     emb = TokenEmbedding(50, 24)
     table = torch.randn(50, 24).to(torch.bfloat16)
