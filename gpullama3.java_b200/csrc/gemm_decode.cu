@@ -114,6 +114,22 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     load_weights(warp * U);
     pdl_launch_dependents();
     pdl_wait();
+    // The norm's factor of each row, made while the first weights are in flight: warp w adds the partial sums of
+    // squares of rows w and w + 8 in a fixed order.  (Measured: here it costs nothing; after the main loop, at
+    // the tail of every CTA, it cost 1 to 3 us per product.)
+    __shared__ float row_factor[16];
+    if (LINK && NT <= 2 && link.in_partials != nullptr) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const int token = warp + 8 * n;
+            float sum = 0.f;
+            if (token < M)
+                for (int col = lane; col < link.n_in; col += 32) sum += link.in_partials[(size_t)token * link.n_in + col];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (lane == 0) row_factor[token] = rsqrtf(sum / (float)link.dim + link.eps);
+        }
+    }
     for (int kb0 = warp * U; kb0 < n_blocks; kb0 += kDecodeWarps * U) {
         uint4 cl[U][MTT], ch[U][MTT];
 #pragma unroll
@@ -139,20 +155,6 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
                 }
     }
 
-    // the norm's factor of each row: warp w adds the partial sums of squares of rows w and w + 8 in a fixed order
-    __shared__ float row_factor[16];
-    if (LINK && NT <= 2 && link.in_partials != nullptr) {
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            const int token = warp + 8 * n;
-            float sum = 0.f;
-            if (token < M)
-                for (int col = lane; col < link.n_in; col += 32) sum += link.in_partials[(size_t)token * link.n_in + col];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-            if (lane == 0) row_factor[token] = rsqrtf(sum / (float)link.dim + link.eps);
-        }
-    }
     // partial sums of the warps meet in shared memory; thread (row, token) adds them in warp order
 #pragma unroll
     for (int m = 0; m < MTT; ++m)
