@@ -114,6 +114,19 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     load_weights(warp * U);
     pdl_launch_dependents();
     pdl_wait();
+    // What the epilogue will add to is asked for now, not at the CTA's tail (one element per thread when the
+    // tile has no more elements than threads; a larger tile reads late).
+    constexpr bool kEarlyC = EPI == 1 && NT * 8 * ROWS <= kDecodeThreads;
+    float c_early = 0.f, w_early = 0.f;
+    if (kEarlyC && (int)threadIdx.x < NT * 8 * ROWS) {
+        const int token = threadIdx.x / ROWS, row = threadIdx.x % ROWS;
+        if (token < M && row0 + row < N) {
+            c_early = to_f32<TC>(C[(size_t)token * ldc + row0 + row]);
+            if (LINK && NT <= 2 && link.out_weight != nullptr)
+                w_early = link.out_weight_f32 ? reinterpret_cast<const float*>(link.out_weight)[row0 + row]
+                                              : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(link.out_weight)[row0 + row]);
+        }
+    }
     // The norm's factor of each row, made while the first weights are in flight: warp w adds the partial sums of
     // squares of rows w and w + 8 in a fixed order.  (Measured: here it costs nothing; after the main loop, at
     // the tail of every CTA, it cost 1 to 3 us per product.)
@@ -180,10 +193,11 @@ gemm_decode_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         } else if (token < M && row0 + row < N) {
             TC* c = C + (size_t)token * ldc + row0 + row;
             if (EPI == 1) {
-                const float x = to_f32<TC>(*c) + s;
+                const float x = (kEarlyC ? c_early : to_f32<TC>(*c)) + s;
                 *c = from_f32<TC>(x);
                 if (LINK && NT <= 2 && link.out_weight != nullptr) {
-                    const float w = link.out_weight_f32 ? reinterpret_cast<const float*>(link.out_weight)[row0 + row]
+                    const float w = kEarlyC ? w_early
+                                  : link.out_weight_f32 ? reinterpret_cast<const float*>(link.out_weight)[row0 + row]
                                                         : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(link.out_weight)[row0 + row]);
                     link.out_act[(size_t)token * link.ld_out_act + row0 + row] = __float2bfloat16_rn(x * w);
                     square = x * x;
