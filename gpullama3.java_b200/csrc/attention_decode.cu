@@ -102,7 +102,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int group = n_heads / n_kv_heads;
     pdl_launch_dependents();
-    pdl_wait();  // queries, the new keys and values, lengths and page tables come from earlier kernels
+    // Lengths and page tables were copied to the device before the step's first kernel started, so they are read
+    // before the wait for the predecessor; the queries, the step's key and value and the cache are read after it.
     const int kv_len = kv_lens[seq];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
     // keys read from the cache: all of them, or all but the step's own when this kernel writes that one
@@ -115,6 +116,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     const size_t page_stride = (size_t)n_kv_heads * kPageTokens * D;
     const size_t head_off = (size_t)kvh * kPageTokens * D;
 
+    const int first_page = blk_begin + warp < blk_end ? pages[(blk_begin + warp) * 32 / kPageTokens] : 0;
+    pdl_wait();
     // query fragments: rows = the heads of this group (rows >= group are zero)
     uint4 ql[KB], qh[KB];
     {
@@ -178,7 +181,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 
     for (int blk = blk_begin + warp; blk < blk_end; blk += kAttnDecodeWarps) {
         const int base = blk * 32;
-        const size_t page_base = (size_t)pages[base / kPageTokens] * page_stride + head_off;
+        const size_t page_base = (size_t)(blk == blk_begin + warp ? first_page : pages[base / kPageTokens]) * page_stride + head_off;
         const int in_page = base % kPageTokens;
         const __nv_bfloat16* kp = k_pool + page_base;
         const __nv_bfloat16* vp = v_pool + page_base;
