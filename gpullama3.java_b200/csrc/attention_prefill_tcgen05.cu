@@ -122,6 +122,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + 128;  // S: 128 columns, O: D columns
     volatile int* abort_flag = &sm.abort_flag;
+    pdl_launch_dependents();
+    pdl_wait();  // the set-up above overlapped the kernel before; its results are read from here on
 
     if (warp == 0 && lane == 0) {
         // ---- producer: Q once, then per block two K pages and two V^T pages
@@ -407,7 +409,12 @@ __device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_
         ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-__device__ unsigned int g_pair_next_unit;  // work counter of the launch in flight (zeroed on the stream before it)
+// Work counters, kept on the device so that a launch needs nothing from the host (it may be replayed from a
+// graph): words 0 and 1 count units, word 2 is the number of launches that have ended, word 3 counts the CTAs of
+// the running launch that have ended.  A launch takes its units from word (launches ended) % 2 and zeroes the
+// other word for the launch after it; its last CTA advances word 2.  Launches on a device must follow one
+// another in one stream.
+__device__ unsigned int g_pair_ctl[4];
 
 template <int D>
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -443,6 +450,11 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;  // tile t: S in columns 128 t, O in 256 + 64 t, P (bfloat16 pairs) in 384 + 64 t
     volatile int* abort_flag = &sm.abort_flag;
+    pdl_launch_dependents();
+    pdl_wait();  // the set-up above overlapped the kernel before; its results are read from here on
+    const unsigned int launches_ended = *reinterpret_cast<volatile unsigned int*>(&g_pair_ctl[2]);
+    const int counter = (int)(launches_ended & 1u);
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_pair_ctl[counter ^ 1] = 0;
     // The exponentials of a block keep the special-function units busy; reading S, the maximum and the hand-over
     // do not.  So the two tiles' softmax threads alternate: a tile computes its exponentials only while it holds
     // the turn, and the other tile's remaining work runs meanwhile.  Tile 0 has the first turn.
@@ -460,7 +472,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 
     for (;;) {
         __syncthreads();  // the unit before is finished everywhere: tensor memory, Q and the unit number are free
-        if (threadIdx.x == 0) sm.unit = (int)atomicAdd(&g_pair_next_unit, 1u);
+        if (threadIdx.x == 0) sm.unit = (int)atomicAdd(&g_pair_ctl[counter], 1u);
         __syncthreads();
         const int unit = sm.unit;
         if (unit >= total_units || *abort_flag) break;
@@ -733,6 +745,14 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(512) : "memory");
     }
+    if (threadIdx.x == 0) {  // the last CTA to end hands the counters over to the next launch
+        __threadfence();
+        if (atomicAdd(&g_pair_ctl[3], 1u) == gridDim.x - 1) {
+            g_pair_ctl[3] = 0;
+            __threadfence();
+            g_pair_ctl[2] = launches_ended + 1;
+        }
+    }
 }
 
 // 2-D bfloat16 view [rows, cols] with row stride ld elements and boxes of box_cols x box_rows, 128-byte swizzle.
@@ -771,10 +791,8 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         configured = true;
     }
     dim3 grid((max_q_len + kFaRows - 1) / kFaRows, n_heads, n_seqs);
-    attention_prefill_tc_kernel<D><<<grid, kFaThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
-                                                                      page_table, table_stride, n_heads, n_kv_heads, window,
-                                                                      k_rows, v_rows);
-    return launch_status();
+    return launch_pdl(attention_prefill_tc_kernel<D>, grid, dim3(kFaThreads), smem, stream, mq, mk, mv, (__nv_bfloat16*)out,
+                      cu_seqlens, kv_lens, page_table, table_stride, n_heads, n_kv_heads, window, k_rows, v_rows);
 }
 }  // namespace b200
 
@@ -795,16 +813,12 @@ static int launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     int dev = 0, n_sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-    static unsigned int* counter[64] = {};
-    if (e == cudaSuccess && (dev < 0 || dev >= 64)) return kErrBadArgument;
-    if (e == cudaSuccess && counter[dev] == nullptr) e = cudaGetSymbolAddress((void**)&counter[dev], g_pair_next_unit);
-    if (e == cudaSuccess) e = cudaMemsetAsync(counter[dev], 0, sizeof(unsigned int), stream);
     if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return kErrBadArgument;
     const int grid = (int)(units < n_sms ? units : n_sms);  // one CTA per SM; each takes units until none are left
-    attention_prefill_pair_kernel<64><<<grid, kPairThreads, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens, kv_lens,
-                                                                         page_table, table_stride, n_heads, n_kv_heads,
-                                                                         k_rows, v_rows, n_seqs, n_pairs);
-    return launch_status();
+    return launch_pdl(attention_prefill_pair_kernel<64>, dim3(grid), dim3(kPairThreads), smem, stream, mq, mk, mv,
+                      (__nv_bfloat16*)out, cu_seqlens, kv_lens, page_table, table_stride, n_heads, n_kv_heads, k_rows, v_rows,
+                      n_seqs, n_pairs);
 }
 }  // namespace b200
 

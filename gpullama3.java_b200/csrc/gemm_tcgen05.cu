@@ -75,6 +75,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sm.tmem_base;
     volatile int* abort_flag = &sm.abort_flag;
+    // barriers and tensor memory were set up while the kernel before may still have been running; its results
+    // (A, and C for the residual epilogue) are touched only from here on
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---- producer
@@ -222,7 +226,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
     }
     const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(n_tiles < n_sms ? n_tiles : n_sms));
-    kernel<<<grid, kGemmTcThreads, smem, stream>>>(ma, mw, (TC*)C, ldc, M, N, K);
+    return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, (TC*)C, ldc, M, N, K);
     return launch_status();
 }
 
