@@ -10,7 +10,10 @@
 // The uniform number u of each row is an input (the host derives it from seed, request and step
 // counters), so a request's draws do not depend on which batch it sits in.  Sums that decide a
 // token are either accumulated in a fixed order or in integers, so a row always gives the same
-// token.  Equal probabilities are ordered by index in the nucleus.  The nucleus is found without sorting:
+// token.  Equal probabilities are ordered by index in the nucleus.  When few tokens pass the cutoff (a peaked
+// distribution, the usual case at the reference's default temperature 0.1) they are gathered into shared
+// memory; up to 1,024 of them are ordered by counting and walked like the reference does, in float32.
+// Otherwise (a longer list, or the whole row when more than 4,093 pass) the nucleus is found without sorting:
 // the bits of the probability at which the descending running mass crosses a target are decided
 // two at a time, each pair by one pass of masked sums over the row (two such descents: for top_p, then for the draw).
 #include <limits.h>
@@ -20,6 +23,7 @@ namespace b200 {
 
 constexpr int kSampleThreads = 1024;
 constexpr int kSampleWarps = kSampleThreads / 32;
+constexpr int kCandidateCap = 4096;  // nucleus candidates that are gathered into shared memory (32 KB)
 
 __global__ void __launch_bounds__(kSampleThreads)
 argmax_rows_kernel(const float* __restrict__ logits, int ld, int* __restrict__ out, int V) {
@@ -187,6 +191,32 @@ __device__ Crossing mass_descent(const float* __restrict__ probs, int V, float c
     return r;
 }
 
+// A warp's segment [lo, hi) of a row is cut into one contiguous chunk per lane (a multiple of four elements),
+// so that prefix sums over (lane, element) run in index order.  `chunk_exp_sum` adds this lane's exponentials in
+// index order, four independent 16-byte loads at a time when the row allows it.
+__device__ __forceinline__ int lane_chunk(int lo, int hi) { return (((hi - lo + 31) / 32) + 3) & ~3; }
+
+__device__ __forceinline__ float chunk_exp_sum(const float* __restrict__ row, int begin, int end, float inv_t, float zmax, bool vec) {
+    float sum = 0.f;
+    int i = begin;
+    if (vec) {
+        for (; i + 16 <= end; i += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = *reinterpret_cast<const float4*>(row + i + 4 * k);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                sum += expf(v[k].x * inv_t - zmax);
+                sum += expf(v[k].y * inv_t - zmax);
+                sum += expf(v[k].z * inv_t - zmax);
+                sum += expf(v[k].w * inv_t - zmax);
+            }
+        }
+    }
+    for (; i < end; ++i) sum += expf(row[i] * inv_t - zmax);
+    return sum;
+}
+
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ uniforms,
                    int* __restrict__ out, int V, float temperature, float top_p, float* __restrict__ probs_scratch) {
@@ -199,12 +229,32 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
     const int seg = (((V + kSampleWarps - 1) / kSampleWarps + 31) / 32) * 32;
     const int seg_lo = min(V, warp * seg), seg_hi = min(V, (warp + 1) * seg);
 
+    // logits are multiplied by 1 / temperature (Sampler.java:85 divides; the difference is one rounding)
+    const float inv_t = 1.0f / temperature;
+    const bool vec = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
     float zmax = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += kSampleThreads) zmax = fmaxf(zmax, row[i] / temperature);
+    if (vec) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V / 4;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += 4 * kSampleThreads) {
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + k * kSampleThreads;
+                v[k] = i < n4 ? r4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) zmax = fmaxf(zmax, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)) * inv_t);
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += kSampleThreads) zmax = fmaxf(zmax, row[i] * inv_t);
+    }
     zmax = block_max(zmax, sh.red);
 
-    float part = 0.f;
-    for (int i = seg_lo + lane; i < seg_hi; i += 32) part += expf(row[i] / temperature - zmax);
+    const int chunk = lane_chunk(seg_lo, seg_hi);
+    const int my_lo = min(seg_hi, seg_lo + lane * chunk), my_hi = min(seg_hi, my_lo + chunk);
+    float part = chunk_exp_sum(row, my_lo, my_hi, inv_t, zmax, vec);
+    const float my_sum = part;
     part = warp_sum(part);
     if (lane == 0) sh.seg_sum[warp] = part;
     if (threadIdx.x == 0) sh.answer = V - 1;
@@ -223,21 +273,25 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
             excl += sh.seg_sum[w];
         }
         if (warp == w_star) {
-            float running = excl;
-            int answer = seg_hi - 1;
-            for (int base = seg_lo; base < seg_hi; base += 32) {
-                const int i = base + lane;
-                float e = i < seg_hi ? expf(row[i] / temperature - zmax) : 0.f;
+            // the lane whose chunk holds the target, then the element inside that chunk
+            float incl = my_sum;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const float n = __shfl_up_sync(0xffffffffu, e, o);
-                    if (lane >= o) e += n;
-                }
-                const unsigned hit = __ballot_sync(0xffffffffu, i < seg_hi && target < running + e);
-                if (hit) { answer = base + __ffs(hit) - 1; break; }
-                running += __shfl_sync(0xffffffffu, e, 31);
+            for (int o = 1; o < 32; o <<= 1) {
+                const float n = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += n;
             }
-            if (lane == 0) sh.answer = answer;
+            const unsigned hit = __ballot_sync(0xffffffffu, my_lo < my_hi && target < excl + incl);
+            if (hit == 0) {
+                if (lane == 0) sh.answer = seg_hi - 1;  // the target lies within rounding of the segment's end
+            } else if (lane == __ffs(hit) - 1) {
+                float running = excl + incl - my_sum;
+                int answer = my_hi - 1;
+                for (int i = my_lo; i < my_hi; ++i) {
+                    running += expf(row[i] * inv_t - zmax);
+                    if (target < running) { answer = i; break; }
+                }
+                sh.answer = answer;
+            }
         }
         __syncthreads();
         if (threadIdx.x == 0) out[blockIdx.x] = sh.answer;
@@ -247,11 +301,93 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
     // nucleus: the kept set is the shortest descending prefix of the candidates whose mass exceeds top_p.
     // The probabilities are written once to scratch (this row's V floats) and read back by every pass.
     float* probs = probs_scratch + (size_t)blockIdx.x * V;
-    for (int i = threadIdx.x; i < V; i += kSampleThreads) probs[i] = expf(row[i] / temperature - zmax) / total;
-    __syncthreads();
     float cutoff = (1.0f - top_p) / (float)(V - 1);
+    unsigned int n_cand = 0;
+    const float inv_total = 1.0f / total;
+    for (int i0 = seg_lo + lane; i0 < seg_hi; i0 += 128) {  // four loads in flight per lane
+        float x[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x[k] = i0 + 32 * k < seg_hi ? row[i0 + 32 * k] : -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (i0 + 32 * k < seg_hi) {
+                const float p = expf(x[k] * inv_t - zmax) * inv_total;
+                probs[i0 + 32 * k] = p;
+                n_cand += p >= cutoff ? 1u : 0u;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) n_cand += __shfl_xor_sync(0xffffffffu, n_cand, o);
+    if (lane == 0) sh.seg_cnt[warp] = n_cand;
+    __syncthreads();
+    // With a peaked distribution few tokens pass the cutoff.  Then they are gathered, in index order, into
+    // shared memory and everything below works on that short list instead of the row.
+    __shared__ __align__(16) float cand_p[kCandidateCap];
+    __shared__ int cand_i[kCandidateCap];
+    unsigned int total_cand = 0, my_first = 0;
+    for (int w = 0; w < kSampleWarps; ++w) {
+        if (w == warp) my_first = total_cand;
+        total_cand += sh.seg_cnt[w];
+    }
+    const bool gathered = total_cand > 0 && total_cand <= (unsigned)kCandidateCap - 3;
+    if (gathered) {
+        unsigned int at = my_first;
+        for (int base = seg_lo; base < seg_hi; base += 32) {
+            const int i = base + lane;
+            const float p = i < seg_hi ? probs[i] : -1.f;  // the element this lane wrote above
+            const bool in = p >= cutoff;
+            const unsigned mask = __ballot_sync(0xffffffffu, in);
+            if (in) {
+                const unsigned int k = at + __popc(mask & ((1u << lane) - 1u));
+                cand_p[k] = p;
+                cand_i[k] = i;
+            }
+            at += __popc(mask);
+        }
+        if (threadIdx.x < 3) cand_p[total_cand + threadIdx.x] = -1.f;  // padding to a multiple of four: below any cutoff
+    }
+    __syncthreads();
+    if (gathered && total_cand <= (unsigned)kSampleThreads) {
+        // A short list (the usual case at low temperature): every thread finds the place of one candidate in
+        // descending order (ties by index) by counting, and one thread walks the ordered list the way the
+        // reference does, adding in float32 (ToppSampler.java:110-156).
+        __shared__ float ord_p[kSampleThreads];
+        __shared__ int ord_i[kSampleThreads];
+        const int n = (int)total_cand;
+        if ((int)threadIdx.x < n) {
+            const float p = cand_p[threadIdx.x];
+            int place = 0;
+            for (int j = 0; j < n; ++j) {
+                const float q = cand_p[j];
+                place += (q > p || (q == p && j < (int)threadIdx.x)) ? 1 : 0;  // the list is in index order
+            }
+            ord_p[place] = p;
+            ord_i[place] = cand_i[threadIdx.x];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float cum = 0.f;
+            int last = n - 1;
+            for (int j = 0; j < n; ++j) {
+                cum += ord_p[j];
+                if (cum > top_p) { last = j; break; }
+            }
+            const float r = u * cum;
+            float cdf = 0.f;
+            int answer = ord_i[last];
+            for (int j = 0; j <= last; ++j) {
+                cdf += ord_p[j];
+                if (r < cdf) { answer = ord_i[j]; break; }
+            }
+            out[blockIdx.x] = answer;
+        }
+        return;
+    }
+    const float* src = gathered ? cand_p : probs;
+    const int n_src = gathered ? (int)((total_cand + 3u) & ~3u) : V;
     const unsigned long long target1 = (unsigned long long)((double)top_p * kMassScale);
-    Crossing first = mass_descent(probs, V, cutoff, target1, sh);
+    Crossing first = mass_descent(src, n_src, cutoff, target1, sh);
     unsigned long long kept_mass;
     if (first.found) {
         const unsigned long long q1 = first.mass_eq / first.cnt_eq;
@@ -269,7 +405,7 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
         target2 = (unsigned long long)((double)u * (double)kept_mass);
         if (target2 >= kept_mass) target2 = kept_mass - 1;
     }
-    Crossing second = mass_descent(probs, V, cutoff, target2, sh);
+    Crossing second = mass_descent(src, n_src, cutoff, target2, sh);
     if (!second.found) {  // cannot happen while target2 < kept mass; keep the last index as the reference's fallback
         if (threadIdx.x == 0) out[blockIdx.x] = V - 1;
         return;
@@ -281,9 +417,12 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
     if (m2 < 1) m2 = 1;
 
     // the m2-th token, in index order, whose probability has exactly the bits key2
+    const int seg2 = (((n_src + kSampleWarps - 1) / kSampleWarps + 31) / 32) * 32;
+    const int lo2 = min(n_src, warp * seg2), hi2 = min(n_src, (warp + 1) * seg2);
+    __syncthreads();  // seg_cnt is used again
     unsigned int cnt = 0;
-    for (int i = seg_lo + lane; i < seg_hi; i += 32) {
-        const float p = probs[i];
+    for (int i = lo2 + lane; i < hi2; i += 32) {
+        const float p = src[i];
         cnt += (p >= cutoff && __float_as_uint(p) == key2) ? 1u : 0u;
     }
 #pragma unroll
@@ -298,12 +437,12 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
     }
     if (warp == w_star) {
         unsigned long long seen = before;
-        int answer = seg_hi - 1;
-        for (int base = seg_lo; base < seg_hi; base += 32) {
+        int answer = hi2 - 1;
+        for (int base = lo2; base < hi2; base += 32) {
             const int i = base + lane;
             bool match = false;
-            if (i < seg_hi) {
-                const float p = probs[i];
+            if (i < hi2) {
+                const float p = src[i];
                 match = p >= cutoff && __float_as_uint(p) == key2;
             }
             const unsigned mask = __ballot_sync(0xffffffffu, match);
@@ -316,7 +455,7 @@ sample_rows_kernel(const float* __restrict__ logits, int ld, const float* __rest
             }
             seen += n;
         }
-        if (lane == 0) sh.answer = answer;
+        if (lane == 0) sh.answer = gathered ? cand_i[min(answer, (int)total_cand - 1)] : answer;
     }
     __syncthreads();
     if (threadIdx.x == 0) out[blockIdx.x] = sh.answer;

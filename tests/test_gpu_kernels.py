@@ -570,17 +570,24 @@ def test_temperature_sampling_is_the_inverse_cdf_in_index_order(V, temperature):
         assert tok == want or min(abs(u - lo), abs(u - float(cdf[tok]))) < 1e-5, (u, tok, want)
 
 
-@pytest.mark.parametrize("V, top_p, temperature", [(9, 0.6, 1.0), (384, 0.95, 0.8), (5003, 0.9, 0.5), (700, 0.05, 1.0)])
-def test_nucleus_sampling_matches_plain(V, top_p, temperature):
+@pytest.mark.parametrize("V, top_p, temperature, spread", [
+    (9, 0.6, 1.0, 3.0), (384, 0.95, 0.8, 3.0), (5003, 0.9, 0.5, 3.0), (700, 0.05, 1.0, 3.0),
+    (20011, 0.9, 1.0, 0.5),      # flat: every token passes the cutoff, the row itself is walked
+    (128256, 0.95, 0.1, 2.0),    # peaked, the reference's default settings: a short list of candidates is gathered
+    (40000, 0.99, 1.0, 1.5)])    # in between: thousands of candidates
+def test_nucleus_sampling_matches_plain(V, top_p, temperature, spread):
     g = torch.Generator().manual_seed(V + 1)
-    logits = torch.randn(1, V, generator=g) * 3
+    logits = torch.randn(1, V, generator=g) * spread
     logits[0, 5] = logits[0, 3]                      # equal probabilities are ordered by index
     us = [0.0, 0.1, 0.33, 0.5, 0.8, 0.95, 0.9999]
     rows = logits.repeat(len(us), 1).cuda()
     out = torch.empty(len(us), dtype=torch.int32, device="cuda")
     ops().sample_rows(rows, torch.tensor(us, dtype=torch.float32, device="cuda"), out, temperature, top_p)
     p = P.temperature_softmax(logits[0], temperature)
-    order = sorted(range(V), key=lambda i: (-float(p[i]), i))
+    n_candidates = int((p >= (1.0 - top_p) / (V - 1)).sum())
+    assert {20011: n_candidates > 4093, 128256: n_candidates < 200, 40000: n_candidates > 1000}.get(V, True), n_candidates
+    pl = p.tolist()
+    order = sorted(range(V), key=lambda i: (-pl[i], i))
     csum = torch.cumsum(p[order].double(), 0)
     for u, tok in zip(us, out.tolist()):
         want = P.sample_top_p(p, top_p, u)
