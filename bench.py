@@ -304,7 +304,7 @@ def main() -> int:
 
     b1 = points.get("decode_b1")
     line = {
-        "metric": "decode tokens/s (Llama-3.2-1B shape, batch 8, context 4096)", "value": round(value, 1),
+        "metric": f"decode tokens/s (Llama-3.2-1B shape, batch {args.batch}, context {args.context})", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": len(times), "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(b1 / PUBLISHED_BEST_1B_TOKS, 2) if b1 else None,
