@@ -321,7 +321,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 }
 
 // ---------------------------------------------------------------------------------------------
-// The pair kernel (head_dim 64, no window): one CTA owns 256 consecutive query tokens as two tiles of 128
+// The pair kernel (head_dim 64 or 128, no window): one CTA owns 256 consecutive query tokens as two tiles of 128
 // and keeps both in flight.  Each tile has its own S and O in tensor memory and its own warpgroup of
 // softmax threads, ONE thread per query row: the thread reads its row of S (128 scores) into registers in
 // one go, so the maximum, the exponentials and the sum need no exchange between threads and no second
@@ -330,17 +330,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // tiles.  The grid is one CTA per SM; each takes (pair, head, sequence) units from a counter, longest first.  The probabilities never touch shared memory: the thread writes its row of P as bfloat16 pairs into
 // tensor memory and O += P V takes its A operand from there.  One CTA per SM (tensor memory, 512 columns:
 // 2 x 128 of S, 2 x 64 of O, 2 x 64 of P; shared memory: Q 32 KB, four stages of K and V 128 KB).
-constexpr int kPairStages = 4;
+// stages of K and V: what fits beside the two Q tiles (head_dim 64: 32 KB + 4 x 32 KB; 128: 64 KB + 2 x 64 KB)
+template <int D> struct PairStages { static constexpr int value = D == 64 ? 4 : 2; };
 constexpr int kPairThreads = 352;                       // TMA warp, MMA warp of tile 0, eight softmax warps, MMA warp of tile 1
 constexpr int kPairMmaWarp1 = kPairThreads / 32 - 1;
 
 template <int D>
 struct PairSmem {
     alignas(1024) __nv_bfloat16 q[2][kFaRows * D];
-    alignas(1024) __nv_bfloat16 k[kPairStages][kFaKeys * D];
-    alignas(1024) __nv_bfloat16 v[kPairStages][2][D * 64];
+    alignas(1024) __nv_bfloat16 k[PairStages<D>::value][kFaKeys * D];
+    alignas(1024) __nv_bfloat16 v[PairStages<D>::value][2][D * 64];
     alignas(8) uint64_t q_full;
-    uint64_t kv_full[kPairStages], kv_empty[kPairStages];
+    uint64_t kv_full[PairStages<D>::value], kv_empty[PairStages<D>::value];
     uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
     uint64_t exp_turn[2];  // the two tiles' softmax threads take turns at the exponentials
     uint32_t tmem_base;
@@ -423,14 +424,19 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                               const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                               const int* __restrict__ page_table, int table_stride, int n_heads, int n_kv_heads,
                               int k_rows_total, int v_rows_total, int n_seqs, int n_pairs) {
-    static_assert(D == 64, "the pair kernel is laid out for head_dim 64");
+    static_assert(D == 64 || D == 128, "the pair kernel is laid out for head_dim 64 and 128");
+    // Tensor memory, 512 columns.  Tile t: S in columns 128 t, O in 256 + D t.  P (bfloat16 pairs, 64 columns): with
+    // head_dim 64 in columns 384 + 64 t; with head_dim 128 nothing is left, so P overwrites the first half of S, which
+    // its thread has read into registers by then, and the next scores are only issued after O += P V.
+    constexpr bool kEarlyScores = D == 64;
+    constexpr int kAtoms = D / 64;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     PairSmem<D>& sm = *reinterpret_cast<PairSmem<D>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        for (int s = 0; s < kPairStages; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 2); }
+        for (int s = 0; s < PairStages<D>::value; ++s) { mbar_init(&sm.kv_full[s], 1); mbar_init(&sm.kv_empty[s], 2); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&sm.s_full[t], 1); mbar_init(&sm.s_free[t], 4); mbar_init(&sm.p_full[t], 4); mbar_init(&sm.pv_done[t], 1);
             mbar_init(&sm.exp_turn[t], 4);
@@ -494,11 +500,14 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
             const int* pages = page_table + (size_t)seq * table_stride;
             const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
             mbar_expect_tx(&sm.q_full, (rows1 > 0 ? 2 : 1) * kFaRows * D * 2);
-            tma_load_2d(sm.q[0], &map_q, head * D, tok0 + q0, &sm.q_full);
-            if (rows1 > 0) tma_load_2d(sm.q[1], &map_q, head * D, tok0 + q0 + kFaRows, &sm.q_full);
+#pragma unroll
+            for (int a = 0; a < kAtoms; ++a) {  // an operand tile is stored as atoms of 64 dims (one swizzle span)
+                tma_load_2d(sm.q[0] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0, &sm.q_full);
+                if (rows1 > 0) tma_load_2d(sm.q[1] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0 + kFaRows, &sm.q_full);
+            }
             for (int j = 0; j < nb; ++j) {
-                const int g = kv_base + j, s = g % kPairStages;
-                if (g >= kPairStages && !mbar_wait(&sm.kv_empty[s], ((g / kPairStages) - 1) & 1, abort_flag)) {
+                const int g = kv_base + j, s = g % PairStages<D>::value;
+                if (g >= PairStages<D>::value && !mbar_wait(&sm.kv_empty[s], ((g / PairStages<D>::value) - 1) & 1, abort_flag)) {
                     *abort_flag = 1; atomicCAS(&g_fa_status, 0, (11 << 8) | s); break;
                 }
                 mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
@@ -507,7 +516,10 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     const int lp = j * 2 + h;  // logical page; pages the sequence does not have are read as zeros
                     const bool have = lp < n_pages_seq;
                     const int page = have ? pages[lp] : 0;
-                    tma_load_2d(sm.k[s] + h * 64 * 64, &map_k, 0, have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
+#pragma unroll
+                    for (int a = 0; a < kAtoms; ++a)
+                        tma_load_2d(sm.k[s] + a * kFaKeys * 64 + h * 64 * 64, &map_k, a * 64,
+                                    have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
                     tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
                 }
             }
@@ -528,8 +540,8 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
             }
             auto need_block = [&](int j) {
                 while (ok && kv_ready <= kv_base + j) {
-                    const int s = kv_ready % kPairStages;
-                    if (!mbar_wait(&sm.kv_full[s], (kv_ready / kPairStages) & 1, abort_flag)) {
+                    const int s = kv_ready % PairStages<D>::value;
+                    if (!mbar_wait(&sm.kv_full[s], (kv_ready / PairStages<D>::value) & 1, abort_flag)) {
                         *abort_flag = 1; atomicCAS(&g_fa_status, 0, (13 << 8) | s); ok = false;
                     } else {
                         ++kv_ready;
@@ -538,11 +550,12 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             };
             // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
-            const uint64_t q_desc = umma_desc(sm.q[t]);
             auto scores = [&](int j) {  // S = Q K_j^T
-                const uint64_t kd = umma_desc(sm.k[(kv_base + j) % kPairStages]);
+                const __nv_bfloat16* kt = sm.k[(kv_base + j) % PairStages<D>::value];
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem + 128 * t, q_desc + 2 * kk, kd + 2 * kk, idesc_s, kk != 0);
+                for (int kk = 0; kk < D / 16; ++kk)
+                    umma_bf16(tmem + 128 * t, umma_desc(sm.q[t] + (kk / 4) * kFaRows * 64) + 2 * (kk % 4),
+                              umma_desc(kt + (kk / 4) * kFaKeys * 64) + 2 * (kk % 4), idesc_s, kk != 0);
                 umma_commit(&sm.s_full[t]);
             };
             if (ok) {
@@ -550,7 +563,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 if (ok) scores(0);
             }
             for (int i = 0; i < nbt && ok; ++i) {
-                if (i + 1 < nbt) {
+                if (kEarlyScores && i + 1 < nbt) {
                     if (!mbar_wait(&sm.s_free[t], (tile_blocks[t] + i) & 1, abort_flag)) {
                         *abort_flag = 1; atomicCAS(&g_fa_status, 0, (17 << 8) | t); ok = false; break;
                     }
@@ -562,13 +575,18 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int s = (kv_base + i) % kPairStages;
+                const int s = (kv_base + i) % PairStages<D>::value;
                 const uint64_t vd0 = umma_desc(sm.v[s][0]), vd1 = umma_desc(sm.v[s][1]);
 #pragma unroll
                 for (int kk = 0; kk < kFaKeys / 16; ++kk)  // O += P V_i; 16 keys = 8 columns of P
-                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + 384 + 64 * t + 8 * kk, (kk < 4 ? vd0 : vd1) + 2 * (kk % 4),
-                                     idesc_o, (i | kk) != 0);
+                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + (D == 64 ? 384 + 64 * t : 128 * t) + 8 * kk,
+                                     (kk < 4 ? vd0 : vd1) + 2 * (kk % 4), idesc_o, (i | kk) != 0);
                 umma_commit(&sm.pv_done[t]);
+                if (!kEarlyScores && i + 1 < nbt) {  // P lies where the next scores go: they follow the product that reads it
+                    need_block(i + 1);
+                    if (!ok) break;
+                    scores(i + 1);
+                }
                 // a stage is free after two arrivals: one from each tile that reads the block, two from a lone reader
                 umma_commit(&sm.kv_empty[s]);
                 if (i >= nb_other) umma_commit(&sm.kv_empty[s]);
@@ -582,7 +600,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
             const int p_first = start + q0 + kFaRows * t;
             const int pos = p_first + min(r, max(rows_t, 1) - 1);  // rows past the end mirror the last one (never stored)
             const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);
-            const uint32_t tmem_s = tmem + 128 * t, tmem_o = tmem + 256 + D * t, tmem_p = tmem + 384 + 64 * t;
+            const uint32_t tmem_s = tmem + 128 * t, tmem_o = tmem + 256 + D * t, tmem_p = D == 64 ? tmem + 384 + 64 * t : tmem_s;
             float m_ref = -INFINITY, l = 0.f;
             bool ok = true;
             for (int j = 0; j < nbt; ++j) {
@@ -797,13 +815,14 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
 }  // namespace b200
 
 namespace b200 {
+template <int D>
 static int launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* cu_seqlens,
                        const int* kv_lens, const int* page_table, int table_stride, int n_seqs, int max_q_len, int n_heads,
                        int n_kv_heads, int k_rows, int v_rows, cudaStream_t stream) {
-    const size_t smem = sizeof(PairSmem<64>) + 1024;
+    const size_t smem = sizeof(PairSmem<D>) + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_pair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_prefill_pair_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
     }
@@ -816,7 +835,7 @@ static int launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return kErrBadArgument;
     const int grid = (int)(units < n_sms ? units : n_sms);  // one CTA per SM; each takes units until none are left
-    return launch_pdl(attention_prefill_pair_kernel<64>, dim3(grid), dim3(kPairThreads), smem, stream, mq, mk, mv,
+    return launch_pdl(attention_prefill_pair_kernel<D>, dim3(grid), dim3(kPairThreads), smem, stream, mq, mk, mv,
                       (__nv_bfloat16*)out, cu_seqlens, kv_lens, page_table, table_stride, n_heads, n_kv_heads, k_rows, v_rows,
                       n_seqs, n_pairs);
 }
@@ -843,9 +862,13 @@ extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_
         !make_map_2d(&mk, k_pool, k_rows, head_dim, head_dim, 64, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, head_dim))
         return kErrUnsupportedSize;
     // tiles in pairs when there are enough pairs to give every SM one (fewer: the single-tile kernel fills more SMs)
-    if (head_dim == 64 && window <= 0 && (long long)((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows)) * n_heads * n_seqs >= 148)
-        return launch_pair(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
-                           n_kv_heads, (int)k_rows, (int)v_rows, stream);
+    if (window <= 0 && (long long)((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows)) * n_heads * n_seqs >= 148) {
+        if (head_dim == 64)
+            return launch_pair<64>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
+                                   n_kv_heads, (int)k_rows, (int)v_rows, stream);
+        return launch_pair<128>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
+                                n_kv_heads, (int)k_rows, (int)v_rows, stream);
+    }
     if (head_dim == 64)
         return launch_fa<64>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
                              n_kv_heads, window, (int)k_rows, (int)v_rows, stream);

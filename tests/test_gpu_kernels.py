@@ -489,11 +489,12 @@ def test_attention_prefill_on_tcgen05_against_plain(H, KVH, window, D):
     torch.testing.assert_close(out.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * float(ref.abs().max()))
 
 
-def test_attention_prefill_pairs_of_tiles_against_plain():
-    """With enough work the head-size-64 kernel takes query tiles in pairs, one CTA per SM walking through many
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_prefill_pairs_of_tiles_against_plain(D):
+    """With enough work the tensor-memory kernel takes query tiles in pairs, one CTA per SM walking through many
     (pair, head, sequence) units: long and short sequences, a tile pair whose second tile is empty or partial,
     prefixes that are no multiple of the block, more units than SMs so that every CTA handles several."""
-    H, KVH, D = 16, 4, 64
+    H, KVH = 16, 4
     kv_lens = [1500, 129, 128, 257, 700, 64, 1, 385]
     q_starts = [0, 0, 0, 1, 300, 63, 0, 130]
     k_pool, v_pool, table, dense = _paged_setup(torch.bfloat16, len(kv_lens), kv_lens, KVH, D, n_pages=70, seed=11)
