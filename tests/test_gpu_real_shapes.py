@@ -67,3 +67,55 @@ def test_layers_of_real_size(session_tmp, name, dtype):
             check(out[i:i + 1], i, slice(h + t, h + t + 1), f"{name} decoded token {t} of {i}")
     for s in slots:
         cache.release(s)
+
+
+@pytest.mark.parametrize("name", ["1B", "3B"])
+def test_long_prompts_of_real_size(session_tmp, name):
+    """Prompts of 700, 260 and 130 tokens with 32 (24) heads make more attention work than there are SMs: the prompt
+    step takes the kernel that handles query tiles in pairs (head sizes 64 and 128), the decode steps after it cut
+    the 700 keys into spans.  One layer, bfloat16, the yardstick of the test above."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+    from gpullama3.java_b200.kernels import ops
+
+    shape = SHAPES["3B"] if name == "3B" else dict(
+        hidden_size=2048, num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192,
+        rope_scaling=SHAPES["3B"]["rope_scaling"], tie_word_embeddings=True)
+    cfg_json = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, vocab_size=1000, rope_theta=500000.0,
+                    rms_norm_eps=1e-5, max_position_embeddings=8192, **shape)
+    d = make_model_dir(session_tmp, cfg_json, seed=33)
+    cfg, w = plain_inputs(d)
+    lengths = [700, 260, 130]
+    assert -(-max(lengths) // 256) * cfg["num_attention_heads"] * len(lengths) >= 148
+    prompts = random_prompts(1000, lengths, seed=9)
+    tail = 3
+    refs = [P.forward(cfg, w, p, round_to=torch.bfloat16) for p in prompts]
+    exact = [P.forward(cfg, w, p, dtype=torch.float64) for p in prompts]
+    scale = max(float(e.abs().max()) for e in exact)
+
+    def check(got, i, rows, what):
+        g, e, r = got.cpu().double(), exact[i][rows].double(), refs[i][rows].double()
+        assert torch.isfinite(g).all(), what
+        err, noise = float((g - e).abs().max()), float((r - e).abs().max())
+        assert err <= 2.0 * noise + 2e-5 * scale, f"{what}: max err {err:.3e}, plain noise {noise:.3e}, scale {scale:.3e}"
+        err_m, noise_m = float((g - e).abs().mean()), float((r - e).abs().mean())
+        assert err_m <= 2.0 * noise_m + 2e-6 * scale, f"{what}: mean err {err_m:.3e}, plain noise {noise_m:.3e}"
+
+    model = load_model(d, torch.bfloat16)
+    cache = model.new_cache(64 * 20)
+    step = StepFunction(model, cache)
+    slots = [cache.acquire() for _ in prompts]
+    heads = [n - tail for n in lengths]
+    wanted = [list(range(0, h, 37)) + [h - 1] for h in heads]      # rows spread over every tile, and the last one
+    out = step([SequenceInput(s, p[:h], rows) for s, p, h, rows in zip(slots, prompts, heads, wanted)])
+    assert ops.attention_prefill_tc_status() == 0
+    off = 0
+    for i, rows in enumerate(wanted):
+        check(out[off:off + len(rows)], i, rows, f"{name} prompt {i}")
+        off += len(rows)
+    for t in range(tail):
+        out = step([SequenceInput(s, [p[h + t]], [0]) for s, p, h in zip(slots, prompts, heads)])
+        for i, h in enumerate(heads):
+            check(out[i:i + 1], i, slice(h + t, h + t + 1), f"{name} decoded token {t} of {i}")
+    for s in slots:
+        cache.release(s)
