@@ -162,3 +162,27 @@ def test_sampling_params_are_validated_like_the_reference():
     with pytest.raises(ValueError):
         SamplingParams(top_p=1.5)
     assert SamplingParams().greedy and not SamplingParams(temperature=0.1).greedy
+
+
+def test_decode_steps_go_to_the_step_and_draw_call_when_it_is_offered():
+    """A step function may offer ``decode_and_sample`` (one call that runs a decode step and draws the tokens);
+    the loop then uses it for every decode step, passes it the draws' identities, and falls back to step-then-
+    sample for the steps it declines (returns None).  The prompt step is always sampled by the sampler."""
+    gen, step, cache = make()
+    fused_calls = []
+
+    def decode_and_sample(inputs, sampler, requests, draws):
+        if len(fused_calls) % 2 == 1:          # decline every other step
+            fused_calls.append(None)
+            return None
+        logits = step(inputs)
+        fused_calls.append((list(requests), list(draws)))
+        return logits.argmax(dim=-1).tolist()
+
+    step.decode_and_sample = decode_and_sample
+    prompts = [[1, 2, 3], [4] * 11]
+    res = gen.generate(prompts, 5, SamplingParams(), request_ids=[7, 9])
+    assert [r.tokens for r in res] == [expected_tokens(p, 5) for p in prompts]
+    assert len(fused_calls) == 4 and fused_calls[1] is None and fused_calls[3] is None
+    assert fused_calls[0] == ([7, 9], [1, 1]) and fused_calls[2] == ([7, 9], [3, 3])
+    assert cache.live_slots() == []
