@@ -126,10 +126,13 @@ class SequenceCache:
             else:
                 raise TypeError(f"cache entry needs must be KVCacheNeed or StateNeed, got {need!r}")
         self._slot: dict[int, _Slot] = {}
+        # counts acquisitions and releases: while it stands still, a slot number means the same sequence
+        self.ownership_changes = 0
 
     # ---- slots
     def acquire(self) -> int:
         slot = self.slots.acquire()
+        self.ownership_changes += 1
         self._slot[slot] = _Slot(len(self.kv_groups))
         for g in self.state_groups:
             g.data[:, slot].zero_()
@@ -139,6 +142,7 @@ class SequenceCache:
         if not self.slots.is_live(slot):
             raise CacheError(f"slot {slot} is not live")
         s = self._slot.pop(slot)
+        self.ownership_changes += 1
         for g, pages in zip(self.kv_groups, s.pages):
             g.pool.free([p for p in pages if p >= 0])
         self.slots.release(slot)

@@ -118,19 +118,22 @@ class DecodeGraph:
         self.d2h_bytes = n_seqs * 4 if sampler is not None else 0
         self.last_slots: list[int] | None = None
         self.last_pos: list[int] | None = None
+        self.last_owners = -1                         # the cache's ownership count at the last refresh
         kv_heads = [g.need.n_kv_heads for g in cache.kv_groups] or [1]
         self.kv_capacity = max(widths, default=1) * PAGE_TOKENS
         self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), self.kv_capacity)
 
     def refresh(self, slots, start_pos, tokens, uniforms=None) -> None:
-        """Fill the staging buffer for this step.  A step that continues the one before (same slots, every
-        position one further) only rewrites what moved: tokens, positions, lengths, and the table row of a
-        sequence that has just entered a new page."""
+        """Fill the staging buffer for this step.  A step that continues the one before (same slots, still the
+        same sequences in them, every position one further) only rewrites what moved: tokens, positions,
+        lengths, and the table row of a sequence that has just entered a new page."""
         if self.pending:
             self.done.synchronize()  # the run before must have read the staging buffer
             self.pending = False
         n, h = self.n, self.host_np
-        if self.last_slots == slots and all(p == q + 1 for p, q in zip(start_pos, self.last_pos)):
+        owners = getattr(self.cache, "ownership_changes", None)
+        if (self.last_slots == slots and owners is not None and owners == self.last_owners
+                and all(p == q + 1 for p, q in zip(start_pos, self.last_pos))):
             h[0:n] = tokens
             h[n:2 * n] = start_pos
             h[4 * n + 1:5 * n + 1] = h[n:2 * n] + 1
@@ -145,7 +148,7 @@ class DecodeGraph:
             np.concatenate(pieces, out=h[:self.uniform_offset])
         if self.draws:
             h[self.uniform_offset:self.uniform_offset + n] = np.asarray(uniforms, dtype=np.float32).view(np.int32)
-        self.last_slots, self.last_pos = list(slots), list(start_pos)
+        self.last_slots, self.last_pos, self.last_owners = list(slots), list(start_pos), owners
 
     def _launches(self, slots, start_pos):
         """The step as it is issued and as it is recorded: staging buffer in, model, draw, tokens out."""

@@ -139,3 +139,37 @@ def test_a_step_that_does_not_fit_changes_nothing(setup):
             step(bad)
     again = step([SequenceInput(b, requests["r0"][:20], [19])]).cpu()       # the other slot, same tokens, same logits
     assert torch.equal(first, again)
+
+
+def test_slots_given_to_new_sequences_at_the_position_the_old_ones_stopped(session_tmp):
+    """A recorded decode step only rewrites what moved when it continues the step before.  New sequences that get
+    the same slot numbers, with other pages, and happen to stand one position after the old ones' last step must
+    not be taken for a continuation: their page tables have to reach the device."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    cfg_json, norm_std = TINY["A"]
+    d = make_model_dir(session_tmp, cfg_json, seed=41, norm_std=norm_std, scale=PEAKED)
+    cfg, w = plain_inputs(d)
+    model = load_model(d, torch.bfloat16)
+    cache = model.new_cache(64 * 8, max_slots=4)
+    step = StepFunction(model, cache)
+    old = random_prompts(cfg["vocab_size"], [8, 8], seed=1)
+    a, b, keep = cache.acquire(), cache.acquire(), cache.acquire()
+    step([SequenceInput(a, old[0][:5], []), SequenceInput(b, old[1][:5], [])])
+    for t in range(5, 8):                                   # decode steps at positions 5, 6, 7 (the second one is recorded)
+        step([SequenceInput(a, [old[0][t]], [0]), SequenceInput(b, [old[1][t]], [0])])
+    cache.release(a)
+    cache.release(b)
+    filler = random_prompts(cfg["vocab_size"], [130], seed=2)[0]
+    step([SequenceInput(keep, filler, [])])                 # takes the pages the old sequences gave back
+    new_slots = [cache.acquire(), cache.acquire()]
+    new = random_prompts(cfg["vocab_size"], [9, 9], seed=3)
+    by_slot = dict(zip(sorted(new_slots), new))             # in the order of the old step: slots a, b
+    assert sorted(new_slots) == sorted([a, b])
+    step([SequenceInput(s, by_slot[s][:8], []) for s in (a, b)])
+    out = step([SequenceInput(s, [by_slot[s][8]], [0]) for s in (a, b)])   # position 8 = the old last position + 1
+    for i, s in enumerate((a, b)):
+        ref = plain_llama.forward(cfg, w, by_slot[s], round_to=torch.bfloat16)[-1]
+        assert_close_logits(out[i], ref, torch.bfloat16, f"sequence in slot {s}")
+    cache.check_invariants()
