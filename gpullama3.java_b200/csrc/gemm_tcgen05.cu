@@ -208,8 +208,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+static int sm_count() {
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0)
+            n_sms = 148;
+    }
+    return n_sms;
+}
+
+// Width of the tiles for an M x N product.  The widest tile moves the fewest operand bytes per flop and wins whenever
+// its tiles fill the SMs; a product of few tiles (a few hundred tokens, a narrow output) leaves SMs idle, and narrower
+// tiles, each finished sooner, end it earlier.  A CTA's tiles run one after another, so the estimate is the number of
+// rounds times the time of one tile, which follows the bytes a tile's k-step brings in (48, 32, 24 KB) rather than
+// its tensor-core cycles; the relative times below are measured (M 192..4096 at widths 2048..16384).  Ties go to
+// the wider tile.
+static int tile_width_for(int M, int N) {
+    const long long tiles_m = (M + BM - 1) / BM;
+    const int widths[3] = {256, 128, 64}, tile_time[3] = {128, 85, 66};
+    int best = 256;
+    long long best_time = 0;
+    for (int i = 0; i < 3; ++i) {
+        const long long tiles = tiles_m * ((N + widths[i] - 1) / widths[i]);
+        const long long time = ((tiles + sm_count() - 1) / sm_count()) * tile_time[i];
+        if (i == 0 || time < best_time) { best = widths[i]; best_time = time; }
+    }
+    return best;
+}
+
 template <int BN, int STAGES, int EPI, typename TC>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
@@ -218,16 +249,19 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int 
             return (int)cudaGetLastError();
         configured = true;
     }
-    static int n_sms = 0;
-    if (n_sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0)
-            n_sms = 148;
-    }
+    const int n_sms = sm_count();
     const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(n_tiles < n_sms ? n_tiles : n_sms));
     return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, (TC*)C, ldc, M, N, K);
-    return launch_status();
+}
+
+template <int BN, int STAGES>
+static int launch_width(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N, int K,
+                        int epilogue, cudaStream_t stream) {
+    if (epilogue == 2) return launch_tc<BN, STAGES, 2, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    if (epilogue == 1) return launch_tc<BN, STAGES, 1, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    if (c_dtype == kF32) return launch_tc<BN, STAGES, 0, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    return launch_tc<BN, STAGES, 0, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
 }
 
 }  // namespace b200
@@ -241,19 +275,19 @@ extern "C" int b200_gemm_tcgen05_status() {
 }
 
 // A, W bfloat16; C bfloat16 or float32; epilogue 0 store, 1 residual add (C float32), 2 gated SiLU (C bfloat16).
+// tile_width: 256, 128 or 64 output columns per tile; 0 lets the product's shape decide.
 extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                 int N, int K, int epilogue, cudaStream_t stream) {
+                                 int N, int K, int epilogue, int tile_width, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
-    constexpr int BN = 256, STAGES = 4;
-    CUtensorMap ma, mw;
-    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;
-    if (epilogue == 2) return launch_tc<BN, STAGES, 2, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, stream);
-    if (epilogue == 1) return launch_tc<BN, STAGES, 1, float>(ma, mw, C, ldc, M, N, K, stream);
-    if (c_dtype == kF32) return launch_tc<BN, STAGES, 0, float>(ma, mw, C, ldc, M, N, K, stream);
-    return launch_tc<BN, STAGES, 0, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, stream);
+    // a stage holds 16 KB of A and BN / 8 KB of W: the narrower the tile, the deeper the ring
+    const int width = tile_width > 0 ? tile_width : tile_width_for(M, N);
+    if (width == 256) return launch_width<256, 4>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+    if (width == 128) return launch_width<128, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+    if (width == 64) return launch_width<64, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+    return kErrBadArgument;
 }

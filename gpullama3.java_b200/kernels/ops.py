@@ -45,7 +45,7 @@ _SIGNATURES = {
                                                 c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int]),
+                                           c_int, c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -104,7 +104,16 @@ def _check(status: int, name: str) -> None:
         raise KernelError(f"{name}: {what}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  Asked for at every launch (a graph capture changes it), so through the
+    two plain C calls where this torch has them: building a ``torch.cuda.Stream`` object costs several microseconds,
+    which a pass of a hundred short kernels feels."""
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -262,9 +271,11 @@ def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilog
         "gemm_decode_linked")
 
 
-def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> bool:
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
+                 tile_width: int = 0) -> bool:
     """The prefill matrix product on tcgen05 tensor cores (bfloat16 operands, rows 16-byte aligned).
-    Returns False, having done nothing, for operands it does not take."""
+    ``tile_width``: 256, 128 or 64 output columns per tile; 0 lets the shape decide (narrower tiles when the
+    widest would leave SMs without one).  Returns False, having done nothing, for operands it does not take."""
     M, K = a.shape
     if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or K < 8 or a.stride(1) != 1
             or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
@@ -276,7 +287,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
     assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
     _check(_fn("b200_gemm_tcgen05")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
-                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, _stream()), "gemm_tcgen05")
+                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, tile_width, _stream()),
+           "gemm_tcgen05")
     return True
 
 

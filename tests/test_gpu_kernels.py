@@ -315,10 +315,17 @@ def test_gemm_decode_halves_of_a_split_norm(M, hidden, K, N2, w_dtype):
 
 @pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 512), (1, 8, 8), (100, 300, 72), (129, 257, 200),
                                      (300, 1030, 2048), (2048, 512, 1024), (65, 3072, 2048)])
-def test_gemm_tcgen05_and_its_epilogues(M, N, K):
+@pytest.mark.parametrize("width", [0, 256, 128, 64])
+def test_gemm_tcgen05_and_its_epilogues(M, N, K, width):
     """The TMA + tcgen05 kernel at tile-exact sizes, at ragged edges in M, N and K, and with several
-    waves of tiles; every internal wait must have completed (status word 0)."""
+    waves of tiles, for each width of tile and for the width the shape picks (0); every internal wait must
+    have completed (status word 0)."""
+    import functools
     o = ops()
+    real = o.gemm_tcgen05
+    o = type("WithWidth", (), {k: getattr(o, k) for k in ("EPILOGUE_STORE", "EPILOGUE_RESIDUAL_ADD", "EPILOGUE_GATED_SILU",
+                                                        "gemm_tcgen05_status")})
+    o.gemm_tcgen05 = staticmethod(functools.partial(real, tile_width=width))
     g = torch.Generator().manual_seed(M + N + K)
     a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
