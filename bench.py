@@ -244,7 +244,7 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "AskMyu/GPULlama3.java is a Java 21 + TornadoVM application (no Python package, no JDK, Maven or "
-                          "TornadoVM SDK on this image, no network); pip install of /root/reference finds no project to build"}))
+                          "TornadoVM SDK on this image, no network); pip install of the reference checkout finds no Python project to build"}))
         return 0
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
