@@ -208,6 +208,176 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same product for a few hundred tokens and a long K (the down product of a short prompt): its few tiles
+// leave most SMs idle and each CTA walks the whole of K alone.  Here the K range of a tile is cut into 2 or 4
+// spans, one CTA each, which form a thread-block cluster.  Every CTA accumulates its span in tensor memory, copies
+// the 128 x 128 partial tile to its shared memory (where the ring was), and after a cluster barrier each CTA adds,
+// for its share of the tile's rows, the partial tiles in span order through distributed shared memory and runs
+// the epilogue on whole rows (512 contiguous bytes per warp).  No atomics: the result does not depend on timing.
+constexpr int kSplitBN = 128;
+constexpr int kSplitStages = 6;
+constexpr int kSplitPitch = kSplitBN + 4;  // floats per row of the partial tile: float4 stores of 8 rows hit 32 banks
+
+__device__ __forceinline__ float4 cluster_load_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+template <int EPI, typename TC>
+__global__ void __launch_bounds__(kGemmTcThreads, 1)
+gemm_tcgen05_spans_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          TC* __restrict__ C, int ldc, int M, int N, int K, int blocks_per_span) {
+    constexpr int BN = kSplitBN, STAGES = kSplitStages;
+    using Smem = GemmSmem<BN, STAGES>;
+    static_assert(sizeof(float) * BM * kSplitPitch <= sizeof(Smem::a), "the partial tile fits in the stages of A");
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int tile = blockIdx.x, span = blockIdx.y, n_spans = gridDim.y;  // the cluster is (1, n_spans, 1)
+    const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+    const int kb_total = (K + BK - 1) / BK;
+    const int kb_begin = span * blocks_per_span;
+    const int k_iters = max(0, min(kb_total, kb_begin + blocks_per_span) - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        mbar_init(&sm.acc_full[0], 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+    float* partial = reinterpret_cast<float*>(sm.a);  // [BM][kSplitPitch] once the accumulator is complete
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        for (int k = 0; k < k_iters; ++k) {
+            const int s = k % STAGES;
+            if (k >= STAGES && !mbar_wait(&sm.empty[s], ((k / STAGES) - 1) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (5 << 8) | s); break;
+            }
+            mbar_expect_tx(&sm.full[s], (BM + BN) * BK * 2);
+            tma_load_2d(sm.a[s], &map_a, (kb_begin + k) * BK, m0, &sm.full[s]);
+            tma_load_2d(sm.b[s], &map_w, (kb_begin + k) * BK, n0, &sm.full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        bool ok = true;
+        for (int k = 0; k < k_iters; ++k) {
+            const int s = k % STAGES;
+            if (!mbar_wait(&sm.full[s], (k / STAGES) & 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (6 << 8) | s); ok = false; break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) umma_bf16(tmem, ad + 2 * kk, bd + 2 * kk, idesc, (k | kk) != 0);
+            umma_commit(&sm.empty[s]);
+        }
+        if (ok && k_iters > 0) umma_commit(&sm.acc_full[0]);
+    } else if (warp >= 2) {
+        // the accumulator's rows to shared memory: warp w reads TMEM lanes 32 * (w % 4) .. + 31, a row per thread
+        const int quarter = warp & 3, r = quarter * 32 + lane;
+        bool ok = true;
+        if (k_iters > 0) {
+            ok = mbar_wait(&sm.acc_full[0], 0, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (7 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                if (k_iters > 0) {
+                    tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                }
+                float4* dst = reinterpret_cast<float4*>(partial + (size_t)r * kSplitPitch + c0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();     // the roles have joined again: whole warps reach the cluster barrier
+    cluster_sync_all();  // every span's partial tile is in its CTA's shared memory
+    if (warp >= 2) {
+        const int rows_here = BM / n_spans;  // n_spans is 2 or 4
+        const int col = n0 + 4 * lane;
+        uint32_t peer[4];
+#pragma unroll
+        for (int sp = 0; sp < 4; ++sp) peer[sp] = cluster_peer_address(partial + 4 * lane, sp < n_spans ? sp : 0);
+#pragma unroll 2
+        for (int i = warp - 2; i < rows_here; i += 4) {
+            const int r = span * rows_here + i, row = m0 + r;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int sp = 0; sp < 4; ++sp) {
+                if (sp < n_spans) {
+                    const float4 p = cluster_load_f32x4(peer[sp] + (uint32_t)r * kSplitPitch * 4);
+                    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+                }
+            }
+            if (row >= M || col >= N) continue;
+            const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+            if (EPI == 2) {  // columns are gate, up, gate, up
+                TC* dst = C + (size_t)row * ldc + (col >> 1);
+                const float h0 = (v[0] / (1.0f + expf(-v[0]))) * v[1], h1 = (v[2] / (1.0f + expf(-v[2]))) * v[3];
+                if (col + 4 <= N && ((uintptr_t)dst & 3) == 0 && sizeof(TC) == 2) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(h0, h1);
+                    *reinterpret_cast<__nv_bfloat162*>(dst) = h;
+                } else {
+                    if (col + 1 < N) dst[0] = from_f32<TC>(h0);
+                    if (col + 3 < N) dst[1] = from_f32<TC>(h1);
+                }
+            } else {
+                TC* dst = C + (size_t)row * ldc + col;
+                const bool whole = col + 4 <= N && ((uintptr_t)dst & (sizeof(TC) * 4 - 1)) == 0;
+                if (EPI == 1) {  // C is the float32 residual stream
+                    float* d = reinterpret_cast<float*>(dst);
+                    if (whole) {
+                        float4 x = *reinterpret_cast<float4*>(d);
+                        x.x += v[0]; x.y += v[1]; x.z += v[2]; x.w += v[3];
+                        *reinterpret_cast<float4*>(d) = x;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) if (col + j < N) d[j] += v[j];
+                    }
+                } else if (whole && sizeof(TC) == 4) {
+                    *reinterpret_cast<float4*>(dst) = acc;
+                } else if (whole) {
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) if (col + j < N) dst[j] = from_f32<TC>(v[j]);
+                }
+            }
+        }
+    }
+    cluster_sync_all();  // no CTA leaves while a peer may still read its shared memory
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    }
+}
+
 static int sm_count() {
     static int n_sms = 0;
     if (n_sms == 0) {
@@ -264,6 +434,45 @@ static int launch_width(const void* A, int lda, const void* W, int ldw, void* C,
     return launch_tc<BN, STAGES, 0, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
 }
 
+// Spans of K per tile for the cluster kernel (1: the plain kernel).  Worth it when the 128 x 128 tiles times the spans
+// still fit the SMs, a span keeps 8 k-steps or more, and the estimate (k-steps of a span plus 12 for the cluster's
+// barriers and the second pass over the tile, in the units of tile_width_for) beats the plain kernel's.
+static int k_spans_for(int M, int N, int K) {
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + kSplitBN - 1) / kSplitBN);
+    const int kb = (K + BK - 1) / BK;
+    const int widths[3] = {256, 128, 64}, tile_time[3] = {128, 85, 66};
+    long long plain = 0;
+    for (int i = 0; i < 3; ++i) {
+        const long long t = (long long)((M + BM - 1) / BM) * ((N + widths[i] - 1) / widths[i]);
+        const long long time = ((t + sm_count() - 1) / sm_count()) * tile_time[i] * kb;
+        if (i == 0 || time < plain) plain = time;
+    }
+    for (int spans = 4; spans >= 2; spans -= 2) {
+        if (tiles * spans > sm_count() || kb / spans < 8) continue;
+        if ((long long)((kb + spans - 1) / spans + 12) * 85 < plain) return spans;
+    }
+    return 1;
+}
+
+template <int EPI, typename TC>
+static int launch_spans(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int spans,
+                        cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, kSplitBN)) return kErrUnsupportedSize;
+    const size_t smem = sizeof(GemmSmem<kSplitBN, kSplitStages>) + 1024;
+    static bool configured = false;
+    auto kernel = gemm_tcgen05_spans_kernel<EPI, TC>;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        configured = true;
+    }
+    const int kb = (K + BK - 1) / BK;
+    const int tiles = ((N + kSplitBN - 1) / kSplitBN) * ((M + BM - 1) / BM);
+    return launch_pdl_cluster(kernel, dim3(tiles, spans), dim3(kGemmTcThreads), smem, stream, dim3(1, spans, 1), true,
+                              ma, mw, (TC*)C, ldc, M, N, K, (kb + spans - 1) / spans);
+}
+
 }  // namespace b200
 
 // Reads and clears the status word of the tensor-core GEMM (0 = every wait completed).  Synchronises.
@@ -275,15 +484,32 @@ extern "C" int b200_gemm_tcgen05_status() {
 }
 
 // A, W bfloat16; C bfloat16 or float32; epilogue 0 store, 1 residual add (C float32), 2 gated SiLU (C bfloat16).
+// Spans of K that the product's shape asks for (1: none).
+extern "C" int b200_gemm_tcgen05_k_spans(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 1;
+    return b200::k_spans_for(M, N, K);
+}
+
 // tile_width: 256, 128 or 64 output columns per tile; 0 lets the product's shape decide.
+// k_spans: 2 or 4 cuts K among the CTAs of a cluster (128-column tiles; tile_width is then ignored), 1 never does,
+// 0 lets the shape decide.
 extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                 int N, int K, int epilogue, int tile_width, cudaStream_t stream) {
+                                 int N, int K, int epilogue, int tile_width, int k_spans, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
     if (epilogue < 0 || epilogue > 2 || (epilogue == 1 && c_dtype != kF32) || (epilogue == 2 && ((N & 1) || c_dtype != kBF16)))
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
+    if (k_spans != 0 && k_spans != 1 && k_spans != 2 && k_spans != 4) return kErrBadArgument;
+    const int spans = k_spans > 0 ? k_spans : (tile_width > 0 ? 1 : k_spans_for(M, N, K));
+    if (spans > 1) {
+        if ((K + BK - 1) / BK < spans) return kErrBadArgument;
+        if (epilogue == 2) return launch_spans<2, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, spans, stream);
+        if (epilogue == 1) return launch_spans<1, float>(A, lda, W, ldw, C, ldc, M, N, K, spans, stream);
+        if (c_dtype == kF32) return launch_spans<0, float>(A, lda, W, ldw, C, ldc, M, N, K, spans, stream);
+        return launch_spans<0, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, spans, stream);
+    }
     // a stage holds 16 KB of A and BN / 8 KB of W: the narrower the tile, the deeper the ring
     const int width = tile_width > 0 ? tile_width : tile_width_for(M, N);
     if (width == 256) return launch_width<256, 4>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);

@@ -45,7 +45,7 @@ _SIGNATURES = {
                                                 c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int, c_int]),
+                                           c_int, c_int, c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -272,24 +272,33 @@ def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilog
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
-                 tile_width: int = 0) -> bool:
+                 tile_width: int = 0, k_spans: int = 0) -> bool:
     """The prefill matrix product on tcgen05 tensor cores (bfloat16 operands, rows 16-byte aligned).
     ``tile_width``: 256, 128 or 64 output columns per tile; 0 lets the shape decide (narrower tiles when the
-    widest would leave SMs without one).  Returns False, having done nothing, for operands it does not take."""
+    widest would leave SMs without one).  ``k_spans``: 2 or 4 cuts K among the CTAs of a cluster, which add their
+    partial tiles in a fixed order (few tiles, long K); 1 never; 0 lets the shape decide.
+    Returns False, having done nothing, for operands it does not take."""
     M, K = a.shape
-    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or K < 8 or a.stride(1) != 1
-            or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8 or (a.data_ptr() | w.data_ptr()) & 15):
+    lda, a_inner = a.stride()
+    ldw, w_inner = w.stride()
+    pa, pw = a.data_ptr(), w.data_ptr()
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or K % 8 or K < 8 or a_inner != 1 or w_inner != 1
+            or lda % 8 or ldw % 8 or (pa | pw) & 15):
         return False
     if epilogue == EPILOGUE_GATED_SILU and c.dtype != torch.bfloat16:
         return False
     _dev(a, w, c)
-    N = w.shape[0]
-    assert w.shape[1] == K and c.stride(1) == 1 and c.shape[0] == M
-    assert c.shape[1] == (N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
-    _check(_fn("b200_gemm_tcgen05")(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(),
-                                    dtype_code(c.dtype), c.stride(0), M, N, K, epilogue, tile_width, _stream()),
-           "gemm_tcgen05")
+    N, Kw = w.shape
+    ldc, c_inner = c.stride()
+    assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
+    _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
+                                    tile_width, k_spans, _stream()), "gemm_tcgen05")
     return True
+
+
+def gemm_tcgen05_k_spans(M: int, N: int, K: int) -> int:
+    """Into how many spans ``gemm_tcgen05`` cuts K for this shape when it is left the choice (1: it does not)."""
+    return int(library("gemm_tcgen05").b200_gemm_tcgen05_k_spans(M, N, K))
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,

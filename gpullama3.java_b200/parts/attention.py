@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.sequence_cache import KVCacheNeed, KVView
-from ..kernels import ops
+from ..kernels import fast, ops
 from ..weights.loader import ParamSpec
 from .base import Mixer, PositionEncoding, StepContext, register_mixer
 from .linear import Linear
@@ -47,8 +47,6 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True, then_norm=None):
         qkv = self.qkv.store(x, ctx.dtype)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
-        from ..kernels import fast
-
         table = ctx.page_tables[cache.group]
         out = torch.empty((x.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
         if not fast.try_decode_attention_with_rope(qkv, out, ctx, table, cache, self, writes_cache):

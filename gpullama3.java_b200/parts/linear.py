@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import fast, ops
 from .base import ScaledRows
 
 
@@ -18,8 +18,6 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def _run(self, a, c: torch.Tensor, epilogue: int) -> None:
-        from ..kernels import fast
-
         if isinstance(a, ScaledRows):  # only handed to a product that said it links (links_with)
             ops.gemm_decode_linked(a.data, self.weight, c, epilogue, row_factors=(a.partials, a.eps, a.dim))
             return

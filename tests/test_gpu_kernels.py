@@ -313,40 +313,62 @@ def test_gemm_decode_halves_of_a_split_norm(M, hidden, K, N2, w_dtype):
     torch.testing.assert_close(part2.sum(dim=1).cpu().double(), (res2.cpu().double() ** 2).sum(dim=1), rtol=1e-5, atol=0)
 
 
-@pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 512), (1, 8, 8), (100, 300, 72), (129, 257, 200),
-                                     (300, 1030, 2048), (2048, 512, 1024), (65, 3072, 2048)])
-@pytest.mark.parametrize("width", [0, 256, 128, 64])
-def test_gemm_tcgen05_and_its_epilogues(M, N, K, width):
-    """The TMA + tcgen05 kernel at tile-exact sizes, at ragged edges in M, N and K, and with several
-    waves of tiles, for each width of tile and for the width the shape picks (0); every internal wait must
-    have completed (status word 0)."""
-    import functools
+def _check_gemm_tcgen05(gemm, M, N, K):
+    """Store (both output types), residual add and gated SiLU of ``gemm`` against the plain product."""
     o = ops()
-    real = o.gemm_tcgen05
-    o = type("WithWidth", (), {k: getattr(o, k) for k in ("EPILOGUE_STORE", "EPILOGUE_RESIDUAL_ADD", "EPILOGUE_GATED_SILU",
-                                                        "gemm_tcgen05_status")})
-    o.gemm_tcgen05 = staticmethod(functools.partial(real, tile_width=width))
     g = torch.Generator().manual_seed(M + N + K)
     a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
     ref = a.float().cpu().double() @ w.float().cpu().double().t()
     for c_dtype in (torch.bfloat16, torch.float32):
         c = torch.full((M, N), 7.0, dtype=c_dtype, device="cuda")
-        assert o.gemm_tcgen05(a, w, c, o.EPILOGUE_STORE)
+        assert gemm(a, w, c, o.EPILOGUE_STORE)
         torch.testing.assert_close(c.float().cpu(), ref.float().to(c_dtype).float(), **tol(c_dtype, ref))
     res0 = torch.randn(M, N, generator=g)
     res = res0.clone().cuda()
-    assert o.gemm_tcgen05(a, w, res, o.EPILOGUE_RESIDUAL_ADD)
+    assert gemm(a, w, res, o.EPILOGUE_RESIDUAL_ADD)
     torch.testing.assert_close(res.cpu(), (res0.double() + ref).float(), **tol(torch.float32, ref))
     if N % 2 == 0:
         h = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
-        assert o.gemm_tcgen05(a, w, h, o.EPILOGUE_GATED_SILU)
+        assert gemm(a, w, h, o.EPILOGUE_GATED_SILU)
         gated = P.swiglu(ref[:, 0::2], ref[:, 1::2])
         torch.testing.assert_close(h.float().cpu(), gated.float().to(torch.bfloat16).float(), **tol(torch.bfloat16, gated))
     assert o.gemm_tcgen05_status() == 0
+    return a, w
+
+
+@pytest.mark.parametrize("M, N, K", [(128, 256, 64), (128, 256, 512), (1, 8, 8), (100, 300, 72), (129, 257, 200),
+                                     (300, 1030, 2048), (2048, 512, 1024), (65, 3072, 2048)])
+@pytest.mark.parametrize("width", [0, 256, 128, 64])
+def test_gemm_tcgen05_and_its_epilogues(M, N, K, width):
+    """The TMA + tcgen05 kernel at tile-exact sizes, at ragged edges in M, N and K, and with several
+    waves of tiles, for each width of tile and for the choice the shape makes (0); every internal wait must
+    have completed (status word 0)."""
+    import functools
+    o = ops()
+    a, w = _check_gemm_tcgen05(functools.partial(o.gemm_tcgen05, tile_width=width), M, N, K)
     assert not o.gemm_tcgen05(a.float(), w, torch.empty(M, N, device="cuda"))
     if K % 16 == 8:   # a view whose rows are not 16-byte aligned is left to the plain kernel
         assert not o.gemm_tcgen05(a[:, 4:], w[:, 4:], torch.empty(M, N, device="cuda"))
+
+
+@pytest.mark.parametrize("M, N, K, spans", [(128, 128, 128, 2), (100, 300, 328, 4), (300, 1030, 2048, 2), (256, 2048, 8192, 4),
+                                            (129, 130, 320, 4), (512, 2048, 8192, 0), (256, 1024, 4096, 0)])
+def test_gemm_tcgen05_with_k_cut_among_a_cluster(M, N, K, spans):
+    """K cut into 2 or 4 spans whose partial tiles meet through distributed shared memory: exact tiles, ragged
+    edges, a K whose last span is short or empty (328 = 6 k-steps over 4 spans: 2, 2, 2, 0; 320: 2, 2, 1, 0), and
+    the shapes (few tiles, long K) for which the kernel is chosen without being asked.  Run twice: the sum must
+    not depend on timing."""
+    import functools
+    o = ops()
+    a, w = _check_gemm_tcgen05(functools.partial(o.gemm_tcgen05, k_spans=spans), M, N, K)
+    c1 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    c2 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    assert o.gemm_tcgen05(a, w, c1, k_spans=spans) and o.gemm_tcgen05(a, w, c2, k_spans=spans)
+    assert torch.equal(c1, c2)
+    if spans == 0:
+        assert o.gemm_tcgen05_k_spans(M, N, K) == {512: 2, 256: 4}[M]
+    assert o.gemm_tcgen05_status() == 0
 
 
 @pytest.mark.parametrize("M", [1, 17, 32, 33, 64, 100, 128])
