@@ -81,6 +81,28 @@ def test_reserve_commit_release_and_reuse():
     c.check_invariants()
 
 
+def test_a_slot_number_means_the_same_sequence_only_while_the_counter_stands_still():
+    """What a recorded decode step keeps on the device about its slots stays valid only as long as nobody was
+    given or gave back a slot: the cache counts both, and nothing else moves the count."""
+    c = _cache()
+    n0 = c.ownership_changes
+    a = c.acquire()
+    assert c.ownership_changes == n0 + 1
+    c.reserve([(a, 70)])
+    c.commit(a, 70)
+    c.length(a), c.page_rows(0, [a])
+    assert c.ownership_changes == n0 + 1
+    with pytest.raises(CacheFull):
+        c.reserve([(a, 64 * 10)])
+    assert c.ownership_changes == n0 + 1
+    c.release(a)
+    assert c.ownership_changes == n0 + 2
+    with pytest.raises(CacheError):
+        c.release(a)                       # a refused release is no change of owner
+    assert c.ownership_changes == n0 + 2
+    assert c.acquire() == a and c.ownership_changes == n0 + 3   # same number, another sequence
+
+
 def test_random_walk_never_loses_or_doubles_a_page():
     rng = random.Random(0)
     c = _cache(max_tokens=64 * 16, max_slots=5)
