@@ -159,14 +159,20 @@ def time_decode(engine, batch, context, steps, warmup, sampler=None):
         torch.cuda.synchronize()
         toks = torch.randint(0, V, (batch,), generator=g).tolist()
         times, launches0 = [], None
+        # a step's clock starts when its host side (token and page-table staging) is done, right before the launch;
+        # the host side is part of the end-to-end number
+        started = []
+        step.before_launch = lambda: started.append(True) or started[0].record()
         for it in range(warmup + steps):
             if it == warmup:
                 torch.cuda.synchronize()
                 launches0 = ops.launch_count() + step.graph_launches
                 t_begin = time.time()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+            started[:] = [e0]
             logits = step([SequenceInput(s, [t], [0]) for s, t in zip(slots, toks)], reuse_output=True)
+            if len(started) == 1:
+                raise RuntimeError("the decode step did not go through the recorded path; bench.py times that path")
             out = torch.empty(batch, dtype=torch.int32, device=logits.device)
             ops.argmax_rows(logits, out)
             e1.record()
@@ -178,6 +184,7 @@ def time_decode(engine, batch, context, steps, warmup, sampler=None):
         launches = ops.launch_count() + step.graph_launches - launches0
         return times, launches, (t_begin, t_end)
     finally:
+        step.before_launch = None
         for s in slots:
             cache.release(s)
 
@@ -225,6 +232,9 @@ def time_e2e(engine, batch, context, steps, warmup):
     if dt is None:
         dt = stamps[max(stamps)] - stamps[warmup + 1]
         steps = max(stamps) - (warmup + 1)
+    gaps = sorted((stamps[k + 1] - stamps[k]) * 1e3 for k in range(warmup + 1, warmup + 1 + steps) if k + 1 in stamps)
+    if gaps:
+        log(f"e2e steps: median {gaps[len(gaps) // 2]:.3f} ms, longest {gaps[-1]:.3f} ms, shortest {gaps[0]:.3f} ms")
     return batch * steps / dt, dt / steps * 1e3
 
 

@@ -345,6 +345,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     }
 }
 
+// One CTA per (sequence, head), one thread per dimension.  The partial results of up to 8 spans are requested
+// together before any is used (a loop over a run-time count of spans that loads, scales and adds one span at a time
+// pays one round trip to L2 per span); they are added in span order, so the sum is the same.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               __nv_bfloat16* __restrict__ out, int n_splits, int D) {
     pdl_launch_dependents();
@@ -352,14 +355,33 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     const size_t row = blockIdx.x;  // seq * n_heads + head
     const float* ml = part_ml + row * n_splits * 2;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        float ms[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ms[j] = s0 + j < n_splits ? ml[2 * (s0 + j)] : -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
+    }
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float l = 0.f, acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = ml[2 * s];
-            const float f = ms == -INFINITY ? 0.f : expf(ms - m);
-            l += ml[2 * s + 1] * f;
-            acc += part_o[(row * n_splits + s) * D + d] * f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float ms[8], ls[8], po[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int s = s0 + j;
+                const bool ok = s < n_splits;
+                ms[j] = ok ? ml[2 * s] : -INFINITY;
+                ls[j] = ok ? ml[2 * s + 1] : 0.f;
+                po[j] = ok ? part_o[(row * n_splits + s) * D + d] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (s0 + j < n_splits) {
+                    const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
+                    l += ls[j] * f;
+                    acc += po[j] * f;
+                }
+            }
         }
         out[row * D + d] = __float2bfloat16_rn(acc / l);
     }

@@ -164,10 +164,14 @@ class DecodeGraph:
             self.tokens_host.copy_(self.tokens_dev, non_blocking=True)
         return logits
 
-    def run(self, slots, start_pos, tokens, uniforms=None) -> torch.Tensor:
+    def run(self, slots, start_pos, tokens, uniforms=None, before_launch=None) -> torch.Tensor:
+        """``before_launch``: called when the host side of the step is done, right before the step's first
+        launch (a measurement records its start event there)."""
         from ..kernels import ops
 
         self.refresh(slots, start_pos, tokens, uniforms)
+        if before_launch is not None:
+            before_launch()
         if self.graph is None:
             # the first step runs as ordinary launches (this also loads every kernel library the step
             # needs); the same launch sequence is then recorded, without running, for later steps
@@ -222,6 +226,7 @@ class StepFunction:
         self.graph_launches = 0     # kernel launches replayed from graphs so far
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy (tokens, positions, page tables)
         self.last_d2h_bytes = 0     # bytes of the last step's copy of drawn tokens to the host (decode_and_sample)
+        self.before_launch = None   # measurement hook: called between a recorded decode step's host work and its launch
 
     def _graph_for(self, slots: list[int], start: list[int], sampler=None) -> DecodeGraph:
         """The recorded step that fits these sequences: table widths are powers of two of at least 4 pages."""
@@ -269,7 +274,7 @@ class StepFunction:
         start = [cache.length(s) for s in slots]
         g = self._graph_for(slots, start)
         replayed = g.graph is not None
-        logits = g.run(slots, start, [s.tokens[0] for s in inputs])
+        logits = g.run(slots, start, [s.tokens[0] for s in inputs], before_launch=self.before_launch)
         self.last_h2d_bytes = g.h2d_bytes
         if replayed:
             self.graph_launches += g.n_launches
