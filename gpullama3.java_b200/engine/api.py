@@ -31,11 +31,13 @@ def _resolve_dtype(dtype) -> torch.dtype:
 
 class _LoopStep:
     """The step function as the generation loop uses it: the loop samples from a step's logits before it runs
-    the next step, so the logits need not be copied; decode steps may come back as drawn tokens directly."""
+    the next step, so the logits need not be copied; decode steps may come back as drawn tokens directly, and may be launched
+    one ahead of the tokens the host has read."""
 
     def __init__(self, step_fn: StepFunction):
         self.step_fn = step_fn
         self.decode_and_sample = step_fn.decode_and_sample
+        self.decode_ahead, self.collect, self.abandon = step_fn.decode_ahead, step_fn.collect, step_fn.abandon
 
     def __call__(self, inputs):
         return self.step_fn(inputs, reuse_output=True)

@@ -101,6 +101,9 @@ class Generator:
             try:
                 self._run_batch(batch, slots, prompts, results, ids, max_new_tokens, sampler, stop, on_token, metrics)
             finally:
+                abandon = getattr(self.step_fn, "abandon", None)
+                if abandon is not None:
+                    abandon()  # after an error a step may still be in flight; its tokens belong to no one
                 for s in slots.values():
                     self.cache.release(s)
         metrics.seconds = time.perf_counter() - t_start
@@ -114,15 +117,13 @@ class Generator:
         logits = self.step_fn(inputs)
         metrics.prompt_tokens += sum(len(prompts[i]) for i in live)
         tokens = sampler.sample(logits, [ids[i] for i in live], [len(results[i].tokens) for i in live])
-        fused = getattr(self.step_fn, "decode_and_sample", None)  # step and draw as one recorded launch, if offered
-        first = True
-        while live:
-            if first:
-                metrics.prefill_seconds += time.perf_counter() - t0
-                t0 = time.perf_counter()
-                first = False
+        metrics.prefill_seconds += time.perf_counter() - t0
+        t0 = time.perf_counter()
+
+        def take(who, toks):
+            """Record one new token for each sequence of ``who``; returns the sequences that go on."""
             nxt = []
-            for i, tok in zip(live, tokens):
+            for i, tok in zip(who, toks):
                 r = results[i]
                 r.tokens.append(tok)
                 metrics.generated_tokens += 1
@@ -136,13 +137,46 @@ class Generator:
                     r.finish_reason = FINISH_CONTEXT  # no room to feed the token back
                 else:
                     nxt.append(i)
-            live = nxt
-            if not live:
-                break
+            return nxt
+
+        def goes_on_unless_it_stops(i):
+            """Whether sequence i, with the token of the step in flight still to come, has room for one more."""
+            r = results[i]
+            return len(r.tokens) + 1 < max_new_tokens and r.prompt_length + len(r.tokens) + 1 < self.max_length
+
+        fused = getattr(self.step_fn, "decode_and_sample", None)  # step and draw as one recorded launch, if offered
+        ahead = getattr(self.step_fn, "decode_ahead", None)       # the same without waiting for the tokens
+        collect = getattr(self.step_fn, "collect", None)
+        if collect is None:
+            ahead = None
+        live = take(live, tokens)
+        while live:
             inputs = [SequenceInput(slots[i], [results[i].tokens[-1]], [0]) for i in live]
             requests, draws = [ids[i] for i in live], [len(results[i].tokens) for i in live]
-            tokens = fused(inputs, sampler, requests, draws) if fused is not None else None
-            if tokens is None:
-                tokens = sampler.sample(self.step_fn(inputs), requests, draws)
             metrics.decode_steps += 1
+            if ahead is None or not ahead(inputs, sampler, requests, draws, False):
+                tokens = fused(inputs, sampler, requests, draws) if fused is not None else None
+                if tokens is None:
+                    tokens = sampler.sample(self.step_fn(inputs), requests, draws)
+                live = take(live, tokens)
+                continue
+            # A step is in flight.  While it runs, the step after it is launched for the same sequences, fed with
+            # the tokens of the step in flight on the device; the host reads tokens one step late.  Only a stop
+            # token can end a sequence unforeseen: the token the step launched ahead drew for it is dropped (what
+            # that step wrote into the cache lies behind the sequence's end), and the batch goes on without it.
+            while True:
+                placeholders = [SequenceInput(slots[i], [0], [0]) for i in live]
+                launched_ahead = (all(goes_on_unless_it_stops(i) for i in live)
+                                  and ahead(placeholders, sampler, requests, [len(results[i].tokens) + 1 for i in live], True))
+                nxt = take(live, collect())
+                if not launched_ahead:
+                    live = nxt
+                    break
+                metrics.decode_steps += 1
+                if nxt == live:
+                    continue
+                going = set(nxt)
+                pairs = [(i, tok) for i, tok in zip(live, collect()) if i in going]
+                live = take([i for i, _ in pairs], [tok for _, tok in pairs])
+                break
         metrics.decode_seconds += time.perf_counter() - t0

@@ -90,11 +90,17 @@ class DecodeGraph:
     replayed for every token (tornadovm/TornadoVMMasterPlan.java:149-175 of the reference
     project)."""
 
-    def __init__(self, model, cache: SequenceCache, n_seqs: int, widths: list[int], sampler=None):
+    def __init__(self, model, cache: SequenceCache, n_seqs: int, widths: list[int], sampler=None,
+                 tokens_dev: torch.Tensor | None = None, fed: bool = False):
+        """``tokens_dev``: where the draw leaves its tokens on the device (its own buffer if none is given).
+        ``fed``: the step's input tokens are what ``tokens_dev`` holds when the step starts, i.e. the tokens the
+        step before it drew for the same sequences; the host then stages positions and page tables only."""
         from ..kernels import ops
 
         self.model, self.cache, self.n, self.widths = model, cache, n_seqs, list(widths)
         self.sampler = sampler                        # its launches are recorded after the model's, if given
+        self.fed = bool(fed)
+        assert not fed or (sampler is not None and tokens_dev is not None)
         self.draws = sampler is not None and sampler.uniforms([0], [0]) is not None
         self.sizes = [n_seqs, n_seqs, n_seqs, n_seqs + 1, n_seqs, n_seqs, n_seqs] + [n_seqs * w for w in widths]
         self.table_shapes = [(n_seqs, w) for w in widths]
@@ -107,7 +113,13 @@ class DecodeGraph:
         self.host = torch.empty(total, dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()
         self.dev = torch.empty(total, dtype=torch.int32, device=model.device)
-        self.tokens_dev = torch.empty(n_seqs, dtype=torch.int32, device=model.device) if sampler is not None else None
+        if sampler is None:
+            self.tokens_dev = None
+        elif tokens_dev is not None:
+            assert tokens_dev.shape == (n_seqs,) and tokens_dev.dtype == torch.int32
+            self.tokens_dev = tokens_dev
+        else:
+            self.tokens_dev = torch.empty(n_seqs, dtype=torch.int32, device=model.device)
         self.tokens_host = torch.empty(n_seqs, dtype=torch.int32).pin_memory() if sampler is not None else None
         self.done = torch.cuda.Event()                # the last run of this step, copies included
         self.pending = False
@@ -133,12 +145,13 @@ class DecodeGraph:
         n, h = self.n, self.host_np
         owners = getattr(self.cache, "ownership_changes", None)
         if (self.last_slots == slots and owners is not None and owners == self.last_owners
-                and all(p == q + 1 for p, q in zip(start_pos, self.last_pos))):
+                and all(q < p <= q + 2 for p, q in zip(start_pos, self.last_pos))):
+            # (two further: this recorded step takes turns with another one)
             h[0:n] = tokens
             h[n:2 * n] = start_pos
             h[4 * n + 1:5 * n + 1] = h[n:2 * n] + 1
-            for i, p in enumerate(start_pos):
-                if p % PAGE_TOKENS == 0:
+            for i, (p, q) in enumerate(zip(start_pos, self.last_pos)):
+                if p // PAGE_TOKENS != q // PAGE_TOKENS:
                     for gi, (off, w) in enumerate(zip(self.table_offsets, self.widths)):
                         row = self.cache.page_rows(gi, [slots[i]])[0]
                         dst = h[off + i * w: off + (i + 1) * w]
@@ -157,6 +170,8 @@ class DecodeGraph:
                                   start_pos, [1] * self.n)
         ctx.extras["decode_splits"] = self.splits
         ctx.extras["decode_kv_capacity"] = self.kv_capacity
+        if self.fed:
+            ctx.tokens = self.tokens_dev  # read by the embedding before this step's draw overwrites it
         logits = self.model.forward(ctx, self.cache, rows)
         if self.sampler is not None:
             u = self.dev[self.uniform_offset:self.uniform_offset + self.n].view(torch.float32) if self.draws else None
@@ -227,9 +242,14 @@ class StepFunction:
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy (tokens, positions, page tables)
         self.last_d2h_bytes = 0     # bytes of the last step's copy of drawn tokens to the host (decode_and_sample)
         self.before_launch = None   # measurement hook: called between a recorded decode step's host work and its launch
+        self._drawn: dict[int, torch.Tensor] = {}   # per number of sequences: where every recorded draw leaves its tokens
+        self._in_flight: list[DecodeGraph] = []     # steps launched by decode_ahead, oldest first, not yet collected
+        self._fed_turn = 0
 
-    def _graph_for(self, slots: list[int], start: list[int], sampler=None) -> DecodeGraph:
-        """The recorded step that fits these sequences: table widths are powers of two of at least 4 pages."""
+    def _graph_for(self, slots: list[int], start: list[int], sampler=None, variant: int = 0) -> DecodeGraph:
+        """The recorded step that fits these sequences: table widths are powers of two of at least 4 pages.
+        ``variant`` 0 takes its tokens from the host; 1 and 2 are two copies of the step that takes them from the
+        draw before it on the device (two, so that one can be staged while the other runs)."""
         cache = self.cache
         widths = []
         for gi in range(len(cache.kv_groups)):
@@ -238,10 +258,16 @@ class StepFunction:
             while w < need:
                 w *= 2
             widths.append(w)
-        key = (len(slots), tuple(widths), sampler.launch_key() if sampler is not None else None)
+        key = (len(slots), tuple(widths), sampler.launch_key() if sampler is not None else None, variant)
         g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[key] = DecodeGraph(self.model, cache, len(slots), widths, sampler)
+            drawn = None
+            if sampler is not None:
+                drawn = self._drawn.get(len(slots))
+                if drawn is None:
+                    drawn = self._drawn[len(slots)] = torch.empty(len(slots), dtype=torch.int32, device=self.model.device)
+            g = self._graphs[key] = DecodeGraph(self.model, cache, len(slots), widths, sampler, tokens_dev=drawn,
+                                                fed=variant != 0)
         return g
 
     def decode_and_sample(self, inputs: list[SequenceInput], sampler, requests: list[int], draws: list[int]):
@@ -249,23 +275,58 @@ class StepFunction:
         staging copy, model, the sampler's kernels and the copy of the tokens back.  Returns None when the step
         cannot be served that way (graphs off, a part that is not graph-safe, too many sequences); the caller
         then takes the step and the sampler separately."""
+        if self._in_flight:
+            raise StepError("steps launched by decode_ahead have not been collected")
+        if not self.decode_ahead(inputs, sampler, requests, draws):
+            return None
+        return self.collect()
+
+    def decode_ahead(self, inputs: list[SequenceInput], sampler, requests: list[int], draws: list[int],
+                     feed_previous: bool = False) -> bool:
+        """Launch a decode step with its draw and return without waiting for the tokens; ``collect`` hands them
+        out, oldest step first.  With ``feed_previous`` the step's input tokens are the ones the step launched
+        just before it drew, taken on the device (the same sequences in the same order; the tokens in ``inputs``
+        are placeholders): the host can launch step k + 1 while step k runs and read step k's tokens afterwards.
+        Returns False, having done nothing, when the step cannot be served as a recorded launch."""
         if not (self.use_graphs and len(inputs) <= self.max_graph_batch and all(len(s.tokens) == 1 for s in inputs)
                 and hasattr(sampler, "sample_into")):
-            return None
+            return False
+        if len(self._in_flight) >= 2:
+            raise StepError("two steps are in flight already: collect one first")
         self._validate(inputs)
         cache = self.cache
-        cache.reserve([(s.slot, 1) for s in inputs])
         slots = [s.slot for s in inputs]
+        variant = 0
+        if feed_previous:
+            if not self._in_flight or self._in_flight[-1].last_slots != slots:
+                raise StepError("feed_previous needs the step before, for the same sequences, to be in flight")
+            self._fed_turn ^= 1
+            variant = 1 + self._fed_turn
+        cache.reserve([(s, 1) for s in slots])
         start = [cache.length(s) for s in slots]
-        g = self._graph_for(slots, start, sampler)
+        g = self._graph_for(slots, start, sampler, variant)
+        if any(g is f for f in self._in_flight):  # cannot happen with two alternating copies; never stage under a running step
+            raise StepError("the recorded step chosen is still in flight")
         replayed = g.graph is not None
-        g.run(slots, start, [s.tokens[0] for s in inputs], sampler.uniforms(requests, draws))
+        g.run(slots, start, [s.tokens[0] for s in inputs], sampler.uniforms(requests, draws), before_launch=self.before_launch)
         self.last_h2d_bytes, self.last_d2h_bytes = g.h2d_bytes, g.d2h_bytes
         if replayed:
             self.graph_launches += g.n_launches
         for s in slots:
             cache.commit(s, 1)
-        return g.sampled()
+        self._in_flight.append(g)
+        return True
+
+    def collect(self) -> list[int]:
+        """The tokens of the oldest step launched by ``decode_ahead`` and not collected yet (waits for it)."""
+        if not self._in_flight:
+            raise StepError("no step is in flight")
+        return self._in_flight.pop(0).sampled()
+
+    def abandon(self) -> None:
+        """Forget the steps in flight (their tokens are not wanted any more; what they write into the cache
+        lies in slots whose sequences are over)."""
+        self._in_flight.clear()
 
     def _decode_with_graph(self, inputs: list[SequenceInput], reuse_output: bool) -> torch.Tensor | None:
         cache = self.cache

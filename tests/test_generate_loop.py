@@ -186,3 +186,121 @@ def test_decode_steps_go_to_the_step_and_draw_call_when_it_is_offered():
     assert len(fused_calls) == 4 and fused_calls[1] is None and fused_calls[3] is None
     assert fused_calls[0] == ([7, 9], [1, 1]) and fused_calls[2] == ([7, 9], [3, 3])
     assert cache.live_slots() == []
+
+
+class AheadStep(ScriptedStep):
+    """A scripted step function that also offers ``decode_ahead`` / ``collect`` / ``abandon`` the way the real
+    one does: a launched step computes at once here, but its tokens stay "on the device" (``self.drawn``) until
+    collected, and a step launched with ``feed_previous`` takes its input from there, not from the host."""
+
+    def __init__(self, cache, decline=lambda n: False):
+        super().__init__(cache)
+        self.in_flight, self.drawn, self.drawn_slots = [], None, None
+        self.launches, self.decline = [], decline
+
+    def decode_ahead(self, inputs, sampler, requests, draws, feed_previous=False):
+        if self.decline(len(self.launches)):
+            assert not feed_previous, "a declined launch ahead would leave the loop without its tokens"
+            return False
+        assert len(self.in_flight) < 2
+        slots = [s.slot for s in inputs]
+        if feed_previous:
+            assert self.in_flight and self.drawn_slots == slots, "fed from a step for other sequences"
+            assert all(s.tokens == [0] for s in inputs), "the host does not know these tokens yet"
+            inputs = [type(s)(s.slot, [t], [0]) for s, t in zip(inputs, self.drawn)]
+        logits = self(inputs)
+        self.drawn, self.drawn_slots = logits.argmax(dim=-1).tolist(), slots
+        self.in_flight.append(list(self.drawn))
+        self.launches.append((bool(feed_previous), list(requests), list(draws)))
+        return True
+
+    def collect(self):
+        return self.in_flight.pop(0)
+
+    def abandon(self):
+        self.in_flight.clear()
+
+
+def make_ahead(decline=lambda n: False, **kw):
+    gen, _, cache = make(**kw)
+    step = AheadStep(cache, decline)
+    gen.step_fn = step
+    return gen, step, cache
+
+
+def test_steps_launched_one_ahead_give_the_same_tokens():
+    """With ``decode_ahead`` the loop launches step k + 1 before it has read step k's tokens.  Results, finish
+    reasons and the draws' identities are those of the plain loop, for stop tokens at every place, unequal
+    lengths, length and context limits, and one batch after another."""
+    import random
+    rng = random.Random(5)
+    for trial in range(60):
+        n = rng.randint(1, 6)
+        prompts = [[rng.randrange(1, VOCAB) for _ in range(rng.randint(1, 40))] for _ in range(n)]
+        new = rng.randint(1, 12)
+        stop = frozenset(rng.sample(range(VOCAB), rng.randint(0, 12)))
+        max_length = rng.choice([None, 45])
+        plain, _, _ = make(max_batch=3, max_length=max_length)
+        want = plain.generate(prompts, new, SamplingParams(), stop_ids=stop)
+        seen = []
+        gen, step, cache = make_ahead(max_batch=3, max_length=max_length)
+        got = gen.generate(prompts, new, SamplingParams(), stop_ids=stop, on_token=lambda i, t: seen.append((i, t)))
+        assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want], trial
+        assert sorted(seen) == sorted((i, t) for i, r in enumerate(want) for t in r.tokens)
+        assert step.in_flight == [] and cache.live_slots() == [] and cache.kv_groups[0].pool.n_held == 0
+        for fed, requests, draws in step.launches:
+            assert len(requests) == len(draws)
+        assert gen.last_metrics.generated_tokens == sum(len(r.tokens) for r in want)
+
+
+def test_a_stop_token_drops_what_was_launched_ahead_for_its_sequence_only():
+    gen, step, cache = make_ahead()
+    prompts = [[1, 2, 3], [4] * 11]
+    first = expected_tokens(prompts[0], 8)
+    stop = {first[2]}                                    # sequence 0 ends with its third token
+    assert first[2] not in expected_tokens(prompts[1], 8)
+    res = gen.generate(prompts, 8, SamplingParams(), stop_ids=stop, request_ids=[7, 9])
+    assert res[0].tokens == first[:3] and res[0].finish_reason == FINISH_STOP
+    assert res[1].tokens == expected_tokens(prompts[1], 8) and res[1].finish_reason == FINISH_LENGTH
+    # token 1 comes from the prompts; steps for tokens 2, 3 and (launched ahead, dropped for sequence 0) 4 hold both
+    # sequences, the first from host tokens, the others fed on the device; then sequence 1 goes on alone
+    assert step.launches[0] == (False, [7, 9], [1, 1])
+    assert step.launches[1] == (True, [7, 9], [2, 2]) and step.launches[2] == (True, [7, 9], [3, 3])
+    assert step.launches[3] == (False, [9], [4]) and all(l[1] == [9] for l in step.launches[3:])
+    assert [l[2] for l in step.launches[3:]] == [[4], [5], [6], [7]]
+    assert [l[0] for l in step.launches[3:]] == [False, True, True, True]
+    assert gen.last_metrics.decode_steps == len(step.launches)
+
+
+def test_nothing_is_launched_past_a_limit_that_is_known_beforehand():
+    """The last token of a sequence that ends by length or by the context limit is known to be its last before
+    it is drawn: no step is launched ahead for it, so the cache never holds a position past the plan."""
+    gen, step, cache = make_ahead(max_length=14)
+    res = gen.generate([[1, 2, 3], [4] * 11], 6, SamplingParams())
+    assert [len(r.tokens) for r in res] == [6, 3] and [r.finish_reason for r in res] == [FINISH_LENGTH, FINISH_CONTEXT]
+    per_slot = {}
+    for call in step.calls:
+        for slot, n in call:
+            per_slot[slot] = per_slot.get(slot, 0) + n
+    assert sorted(per_slot.values()) == [3 + 5, 11 + 2]  # every token but the last is fed back, none beyond
+
+
+def test_a_step_function_that_declines_is_served_the_plain_way():
+    gen, step, cache = make_ahead(decline=lambda n: True)
+    prompts = [[1, 2, 3], [4] * 11]
+    res = gen.generate(prompts, 5, SamplingParams())
+    assert [r.tokens for r in res] == [expected_tokens(p, 5) for p in prompts] and step.launches == []
+
+
+def test_steps_in_flight_are_forgotten_when_the_loop_fails():
+    gen, step, cache = make_ahead()
+
+    def boom(i, tok):
+        if len(step.launches) >= 2:
+            raise RuntimeError("callback failed")
+
+    with pytest.raises(RuntimeError):
+        gen.generate([[1, 2, 3]], 8, SamplingParams(), on_token=boom)
+    assert step.in_flight == [] and cache.live_slots() == []
+    res = gen.generate([[1, 2, 3]], 4, SamplingParams())   # the next request is not served a stale step's tokens
+    assert res[0].tokens == expected_tokens([1, 2, 3], 4)

@@ -93,8 +93,10 @@ def test_temperature_sampling_follows_the_uniform_numbers(session_tmp):
                          ids=["greedy", "temperature", "nucleus"])
 def test_step_and_draw_recorded_together_give_the_tokens_of_step_then_draw(session_tmp, sampling):
     """Decode steps normally run as one recorded launch that ends with the sampler's kernels and the copy of the
-    tokens to the host; with that path switched off the loop runs the step, then the sampler.  Same tokens, and
-    the recorded path is really taken (it reports the bytes it copied back)."""
+    tokens to the host, launched one step ahead of the tokens the host has read and fed with the tokens of the
+    step before on the device; with that switched off the loop waits for each step's tokens, and with the
+    recorded draw switched off too it runs the step, then the sampler.  Same tokens all three ways, and the
+    recorded path is really taken (it reports the bytes it copied back)."""
     from gpullama3.java_b200.engine.api import Engine
 
     cfg_json, norm_std = TINY["A"]
@@ -104,11 +106,17 @@ def test_step_and_draw_recorded_together_give_the_tokens_of_step_then_draw(sessi
     engine = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
     together = engine.generate(prompts, max_new_tokens=70, stop_ids=(), **sampling)   # crosses a page boundary
     assert engine.step_fn.last_d2h_bytes > 0
+    assert any(key[3] != 0 for key in engine.step_fn._graphs), "no step was fed on the device"
+    waiting = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
+    waiting.generator.step_fn.decode_ahead = lambda *a, **k: False
+    in_turn = waiting.generate(prompts, max_new_tokens=70, stop_ids=(), **sampling)
+    assert waiting.step_fn.last_d2h_bytes > 0 and all(key[3] == 0 for key in waiting.step_fn._graphs)
     apart_engine = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
+    apart_engine.generator.step_fn.decode_ahead = lambda *a, **k: False
     apart_engine.generator.step_fn.decode_and_sample = lambda *a, **k: None
     apart = apart_engine.generate(prompts, max_new_tokens=70, stop_ids=(), **sampling)
     assert apart_engine.step_fn.last_d2h_bytes == 0
-    assert together == apart
+    assert together == in_turn == apart
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
