@@ -248,8 +248,19 @@ def test_steps_launched_one_ahead_give_the_same_tokens():
         assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want], trial
         assert sorted(seen) == sorted((i, t) for i, r in enumerate(want) for t in r.tokens)
         assert step.in_flight == [] and cache.live_slots() == [] and cache.kv_groups[0].pool.n_held == 0
+        # token number d of a request (counting from 0, the prompt step's) was drawn as its draw d; a step launched
+        # ahead may have drawn one more for a request that a stop token had just ended, and nothing beyond that
+        drawn = {}
         for fed, requests, draws in step.launches:
             assert len(requests) == len(draws)
+            for r, d in zip(requests, draws):
+                assert d not in drawn.setdefault(r, set()), "a draw was made twice"
+                drawn[r].add(d)
+        for i, r in enumerate(want):
+            made = drawn.get(i, set())
+            kept = set(range(1, len(r.tokens)))
+            extra = made - kept
+            assert kept <= made and extra <= ({len(r.tokens)} if r.finish_reason == FINISH_STOP else set()), (trial, i)
         assert gen.last_metrics.generated_tokens == sum(len(r.tokens) for r in want)
 
 
