@@ -163,3 +163,23 @@ def test_command_line(session_tmp, tmp_path):
     p = subprocess.run([str(ROOT / "bin" / "llama-b200"), "--config", str(tmp_path / "config.json"), "--random-weights", "3",
                         "--prompt", "1 2 3", "-n", "4", "--seed", "1"], capture_output=True, text=True, env=env, timeout=600)
     assert p.returncode == 0 and len(p.stdout.split()) == 4, p.stderr[-2000:]
+
+
+def test_steps_launched_ahead_keep_their_tokens_when_the_page_tables_grow(session_tmp):
+    """330 new tokens on prompts of 3, 200 and 40: the page tables of the recorded steps double twice on the way
+    (4, 8, 16 pages wide), so device-fed steps are recorded anew in mid-flight, each while the step before it
+    runs.  Same tokens as the loop that waits for every step."""
+    from gpullama3.java_b200.engine.api import Engine
+
+    cfg_json, norm_std = TINY["A"]
+    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0})
+    prompts = random_prompts(cfg_json["vocab_size"], [3, 200, 40], seed=6)
+    ahead = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 32, max_batch=4)
+    got = ahead.generate(prompts, max_new_tokens=330, stop_ids=(), temperature=0.7, seed=3)
+    fed_widths = sorted(key[1] for key in ahead.step_fn._graphs if key[3] != 0)
+    assert fed_widths == [(4,), (4,), (8,), (8,), (16,), (16,)]
+    waiting = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 32, max_batch=4)
+    waiting.generator.step_fn.decode_ahead = lambda *a, **k: False
+    assert got == waiting.generate(prompts, max_new_tokens=330, stop_ids=(), temperature=0.7, seed=3)
+    assert [len(t) for t in got] == [330, 330, 330]
+    ahead.cache.check_invariants()
