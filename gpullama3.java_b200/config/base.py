@@ -4,8 +4,10 @@ A configuration is a typed record read from the architecture's own ``config.json
 its numbers it answers four questions, all as data, so that the engine holds no size or constant
 of any model:
 
-* ``layer_specs()``  which mixer, feed-forward, norm and block arrangement each layer has, with
-  the parameters of each part (sizes, eps, window, rope constants);
+* ``layer_specs()``  which block arrangement each layer has and which parts that block is given, by
+  the names the block itself uses (a pre-norm block takes ``mixer``, ``feed_forward`` and two norms;
+  another block may take fewer or other parts), each with its parameters (sizes, eps, window, rope
+  constants);
 * ``schedule()``     in which order layers run; a layer may appear twice, and an entry may read
   the cache that another entry writes;
 * ``tensor_names()`` under which checkpoint name each parameter of each part is stored;
@@ -25,19 +27,27 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class PartSpec:
-    """One part of a layer: the registered kind and the keyword arguments it is built with."""
+    """One part: the family it belongs to (``mixer``, ``feed_forward``, ``norm``, ``position``, ...), the kind
+    registered in that family, and the keyword arguments it is built with.  An argument may itself be a
+    PartSpec (an attention mixer's position encoding, a norm inside a mixer): it is built first and handed
+    over as a part."""
+    family: str
     kind: str
     args: dict[str, Any] = field(default_factory=dict)
+
+    def with_args(self, **changes) -> "PartSpec":
+        return PartSpec(self.family, self.kind, {**self.args, **changes})
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """The parts of one layer and the block that arranges them."""
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    block: str = "pre_norm"
+    """One layer: the registered block kind and the parts it is built from, under the names that block's
+    constructor takes.  Nothing else fixes which parts a layer has."""
+    block: str
+    parts: dict[str, PartSpec]
+
+    def with_parts(self, **changes: PartSpec) -> "LayerSpec":
+        return LayerSpec(self.block, {**self.parts, **changes})
 
 
 @dataclass(frozen=True)
@@ -85,6 +95,16 @@ class ModelConfig:
         """Map from a part's parameter path (``layers.3.mixer.q``, ``embedding.table``,
         ``final_norm.weight``, ``head.weight``) to its checkpoint tensor name."""
         raise NotImplementedError
+
+    def max_sequence_length(self) -> int | None:
+        """The longest sequence (prompt and generated tokens together) the model is meant for, if the
+        configuration gives one; generation stops there even when the cache has room for more."""
+        return None
+
+    def optional_tensor_names(self) -> set[str]:
+        """Checkpoint tensors that may be present without being read (some exporters store the output head
+        of a tied model a second time); anything else that the model does not declare is reported."""
+        return set()
 
     def init_std(self) -> float:
         """Standard deviation of random matrices in the random-weights mode."""

@@ -153,19 +153,20 @@ class LlamaConfig(ModelConfig):
 
     # ---- the model as data
     def layer_specs(self) -> list[LayerSpec]:
-        norm = PartSpec("rmsnorm", {"dim": self.hidden_size, "eps": self.rms_norm_eps})
-        position = PartSpec("rope", {
+        norm = self.final_norm()
+        position = PartSpec("position", "rope", {
             "head_dim": self.head_dim, "theta": self.rope_theta, "pairing": self.rope_pairing,
             "scaling": self.rope_scaling.to_dict() if self.rope_scaling else None})
-        mixer = PartSpec("attention", {
+        mixer = PartSpec("mixer", "attention", {
             "hidden_size": self.hidden_size, "n_heads": self.num_attention_heads,
             "n_kv_heads": self.num_key_value_heads, "head_dim": self.head_dim, "position": position, "window": None})
-        ff = PartSpec("swiglu", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size})
-        return [LayerSpec(mixer=mixer, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm)
-                for _ in range(self.num_hidden_layers)]
+        ff = PartSpec("feed_forward", "swiglu", {"hidden_size": self.hidden_size,
+                                                 "intermediate_size": self.intermediate_size})
+        layer = LayerSpec("pre_norm", {"mixer": mixer, "feed_forward": ff, "mixer_norm": norm, "feed_forward_norm": norm})
+        return [layer for _ in range(self.num_hidden_layers)]
 
     def final_norm(self) -> PartSpec:
-        return PartSpec("rmsnorm", {"dim": self.hidden_size, "eps": self.rms_norm_eps})
+        return PartSpec("norm", "rmsnorm", {"dim": self.hidden_size, "eps": self.rms_norm_eps})
 
     def tensor_names(self) -> dict[str, str]:
         names = {"embedding.table": "model.embed_tokens.weight", "final_norm.weight": "model.norm.weight"}
@@ -180,6 +181,14 @@ class LlamaConfig(ModelConfig):
             for w in ("gate", "up", "down"):
                 names[p + f"feed_forward.{w}"] = c + f"mlp.{w}_proj.weight"
         return names
+
+    def max_sequence_length(self) -> int:
+        # the reference caps every run at the configuration's context length
+        # (inference/InferenceEngine.java:75-77, model/llama/LlamaConfiguration.java:49-64 of the reference project)
+        return self.max_position_embeddings
+
+    def optional_tensor_names(self) -> set[str]:
+        return {"lm_head.weight"} if self.tie_word_embeddings else set()
 
     def init_std(self) -> float:
         return self.initializer_range

@@ -27,6 +27,7 @@
 //
 // Sizes: head_dim 32, 64, 96 or 128; group size (heads per kv head) <= 16.  Others are refused.
 #include "attention_decode_static.h"
+#include <cstdint>
 #include "common.cuh"
 
 namespace b200 {
@@ -406,6 +407,8 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     const int group = n_heads / n_kv_heads;
     if (group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128 || q_row_stride % 8 != 0) return kErrUnsupportedSize;
     if (n_seqs > 65535 || n_kv_heads > 65535) return kErrUnsupportedSize;
+    // queries, keys and values are read 16 bytes at a time
+    if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0) return kErrUnsupportedSize;
     if (fused && rope.pairing == 1 && head_dim != 64 && head_dim != 128) return kErrUnsupportedSize;
     if (fused && (rope.pairing < 0 || rope.pairing > 1 || rope.inv_freq == nullptr)) return kErrBadArgument;
     if (scratch_floats < b200_attention_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)) return 10003;
@@ -510,6 +513,8 @@ extern "C" int b200_attention_decode_static(const void* q, int q_row_stride, voi
         if (e != cudaSuccess) return (int)e;
         g_static_scratch_address[device] = scratch;
     }
+    // Not started early: the kernel reads kv_lens and page_table as soon as it is scheduled, and a caller of
+    // this entry point may well have written them with the kernel just before it on the stream.
     return b200_attention_decode(q, q_row_stride, out, kv_lens, page_table, table_stride, k_pool, v_pool, scratch,
-                                 kStaticScratchFloats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, 1, stream);
+                                 kStaticScratchFloats, n_seqs, n_heads, n_kv_heads, head_dim, window, n_splits, 0, stream);
 }

@@ -14,7 +14,13 @@
 // the library holds that array until the process exits, whether or not this function is called.
 //
 // What a caller has to know:
-//  * Inputs and outputs are the caller's, exactly as for b200_attention_decode.
+//  * Inputs and outputs are the caller's, exactly as for b200_attention_decode.  q, k_pool and v_pool
+//    must be 16-byte aligned (and q_row_stride a multiple of 8 elements); a call that
+//    is not is refused with 10002 and nothing is launched.
+//  * The kernel starts when everything before it on the stream has finished, so kv_lens and
+//    page_table may be written by the kernel right before the call.  (Inside the engine the regular
+//    entry point is allowed to start early, because there those two arrays are copied in ahead of
+//    the step's first kernel; this entry point does not assume that.)
 //  * A call whose partials do not fit (n_seqs * n_heads * n_splits * (head_dim + 2) floats more
 //    than the capacity) is refused with error 10004 and nothing is launched.  n_splits = 1 needs
 //    no scratch at all and always fits.

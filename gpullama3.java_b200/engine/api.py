@@ -12,6 +12,7 @@ from pathlib import Path
 
 import torch
 
+from ..cache.pages import PAGE_TOKENS
 from ..config.base import ModelConfig, read_config_json
 from ..config.registry import architecture_of
 from ..sampling.sampler import Sampler, SamplingParams
@@ -27,6 +28,17 @@ def _resolve_dtype(dtype) -> torch.dtype:
         return _DTYPES[dtype]
     except KeyError:
         raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+def resolve_max_length(config: ModelConfig, cache_tokens: int, asked: int | None = None) -> int:
+    """The longest sequence generation allows: what was asked for, else the smaller of what the cache holds
+    and the configuration's own context length."""
+    if asked is not None:
+        if asked < 1:
+            raise ValueError(f"max_length must be positive, got {asked}")
+        return int(asked)
+    limit = config.max_sequence_length()
+    return cache_tokens if limit is None else min(cache_tokens, int(limit))
 
 
 class _LoopStep:
@@ -51,7 +63,7 @@ class Engine:
         self.config: ModelConfig = model.config
         self.cache = model.new_cache(max_tokens, max_slots=max(max_batch, 1))
         self.step_fn = StepFunction(model, self.cache)
-        self.max_length = max_length if max_length is not None else self.cache.n_pages * 64
+        self.max_length = resolve_max_length(self.config, self.cache.n_pages * PAGE_TOKENS, max_length)
         self.generator = Generator(_LoopStep(self.step_fn), self.cache, Sampler, max_batch=max_batch,
                                    max_length=self.max_length)
 

@@ -94,7 +94,7 @@ class Generator:
             self.last_metrics = metrics
             return results
         sampler = self.sampler_factory(sampling)
-        n_pages = min(g.pool.n_pages for g in self.cache.kv_groups) if self.cache.kv_groups else 1 << 30
+        n_pages = self.cache.pages_for_planning()
         for batch in plan_batches([len(p) for p in prompts], max_new_tokens, min(self.max_batch, self.cache.max_slots),
                                   n_pages, self.max_length):
             slots = {i: self.cache.acquire() for i in batch}

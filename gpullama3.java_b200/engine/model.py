@@ -11,21 +11,12 @@ from pathlib import Path
 
 import torch
 
-from ..cache.sequence_cache import KVCacheNeed, SequenceCache, StateNeed
+from ..cache.sequence_cache import SequenceCache
 from ..config.base import ConfigError, ModelConfig, ScheduleEntry
-from ..parts.base import Block, Part, StepContext, _REGISTRIES, PartRegistryError, build_part
+from ..parts.base import Block, Part, StepContext, all_parts, build_block, build_part
 from ..parts.embedding import OutputHead, TokenEmbedding
 from ..weights.loader import ParamSpec, load_checkpoint_tensors
 from ..weights.safetensors_io import WeightError
-
-
-def _build_block(spec) -> Block:
-    reg = _REGISTRIES["block"]
-    if spec.block not in reg:
-        raise PartRegistryError(f"unknown block kind {spec.block!r}; registered: {', '.join(sorted(reg))}")
-    return reg[spec.block](mixer=build_part("mixer", spec.mixer), feed_forward=build_part("feed_forward", spec.feed_forward),
-                           mixer_norm=build_part("norm", spec.mixer_norm),
-                           feed_forward_norm=build_part("norm", spec.feed_forward_norm))
 
 
 class CausalLM:
@@ -34,8 +25,8 @@ class CausalLM:
             raise ConfigError(f"the engine runs in float32 or bfloat16, not {dtype}")
         self.config, self.dtype, self.device = config, dtype, torch.device(device)
         self.embedding = TokenEmbedding(config.vocab_size, config.hidden_size)
-        self.blocks: list[Block] = [_build_block(s) for s in config.layer_specs()]
-        self.final_norm = build_part("norm", config.final_norm())
+        self.blocks: list[Block] = [build_block(s) for s in config.layer_specs()]
+        self.final_norm = build_part(config.final_norm())
         self.head = OutputHead(config.vocab_size, config.hidden_size,
                                tied_to=self.embedding if config.tie_word_embeddings else None)
         self.schedule: list[ScheduleEntry] = list(config.schedule())
@@ -49,13 +40,13 @@ class CausalLM:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
                 raise ConfigError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
-            need = self.blocks[e.layer].mixer.cache_need()
+            need = self.blocks[e.layer].cache_need()
             if need is None:
                 if e.cache is not None:
-                    raise ConfigError(f"schedule entry {i}: layer {e.layer}'s mixer keeps no cache but entry names cache {e.cache}")
+                    raise ConfigError(f"schedule entry {i}: layer {e.layer} keeps no cache but the entry names cache {e.cache}")
                 continue
             if e.cache is None:
-                raise ConfigError(f"schedule entry {i}: layer {e.layer}'s mixer needs a cache entry")
+                raise ConfigError(f"schedule entry {i}: layer {e.layer} needs a cache entry")
             if e.cache in needs and needs[e.cache] != need:
                 raise ConfigError(f"schedule entry {i}: cache {e.cache} is shared by mixers with different needs")
             needs[e.cache] = need
@@ -72,16 +63,19 @@ class CausalLM:
         """Whether a decode step of this model may be recorded once and replayed as a CUDA graph."""
         return all(p.graph_safe for p in self.named_parts().values()) and all(b.graph_safe for b in self.blocks)
 
-    def cache_needs(self) -> dict[int, KVCacheNeed | StateNeed]:
+    def cache_needs(self) -> dict[int, object]:
+        """Cache entry id -> the need (KVCacheNeed, StateNeed, or a type of the mixer's own) of the runs that use it."""
         return dict(self._cache_needs)
 
     def named_parts(self) -> dict[str, Part]:
+        """Every part by its path: ``embedding``, ``layers.3.mixer``, ``layers.3.mixer.position``, ..."""
         parts: dict[str, Part] = {"embedding": self.embedding}
+        parts.update(all_parts(self.embedding, "embedding."))
         for i, b in enumerate(self.blocks):
-            for name, part in b.children().items():
-                parts[f"layers.{i}.{name}"] = part
-        parts["final_norm"] = self.final_norm
-        parts["head"] = self.head
+            parts.update(all_parts(b, f"layers.{i}."))
+        for name, part in (("final_norm", self.final_norm), ("head", self.head)):
+            parts[name] = part
+            parts.update(all_parts(part, name + "."))
         return parts
 
     def parameter_specs(self) -> dict[str, ParamSpec]:
@@ -116,10 +110,7 @@ class CausalLM:
 
     def load_folder(self, model_dir: str | Path) -> None:
         expected = {name: spec.shape for name, spec in self.checkpoint_specs().items()}
-        optional = set()
-        if self.config.tie_word_embeddings:
-            optional.add("lm_head.weight")  # some exporters store the tied head again; it is not read
-        tensors = load_checkpoint_tensors(model_dir, expected, self.dtype, optional)
+        tensors = load_checkpoint_tensors(model_dir, expected, self.dtype, set(self.config.optional_tensor_names()))
         self.load_tensors(tensors)
 
     def load_random(self, seed: int, *, norm_std: float = 0.0, store_dtype: torch.dtype = torch.bfloat16) -> None:

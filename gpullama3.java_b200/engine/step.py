@@ -40,7 +40,7 @@ def _pack(cache: SequenceCache, slots, start_pos, token_lists, logit_rows, width
     np.cumsum(q_lens, out=cu[1:])
     kv_lens = np.asarray([s + q for s, q in zip(start_pos, q_lens)], dtype=np.int32)
     tables = []
-    for gi in range(len(cache.kv_groups)):
+    for gi in range(len(cache.paged_groups)):
         rows = cache.page_rows(gi, slots)
         width = widths[gi] if widths is not None else max(1, max(len(r) for r in rows))
         tab = np.zeros((n, width), dtype=np.int32)  # unused entries name page 0: never read, never out of range
@@ -53,7 +53,7 @@ def _pack(cache: SequenceCache, slots, start_pos, token_lists, logit_rows, width
     return pieces, q_lens, [t.shape for t in tables]
 
 
-def _context_over(dev: torch.Tensor, sizes, table_shapes, dtype, device, slots, start_pos, q_lens):
+def _context_over(dev: torch.Tensor, sizes, table_shapes, dtype, device, slots, start_pos, q_lens, kv_capacity=None):
     views, off = [], 0
     for n in sizes:
         views.append(dev[off:off + n])
@@ -64,6 +64,7 @@ def _context_over(dev: torch.Tensor, sizes, table_shapes, dtype, device, slots, 
         max_kv_len=max(s + q for s, q in zip(start_pos, q_lens)), tokens=views[0], positions=views[1],
         seq_ids=views[2], cu_seqlens=views[3], kv_lens=views[4], slots_dev=views[5],
         page_tables=[v.view(shape) for v, shape in zip(views[7:], table_shapes)])
+    ctx.kv_capacity = list(kv_capacity) if kv_capacity is not None else [ctx.max_kv_len] * len(table_shapes)
     return ctx, views[6]
 
 
@@ -95,8 +96,6 @@ class DecodeGraph:
         """``tokens_dev``: where the draw leaves its tokens on the device (its own buffer if none is given).
         ``fed``: the step's input tokens are what ``tokens_dev`` holds when the step starts, i.e. the tokens the
         step before it drew for the same sequences; the host then stages positions and page tables only."""
-        from ..kernels import ops
-
         self.model, self.cache, self.n, self.widths = model, cache, n_seqs, list(widths)
         self.sampler = sampler                        # its launches are recorded after the model's, if given
         self.fed = bool(fed)
@@ -131,9 +130,8 @@ class DecodeGraph:
         self.last_slots: list[int] | None = None
         self.last_pos: list[int] | None = None
         self.last_owners = -1                         # the cache's ownership count at the last refresh
-        kv_heads = [g.need.n_kv_heads for g in cache.kv_groups] or [1]
-        self.kv_capacity = max(widths, default=1) * PAGE_TOKENS
-        self.splits = ops.attention_decode_splits(n_seqs, min(kv_heads), self.kv_capacity)
+        # the step is replayed for every length its page tables can address: parts shape their launches for that
+        self.kv_capacity = [w * PAGE_TOKENS for w in widths]
 
     def refresh(self, slots, start_pos, tokens, uniforms=None) -> None:
         """Fill the staging buffer for this step.  A step that continues the one before (same slots, still the
@@ -167,9 +165,7 @@ class DecodeGraph:
         """The step as it is issued and as it is recorded: staging buffer in, model, draw, tokens out."""
         self.dev.copy_(self.host, non_blocking=True)
         ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, slots,
-                                  start_pos, [1] * self.n)
-        ctx.extras["decode_splits"] = self.splits
-        ctx.extras["decode_kv_capacity"] = self.kv_capacity
+                                  start_pos, [1] * self.n, self.kv_capacity)
         if self.fed:
             ctx.tokens = self.tokens_dev  # read by the embedding before this step's draw overwrites it
         logits = self.model.forward(ctx, self.cache, rows)
@@ -252,7 +248,7 @@ class StepFunction:
         draw before it on the device (two, so that one can be staged while the other runs)."""
         cache = self.cache
         widths = []
-        for gi in range(len(cache.kv_groups)):
+        for gi in range(len(cache.paged_groups)):
             need = max(len(r) for r in cache.page_rows(gi, slots))
             w = 4
             while w < need:

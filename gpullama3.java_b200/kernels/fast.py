@@ -30,28 +30,16 @@ def try_decode_attention_with_rope(qkv, out, ctx, page_table, cache, mixer, writ
     if not (ctx.all_decode and ops.attention_decode_rope_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads,
                                                                    mixer.head_dim, pos.rotary_dim, pos.pairing)):
         return False
-    splits, early = _decode_launch_shape(ctx, mixer)
+    splits, early = mixer.plan_decode(ctx, cache)
     ops.attention_decode_rope(qkv, out, ctx.kv_lens, page_table, cache.k, cache.v, pos.inverse_frequencies(qkv.device),
                               mixer.n_heads, mixer.n_kv_heads, mixer.head_dim, pos.pairing, mixer.window or 0, splits,
                               write_cache=writes_cache, early_start=early)
     return True
 
 
-def _decode_launch_shape(ctx, mixer):
-    """Spans per sequence and whether the kernel may start early, from the longest sequence the step can hold
-    (a replayed graph fixes both for every step that fits its page tables)."""
-    capacity = ctx.extras.get("decode_kv_capacity") or ctx.max_kv_len
-    if mixer.window:
-        capacity = min(capacity, mixer.window)
-    splits = ctx.extras.get("decode_splits")
-    if splits is None:
-        splits = ops.attention_decode_splits(ctx.n_seqs, mixer.n_kv_heads, ctx.max_kv_len)
-    return splits, ops.attention_decode_early_start(ctx.n_seqs, mixer.n_kv_heads, capacity, splits)
-
-
 def try_attention(qkv, out, ctx, page_table, cache, mixer) -> bool:
     if ctx.all_decode and ops.attention_decode_supported(qkv.dtype, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim):
-        splits, early = _decode_launch_shape(ctx, mixer)
+        splits, early = mixer.plan_decode(ctx, cache)
         ops.attention_decode(qkv, qkv.shape[1], out, ctx.kv_lens, page_table, cache.k, cache.v, mixer.n_heads,
                              mixer.n_kv_heads, mixer.head_dim, mixer.window or 0, splits, early_start=early)
         return True

@@ -12,6 +12,9 @@ from .build import KernelBuildError, library
 
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64  # must equal b200::kPageTokens
+# what the plain kernels, which take every size the others refuse, are built for
+HEAD_DIM_STEP, MAX_HEAD_DIM = 16, 256   # attention_generic.cu
+MAX_ROTARY_DIM = 512                    # rope_cache.cu
 
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -87,6 +90,7 @@ def _fn(name: str):
 
 
 _launches = 0
+_launches_by_kernel: dict[str, int] = {}
 
 
 def launch_count() -> int:
@@ -94,9 +98,16 @@ def launch_count() -> int:
     return _launches
 
 
+def launches_by_kernel() -> dict[str, int]:
+    """The same count per kernel function (a copy).  A launch recorded into a CUDA graph counts once, when it
+    is recorded.  Decode attention that was told not to start early counts under ``<name>:late``."""
+    return dict(_launches_by_kernel)
+
+
 def _check(status: int, name: str) -> None:
     global _launches
     _launches += 1
+    _launches_by_kernel[name] = _launches_by_kernel.get(name, 0) + 1
     if status != 0:
         what = _ERRORS.get(status)
         if what is None:
@@ -350,9 +361,14 @@ def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int
     return dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) and n_heads // n_kv_heads <= 16
 
 
-def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resident_ctas: int = 592) -> int:
+def resident_ctas(device) -> int:
+    """How many CTAs of the decode attention kernel the GPU holds at once (four per SM)."""
+    return 4 * _sm_count(torch.device(device))
+
+
+def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resident_ctas: int) -> int:
     """How many spans each sequence's keys are cut into.  The grid (spans x kv heads x sequences)
-    should fill the GPU in one wave (148 SMs x 4 resident CTAs) without spilling into a second one,
+    should fill the GPU in one wave (``resident_ctas``) without spilling into a second one,
     and a span should keep at least 8 blocks of 32 keys so that its start-up and the merge pay."""
     blocks = max(1, (max_kv_len + 31) // 32)
     cap = max(1, resident_ctas // max(1, n_seqs * n_kv_heads))
@@ -400,7 +416,8 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, kv_lens: torch.T
         qkv.data_ptr(), qkv.shape[1], out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
         n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, inv_freq.data_ptr(), pairing,
-        1 if write_cache else 0, 1 if early_start else 0, _stream()), "attention_decode_rope")
+        1 if write_cache else 0, 1 if early_start else 0, _stream()),
+        "attention_decode_rope" if early_start else "attention_decode_rope:late")
 
 
 def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_lens: torch.Tensor,
@@ -422,7 +439,7 @@ def attention_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, kv_l
         q.data_ptr(), q_row_stride, out.data_ptr(), kv_lens.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         k_pool.data_ptr(), v_pool.data_ptr(), scratch.data_ptr() if need else None, scratch.numel() if need else 0,
         n_seqs, n_heads, n_kv_heads, head_dim, int(window), n_splits, 1 if early_start else 0, _stream()),
-        "attention_decode")
+        "attention_decode" if early_start else "attention_decode:late")
 
 
 def attention_prefill(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cu_seqlens: torch.Tensor,

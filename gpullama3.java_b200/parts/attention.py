@@ -10,6 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.sequence_cache import KVCacheNeed, KVView
+from ..config.base import ConfigError
 from ..kernels import fast, ops
 from ..weights.loader import ParamSpec
 from .base import Mixer, PositionEncoding, StepContext, register_mixer
@@ -22,7 +23,16 @@ class GroupedQueryAttention(Mixer):
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  window: int | None = None):
         if n_heads % n_kv_heads:
-            raise ValueError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
+            raise ConfigError(f"n_heads {n_heads} must be a multiple of n_kv_heads {n_kv_heads}")
+        # what no kernel takes is refused here, when the model is built, not at the first step
+        if head_dim % ops.HEAD_DIM_STEP or not (0 < head_dim <= ops.MAX_HEAD_DIM):
+            raise ConfigError(f"head_dim {head_dim}: the attention kernels take head sizes in steps of "
+                              f"{ops.HEAD_DIM_STEP} up to {ops.MAX_HEAD_DIM}")
+        if position.rotary_dim > min(head_dim, ops.MAX_ROTARY_DIM) or position.rotary_dim % 2:
+            raise ConfigError(f"rotary_dim {position.rotary_dim} must be even and at most "
+                              f"{min(head_dim, ops.MAX_ROTARY_DIM)} (head_dim {head_dim})")
+        if window is not None and window < 1:
+            raise ConfigError(f"window {window} must be at least 1 (or None for no window)")
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
         self.position, self.window = position, window
         self.q_dim, self.kv_dim = n_heads * head_dim, n_kv_heads * head_dim
@@ -33,8 +43,22 @@ class GroupedQueryAttention(Mixer):
         return {"q": ParamSpec((self.q_dim, self.hidden_size)), "k": ParamSpec((self.kv_dim, self.hidden_size)),
                 "v": ParamSpec((self.kv_dim, self.hidden_size)), "o": ParamSpec((self.hidden_size, self.q_dim))}
 
+    def children(self):
+        return {"position": self.position}
+
     def cache_need(self):
         return KVCacheNeed(self.n_kv_heads, self.head_dim, self.window)
+
+    def plan_decode(self, ctx: StepContext, cache: KVView) -> tuple[int, bool]:
+        """How a decode step's attention is launched: into how many spans each sequence's keys are cut, and
+        whether the kernel may be scheduled while its predecessor still runs.  Both follow from the number of
+        sequences, this mixer's own kv heads and the longest sequence the step must be right for (its cache
+        group's ``kv_capacity``: a recorded step is replayed until its page tables are outgrown)."""
+        capacity = ctx.capacity(cache.group)
+        if self.window:
+            capacity = min(capacity, self.window)
+        splits = ops.attention_decode_splits(ctx.n_seqs, self.n_kv_heads, capacity, ops.resident_ctas(ctx.device))
+        return splits, ops.attention_decode_early_start(ctx.n_seqs, self.n_kv_heads, capacity, splits)
 
     def load(self, tensors, dtype, device):
         q, k, v, o = (tensors[n].to(device) for n in ("q", "k", "v", "o"))

@@ -6,8 +6,9 @@ A part owns its sizes and constants as constructor parameters, declares its para
 which model it is in: names of checkpoint tensors, the number of layers and the order of layers
 live in the configuration.
 
-Adding a part = subclass the interface below and call the matching ``register_*`` with a kind
-name; a configuration then names that kind in its ``LayerSpec``.
+Adding a part = subclass the interface below and call the matching ``register_*`` (or
+``register_part`` with a family name of one's own) with a kind name; a configuration then names
+family and kind in a ``PartSpec``.
 """
 from __future__ import annotations
 
@@ -41,8 +42,15 @@ class StepContext:
     cu_seqlens: torch.Tensor         # [n_seqs + 1]
     kv_lens: torch.Tensor            # [n_seqs] start_pos + q_len
     slots_dev: torch.Tensor          # [n_seqs]
-    page_tables: list[torch.Tensor]  # per KV cache group: [n_seqs, width] physical page ids
+    page_tables: list[torch.Tensor]  # per paged cache group: [n_seqs, width] physical page ids
+    # per paged cache group: the longest sequence this step's launches must be right for.  A step that runs
+    # once needs no more than max_kv_len; a recorded decode step is replayed while its page tables can address
+    # the sequences, so a part that shapes its launch by length (spans of keys) shapes it for this number.
+    kv_capacity: list[int] = field(default_factory=list)
     extras: dict = field(default_factory=dict)  # scratch a part may keep for the duration of a step
+
+    def capacity(self, group: int) -> int:
+        return self.kv_capacity[group] if group < len(self.kv_capacity) else self.max_kv_len
 
 
 @dataclass
@@ -81,6 +89,11 @@ class Part:
     def load(self, tensors: dict[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
         """Take the parameters (CPU or device tensors by local name), move and re-lay them out for
         the kernels.  ``dtype`` is the run's precision."""
+
+    def children(self) -> dict[str, "Part"]:
+        """Parts this part was built with, by the names it gives them.  Their parameters are declared and
+        loaded under ``<this part's path>.<name>``; the part itself only declares its own."""
+        return {}
 
 
 class Norm(Part):
@@ -134,15 +147,26 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of one layer's parts around the residual stream."""
+    """Arrangement of one layer's parts around the residual stream.  A block's constructor takes its parts
+    by keyword, under names of its own choosing (the configuration's ``LayerSpec.parts`` uses the same names)
+    and hands them to ``Block.__init__``; which parts a layer has is therefore the block's business alone."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    def __init__(self, **parts: Part):
+        self.parts: dict[str, Part] = dict(parts)
+        for name, part in parts.items():
+            setattr(self, name, part)
 
     def children(self) -> dict[str, Part]:
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward, "mixer_norm": self.mixer_norm,
-                "feed_forward_norm": self.feed_forward_norm}
+        return dict(self.parts)
+
+    def cache_need(self):
+        """What one run of this block keeps per sequence: the need of its one part that has any."""
+        needs = [(n, p.cache_need()) for n, p in self.parts.items() if hasattr(p, "cache_need")]
+        needs = [(n, need) for n, need in needs if need is not None]
+        if len(needs) > 1:
+            raise ValueError("a block with several caching parts (" + ", ".join(n for n, _ in needs) +
+                             ") must say itself what one run of it keeps (override cache_need)")
+        return needs[0][1] if needs else None
 
     def forward(self, residual: torch.Tensor, ctx: StepContext, cache, writes_cache: bool = True) -> None:
         """Runs the layer on the float32 ``residual`` in place.  A block whose ``takes_scaled_rows(ctx)`` is
@@ -158,6 +182,16 @@ class Block(Part):
         return None
 
 
+def all_parts(root: Part, prefix: str = "") -> dict[str, Part]:
+    """Every part below ``root`` by dotted path (``mixer``, ``mixer.position``), parents before children."""
+    out: dict[str, Part] = {}
+    for name, part in root.children().items():
+        path = f"{prefix}{name}"
+        out[path] = part
+        out.update(all_parts(part, path + "."))
+    return out
+
+
 class PartRegistryError(KeyError):
     pass
 
@@ -165,50 +199,76 @@ class PartRegistryError(KeyError):
 _REGISTRIES: dict[str, dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
 
 
-def _register(family: str, kind: str, cls: type, replace: bool) -> None:
-    reg = _REGISTRIES[family]
+def register_part(family: str, kind: str, cls: type, *, replace: bool = False) -> None:
+    """Register ``cls`` as ``kind`` of ``family``; a family that does not exist yet is created."""
+    reg = _REGISTRIES.setdefault(family, {})
     if kind in reg and not replace:
         raise PartRegistryError(f"{family} kind {kind!r} is already registered")
     reg[kind] = cls
 
 
 def register_mixer(kind: str, cls: type, *, replace: bool = False) -> None:
-    _register("mixer", kind, cls, replace)
+    register_part("mixer", kind, cls, replace=replace)
 
 
 def register_feed_forward(kind: str, cls: type, *, replace: bool = False) -> None:
-    _register("feed_forward", kind, cls, replace)
+    register_part("feed_forward", kind, cls, replace=replace)
 
 
 def register_norm(kind: str, cls: type, *, replace: bool = False) -> None:
-    _register("norm", kind, cls, replace)
+    register_part("norm", kind, cls, replace=replace)
 
 
 def register_position_encoding(kind: str, cls: type, *, replace: bool = False) -> None:
-    _register("position", kind, cls, replace)
+    register_part("position", kind, cls, replace=replace)
 
 
 def register_block(kind: str, cls: type, *, replace: bool = False) -> None:
-    _register("block", kind, cls, replace)
+    register_part("block", kind, cls, replace=replace)
 
 
 def unregister(family: str, kind: str) -> None:
-    _REGISTRIES[family].pop(kind, None)
+    _REGISTRIES.get(family, {}).pop(kind, None)
 
 
 def registered(family: str) -> list[str]:
-    return sorted(_REGISTRIES[family])
+    return sorted(_REGISTRIES.get(family, {}))
 
 
-def build_part(family: str, spec) -> Part:
-    """Instantiate the registered class of ``spec.kind`` with ``spec.args``.  Arguments that are
-    themselves part specs under the key ``position`` are built first."""
+def _registered_class(family: str, kind: str) -> type:
+    reg = _REGISTRIES.get(family)
+    if reg is None:
+        raise PartRegistryError(f"unknown part family {family!r}; families: {', '.join(sorted(_REGISTRIES))}")
+    if kind not in reg:
+        raise PartRegistryError(f"unknown {family} kind {kind!r}; registered: {', '.join(sorted(reg)) or 'none'}")
+    return reg[kind]
+
+
+def _built(value):
+    """``value`` with every PartSpec in it (also inside lists, tuples and dicts) replaced by the built part."""
     from ..config.base import PartSpec
 
-    reg = _REGISTRIES[family]
-    if spec.kind not in reg:
-        raise PartRegistryError(f"unknown {family} kind {spec.kind!r}; registered: {', '.join(sorted(reg)) or 'none'}")
-    args = dict(spec.args)
-    if isinstance(args.get("position"), PartSpec):
-        args["position"] = build_part("position", args["position"])
-    return reg[spec.kind](**args)
+    if isinstance(value, PartSpec):
+        return build_part(value)
+    if isinstance(value, (list, tuple)):
+        return type(value)(_built(v) for v in value)
+    if isinstance(value, dict):
+        return {k: _built(v) for k, v in value.items()}
+    return value
+
+
+def build_part(spec) -> Part:
+    """Instantiate the class registered as ``spec.kind`` in ``spec.family`` with ``spec.args``; arguments that
+    are part specs themselves are built first, whatever their key."""
+    cls = _registered_class(spec.family, spec.kind)
+    return cls(**{k: _built(v) for k, v in spec.args.items()})
+
+
+def build_block(spec) -> Block:
+    """The block of a ``LayerSpec``: its registered class, given the layer's built parts by name."""
+    cls = _registered_class("block", spec.block)
+    try:
+        return cls(**{name: build_part(p) for name, p in spec.parts.items()})
+    except TypeError as e:
+        raise PartRegistryError(f"block kind {spec.block!r} does not take the parts "
+                                f"{sorted(spec.parts)}: {e}") from e

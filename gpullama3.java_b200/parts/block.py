@@ -2,13 +2,18 @@
 inference/InferenceCore.java:72-173 of the reference project.  The residual stream is float32."""
 from __future__ import annotations
 
-from .base import Block, StepContext, register_block
+from .base import Block, StepContext, all_parts, register_block
 
 
 class PreNormBlock(Block):
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm):
+        super().__init__(mixer=mixer, feed_forward=feed_forward, mixer_norm=mixer_norm,
+                         feed_forward_norm=feed_forward_norm)
+
     @property
     def graph_safe(self):
-        return all(p.graph_safe for p in self.children().values())
+        # the block itself launches nothing; its decode step is as replayable as its parts' launches are
+        return all(p.graph_safe for p in all_parts(self).values())
 
     def first_norm(self):
         return self.mixer_norm

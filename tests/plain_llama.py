@@ -130,7 +130,7 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: 
     for h in range(H):
         g = h // kv_mul
         scores = (q[:, h, :] @ k[:, g, :].t()) / scale  # [T, T]
-        pos = torch.arange(T)
+        pos = torch.arange(T, device=q.device)
         mask = pos[None, :] <= pos[:, None]
         if window is not None:
             mask = mask & (pos[None, :] > pos[:, None] - window)
@@ -149,11 +149,21 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 # --------------------------------------------------------------------------- whole model
 def forward(config: dict, weights: dict, tokens, *, dtype=torch.float32, round_to=None,
-            pairing: str | None = None, window: int | None = None) -> torch.Tensor:
+            pairing: str | None = None, window: int | None = None, device=None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence, ``InferenceCore.java:58-180`` run for every
     position at once.  ``weights`` uses checkpoint names (``model.layers.0.self_attn.q_proj.weight``
-    ...), the roles of ``model/loader/ModelLoader.java:265-303``."""
+    ...), the roles of ``model/loader/ModelLoader.java:265-303``.
+
+    ``device``: where torch evaluates these same lines (default: where the weights are, the CPU in
+    almost every test).  Tests at the layer sizes of the real models pass ``"cuda"`` so that a float64
+    run over a thousand tokens takes seconds instead of minutes; reduced-precision matrix modes must be
+    off there, which is checked."""
+    if device is not None and torch.device(device).type == "cuda":
+        assert not torch.backends.cuda.matmul.allow_tf32 and torch.get_float32_matmul_precision() == "highest"
+        weights = {k: t.to(device) for k, t in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
+    if device is not None:
+        tokens = tokens.to(device)
     T = tokens.numel()
     H = config["num_attention_heads"]
     KVH = config.get("num_key_value_heads", H)
@@ -169,6 +179,7 @@ def forward(config: dict, weights: dict, tokens, *, dtype=torch.float32, round_t
 
     inv_freq = rope_inverse_frequencies(D, theta, scaling)
     cos, sin = rope_tables(torch.arange(T), inv_freq, dtype)
+    cos, sin = cos.to(tokens.device), sin.to(tokens.device)
 
     x = embedding(W["model.embed_tokens.weight"], tokens)
     for l in range(config["num_hidden_layers"]):
@@ -186,7 +197,7 @@ def forward(config: dict, weights: dict, tokens, *, dtype=torch.float32, round_t
         x = x + linear(h, W[p + "mlp.down_proj.weight"])
     x = _round(rmsnorm(x, W["model.norm.weight"], eps), round_to)
     head = W["lm_head.weight"] if "lm_head.weight" in W else W["model.embed_tokens.weight"]
-    return linear(x, head).to(torch.float32)
+    return linear(x, head).to(torch.float32).cpu()
 
 
 # --------------------------------------------------------------------------- sampling

@@ -44,8 +44,8 @@ def _cache(max_tokens=64 * 6, **kw):
 
 def test_groups_have_storage_of_their_own():
     c = _cache()
-    assert len(c.kv_groups) == 2
-    g0, g1 = c.kv_groups
+    assert len(c.paged_groups) == 2
+    g0, g1 = c.paged_groups
     assert g0.entries == [0, 1] and g1.entries == [2]
     assert tuple(g0.k.shape) == (2, 6, 2, PAGE_TOKENS, 16) and tuple(g1.v.shape) == (1, 6, 1, 32, PAGE_TOKENS)
     v0, v1, v2 = c.view(0), c.view(1), c.view(2)
@@ -122,17 +122,17 @@ def test_random_walk_never_loses_or_doubles_a_page():
             except CacheFull:
                 pass
         c.check_invariants()
-        for g in c.kv_groups:
+        for g in c.paged_groups:
             assert g.pool.n_held == sum(pages_for(c.length(s)) for s in live)
     for s in live:
         c.release(s)
-    assert all(g.pool.n_free == g.pool.n_pages for g in c.kv_groups) and c.slots.n_free == 5
+    assert all(g.pool.n_free == g.pool.n_pages for g in c.paged_groups) and c.slots.n_free == 5
 
 
 def test_windowed_group_lets_go_of_pages_no_query_can_reach():
     needs = {0: KVCacheNeed(1, 16), 1: KVCacheNeed(1, 16, window=70)}
     c = SequenceCache(needs, max_tokens=64 * 32, max_slots=2, dtype=torch.float32, device="cpu", window_slack=64)
-    full, win = (g for g in c.kv_groups)
+    full, win = (g for g in c.paged_groups)
     assert full.need.window is None and win.need.window == 70
     assert win.pool.n_pages == 2 * (pages_for(70 + 64) + 1) < full.pool.n_pages
     s = c.acquire()
@@ -151,7 +151,7 @@ def test_windowed_group_lets_go_of_pages_no_query_can_reach():
 def test_fixed_size_state_is_zeroed_when_a_slot_is_taken():
     needs = {0: KVCacheNeed(1, 16), 1: StateNeed((3, 4)), 2: StateNeed((3, 4)), 3: StateNeed((2,), torch.int32)}
     c = SequenceCache(needs, max_tokens=128, max_slots=3, dtype=torch.float32, device="cpu")
-    assert len(c.state_groups) == 2 and tuple(c.state_groups[0].data.shape) == (2, 3, 3, 4)
+    assert len(c.slot_groups) == 2 and tuple(c.slot_groups[0].data.shape) == (2, 3, 3, 4)
     s = c.acquire()
     c.view(1).data[s] += 5.0
     c.view(3).data[s] += 2
@@ -163,4 +163,4 @@ def test_fixed_size_state_is_zeroed_when_a_slot_is_taken():
 
 def test_llama_has_no_fixed_state_but_the_cache_has_room_for_it():
     c = _cache()
-    assert c.state_groups == []
+    assert c.slot_groups == []

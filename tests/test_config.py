@@ -98,10 +98,12 @@ def test_the_model_is_data():
     specs = c.layer_specs()
     assert len(specs) == 3
     s = specs[0]
-    assert s.mixer.kind == "attention" and s.feed_forward.kind == "swiglu" and s.mixer_norm.kind == "rmsnorm"
-    assert s.mixer.args["n_heads"] == 3 and s.mixer.args["n_kv_heads"] == 1 and s.mixer.args["head_dim"] == 32
-    assert s.mixer.args["position"].kind == "rope" and s.mixer.args["position"].args["theta"] == 500000.0
-    assert s.mixer_norm.args["eps"] == 1e-6 and s.feed_forward.args["intermediate_size"] == 256
+    assert s.block == "pre_norm" and sorted(s.parts) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm"]
+    assert s.parts["mixer"].kind == "attention" and s.parts["feed_forward"].kind == "swiglu"
+    assert s.parts["mixer_norm"].kind == "rmsnorm" and s.parts["mixer_norm"].family == "norm"
+    assert s.parts["mixer"].args["n_heads"] == 3 and s.parts["mixer"].args["n_kv_heads"] == 1 and s.parts["mixer"].args["head_dim"] == 32
+    assert s.parts["mixer"].args["position"].kind == "rope" and s.parts["mixer"].args["position"].args["theta"] == 500000.0
+    assert s.parts["mixer_norm"].args["eps"] == 1e-6 and s.parts["feed_forward"].args["intermediate_size"] == 256
     assert [e.layer for e in c.schedule()] == [0, 1, 2] and [e.cache for e in c.schedule()] == [0, 1, 2]
     names = c.tensor_names()
     assert names["layers.2.mixer.k"] == "model.layers.2.self_attn.k_proj.weight"

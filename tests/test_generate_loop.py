@@ -71,7 +71,7 @@ def test_unequal_prompts_one_step_then_one_token_each():
     assert sorted(n for _, n in step.calls[0]) == [3, 11, 17]            # all prompts in one step
     assert all(n == 1 for call in step.calls[1:] for _, n in call)       # then one token each
     assert len(step.calls) == 4                                          # the 4th token is not fed back
-    assert cache.live_slots() == [] and cache.kv_groups[0].pool.n_held == 0
+    assert cache.live_slots() == [] and cache.paged_groups[0].pool.n_held == 0
     m = gen.last_metrics
     assert (m.prompt_tokens, m.generated_tokens, m.decode_steps) == (31, 12, 3)
 
@@ -247,7 +247,7 @@ def test_steps_launched_one_ahead_give_the_same_tokens():
         got = gen.generate(prompts, new, SamplingParams(), stop_ids=stop, on_token=lambda i, t: seen.append((i, t)))
         assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want], trial
         assert sorted(seen) == sorted((i, t) for i, r in enumerate(want) for t in r.tokens)
-        assert step.in_flight == [] and cache.live_slots() == [] and cache.kv_groups[0].pool.n_held == 0
+        assert step.in_flight == [] and cache.live_slots() == [] and cache.paged_groups[0].pool.n_held == 0
         # token number d of a request (counting from 0, the prompt step's) was drawn as its draw d; a step launched
         # ahead may have drawn one more for a request that a stop token had just ended, and nothing beyond that
         drawn = {}

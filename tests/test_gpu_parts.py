@@ -209,10 +209,8 @@ class ToyConfig(LlamaConfig):
 
     def layer_specs(self):
         base = super().layer_specs()[0]
-        toy = LayerSpec(PartSpec("test_running_mean", {"hidden_size": self.hidden_size}), base.feed_forward,
-                        base.mixer_norm, base.feed_forward_norm)
-        windowed = LayerSpec(PartSpec("attention", dict(base.mixer.args, window=self.window)), base.feed_forward,
-                             base.mixer_norm, base.feed_forward_norm)
+        toy = base.with_parts(mixer=PartSpec("mixer", "test_running_mean", {"hidden_size": self.hidden_size}))
+        windowed = base.with_parts(mixer=base.parts["mixer"].with_args(window=self.window))
         return [base, toy, windowed, base]
 
     def schedule(self):
@@ -294,7 +292,7 @@ def test_toy_architecture_with_state_is_registered_built_and_stepped(toy_registe
     assert needs[1] == StateNeed((65,), torch.float32) and needs[3] == KVCacheNeed(2, 16, 40)
     assert needs[0] == needs[2] == KVCacheNeed(2, 16, None) and set(needs) == {0, 1, 2, 3}
     cache = model.new_cache(64 * 12, max_slots=3, window_slack=256)
-    assert len(cache.kv_groups) == 2 and len(cache.state_groups) == 1
+    assert len(cache.paged_groups) == 2 and len(cache.slot_groups) == 1
     step = StepFunction(model, cache)
     prompts = [torch.randint(0, 256, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (150, 70, 9)]
 
@@ -405,11 +403,13 @@ class ToyRoutedConfig(LlamaConfig):
 
     def layer_specs(self):
         base = super().layer_specs()[0]
-        pos = PartSpec("test_half_rotary", {"head_dim": self.head_dim, "theta": self.rope_theta, "factor": self.rope_factor})
-        mixer = PartSpec("attention", dict(base.mixer.args, position=pos))
-        ff = PartSpec("test_top1_experts", {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
-                                            "n_experts": self.n_experts})
-        return [LayerSpec(mixer, ff, base.mixer_norm, base.feed_forward_norm) for _ in range(self.num_hidden_layers)]
+        pos = PartSpec("position", "test_half_rotary", {"head_dim": self.head_dim, "theta": self.rope_theta,
+                                                        "factor": self.rope_factor})
+        ff = PartSpec("feed_forward", "test_top1_experts", {"hidden_size": self.hidden_size,
+                                                            "intermediate_size": self.intermediate_size,
+                                                            "n_experts": self.n_experts})
+        layer = base.with_parts(mixer=base.parts["mixer"].with_args(position=pos), feed_forward=ff)
+        return [layer for _ in range(self.num_hidden_layers)]
 
     def tensor_names(self):
         names = {"embedding.table": "wte", "final_norm.weight": "ln_f", "head.weight": "head"}

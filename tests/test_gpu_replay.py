@@ -173,3 +173,32 @@ def test_slots_given_to_new_sequences_at_the_position_the_old_ones_stopped(sessi
         ref = plain_llama.forward(cfg, w, by_slot[s], round_to=torch.bfloat16)[-1]
         assert_close_logits(out[i], ref, torch.bfloat16, f"sequence in slot {s}")
     cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_one_step_holds_a_decoded_token_a_chunk_and_a_fresh_prompt(setup, dtype):
+    """Three sequences in one step, each at another stage: one goes on by a single token behind 70 cached ones, one
+    brings the middle chunk of its prompt (positions 40..99 of 129), one starts.  Then all three go on together by
+    one token.  Every wanted place gives the plain implementation's logits for the whole sequence."""
+    from gpullama3.java_b200.engine.step import SequenceInput, StepFunction
+    from gpullama3.java_b200.engine.trace import load_model
+
+    d, cfg, weights, requests, refs = setup
+    if dtype not in refs:
+        refs[dtype] = _reference(cfg, weights, requests, dtype)
+    model = load_model(d, dtype)
+    cache = model.new_cache(64 * 6)
+    step = StepFunction(model, cache)
+    one, chunk, fresh = requests["r3"], requests["r4"], requests["r0"]            # 100, 129 and 33 tokens
+    a, b, c = cache.acquire(), cache.acquire(), cache.acquire()
+    step([SequenceInput(a, one[:70], []), SequenceInput(b, chunk[:40], [])])
+    out = step([SequenceInput(a, [one[70]], [0]), SequenceInput(b, chunk[40:100], [0, 30, 59]),
+                SequenceInput(c, fresh[:20], [0, 19])]).cpu()
+    ref = refs[dtype]
+    assert_close_logits(out[0:1], ref["r3"][[70]], dtype, "the sequence that goes on by one token")
+    assert_close_logits(out[1:4], ref["r4"][[40, 70, 99]], dtype, "the middle chunk")
+    assert_close_logits(out[4:6], ref["r0"][[0, 19]], dtype, "the fresh prompt")
+    out = step([SequenceInput(a, [one[71]], [0]), SequenceInput(b, [chunk[100]], [0]), SequenceInput(c, [fresh[20]], [0])]).cpu()
+    assert_close_logits(out, torch.stack([ref["r3"][71], ref["r4"][100], ref["r0"][20]]), dtype, "then one token each")
+    assert [cache.length(s) for s in (a, b, c)] == [72, 101, 21]
+    cache.check_invariants()

@@ -35,6 +35,21 @@ def _problem(seed, kv_lens, H, KVH, D):
     return [t.cuda().contiguous() for t in (qkv, torch.tensor(kv_lens, dtype=torch.int32), table, k_pool, v_pool)]
 
 
+def _plain(qkv, kv_lens, table, k_pool, v_pool, H, KVH, D):
+    """The plain implementation's attention of each sequence's one query over its cached keys."""
+    import plain_llama as P
+
+    rows = []
+    for i, n in enumerate(kv_lens):
+        pages = table[i, : -(-n // 64)].long().cpu()
+        k = k_pool.cpu().float()[pages].permute(0, 2, 1, 3).reshape(-1, KVH, D)[:n]        # [n, KVH, D]
+        v = v_pool.cpu().float()[pages].permute(0, 3, 1, 2).reshape(-1, KVH, D)[:n]
+        q = torch.zeros(n, H, D)
+        q[-1] = qkv[i, : H * D].cpu().float().view(H, D)                                    # the query sits at the last position
+        rows.append(P.causal_attention(q, k, v)[-1].reshape(H * D))
+    return torch.stack(rows)
+
+
 def test_entry_point_without_allocation_matches_the_regular_one():
     from gpullama3.java_b200.kernels import ops
     from gpullama3.java_b200.kernels.build import library
@@ -54,19 +69,31 @@ def test_entry_point_without_allocation_matches_the_regular_one():
         want = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
         ops.attention_decode(qkv, qkv.shape[1], want, lens, table, k_pool, v_pool, H, KVH, D, 0, splits)
         got = torch.full_like(want, 7.0)
+        # The lengths reach the device through a kernel that runs right before the call, as they would in a
+        # serving loop that keeps them on the device: the entry point must not read them before that kernel is done.
+        lens_late = torch.zeros_like(lens)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        status = fn(qkv.data_ptr(), qkv.shape[1], got.data_ptr(), lens.data_ptr(), table.data_ptr(), table.shape[1],
+        free_before, _ = torch.cuda.mem_get_info()      # the driver's own count: sees any cudaMalloc, not only torch's
+        lens_late.add_(lens)
+        status = fn(qkv.data_ptr(), qkv.shape[1], got.data_ptr(), lens_late.data_ptr(), table.data_ptr(), table.shape[1],
                     k_pool.data_ptr(), v_pool.data_ptr(), B, H, KVH, D, 0, splits, stream)
         torch.cuda.synchronize()
         assert status == 0
-        assert torch.cuda.memory_allocated() == before
-        # the tolerance of the decode-attention tests; the two entry points run the same kernels
-        scale = float(want.float().abs().max())
-        torch.testing.assert_close(got.float(), want.float(), rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.equal(got, want)                   # the same kernels on the same inputs: the same bits
+        ref = _plain(qkv, kv_lens, table, k_pool, v_pool, H, KVH, D)
+        scale = float(ref.abs().max())
+        torch.testing.assert_close(got.float().cpu(), ref, rtol=2.0 ** -7, atol=2.0 ** -8 * scale)
 
-    # 64 sequences x 32 heads x 16 spans x (128 + 2) floats = 4.26 M floats: more than the array holds
+    # Too large for the array: 64 sequences x 32 heads x 16 spans x (128 + 2) floats = 4.26 M floats.  The inputs
+    # have the sizes the call names, so that a call wrongly let through would still stay inside them.
+    qkv, lens, table, k_pool, v_pool = _problem(3, [40] * 64, 32, 8, 128)
+    got = torch.zeros(64, 32 * 128, dtype=torch.bfloat16, device="cuda")
     status = fn(qkv.data_ptr(), qkv.shape[1], got.data_ptr(), lens.data_ptr(), table.data_ptr(), table.shape[1],
                 k_pool.data_ptr(), v_pool.data_ptr(), 64, 32, 8, 128, 0, 16, stream)
     assert status == 10004
+    # Misaligned queries (raw pointers come from anywhere): refused, not faulted on.
+    status = fn(qkv.data_ptr() + 2, qkv.shape[1], got.data_ptr(), lens.data_ptr(), table.data_ptr(), table.shape[1],
+                k_pool.data_ptr(), v_pool.data_ptr(), 63, 32, 8, 128, 0, 1, stream)
+    assert status == 10002
     torch.cuda.synchronize()
