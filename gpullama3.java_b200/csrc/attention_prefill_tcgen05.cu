@@ -68,6 +68,27 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+
+// The values of a block arrive as whole pages, and the page that holds a sequence's last key also holds whatever an
+// earlier owner left behind it.  Those keys get probability 0, but 0 times a value that is not finite is not 0: the
+// values of keys at or beyond the sequence's end are therefore set to zero in shared memory before O += P V reads
+// them.  v0, v1: the block's two halves of 64 keys, each [D][64] bfloat16 in 128-byte rows with the 128-byte swizzle
+// (the 16-byte chunk index XORed with row % 8); first_stale: the first such key, counted from the block's first.
+template <int D>
+__device__ __forceinline__ void zero_values_beyond_end(__nv_bfloat16* v0, __nv_bfloat16* v1, int first_stale, int tid, int n_threads) {
+    for (int item = tid; item < 2 * D * 8; item += n_threads) {
+        const int h = item / (D * 8), d = (item / 8) % D, ch = item % 8;
+        const int first = first_stale - 64 * h - 8 * ch;  // within this chunk of 8 keys
+        if (first >= 8) continue;
+        uint8_t* chunk = reinterpret_cast<uint8_t*>(h ? v1 : v0) + d * 128 + ((ch ^ (d & 7)) * 16);
+        if (first <= 0) {
+            *reinterpret_cast<uint4*>(chunk) = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            for (int k = first; k < 8; ++k) reinterpret_cast<uint16_t*>(chunk)[k] = 0;
+        }
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, D == 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -271,6 +292,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const int chunk = (c * 4 + ch) ^ (r & 7);
                     *reinterpret_cast<uint4*>(row_base + chunk * 16) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
                 }
+            }
+            if ((blk + 1) * kFaKeys > kv_len) {  // the block holds the sequence's end: see zero_values_beyond_end
+                const int s = it & 1;
+                if (mbar_wait(&sm.kv_full[s], (it >> 1) & 1, abort_flag))  // has completed; taken for the values' visibility
+                    zero_values_beyond_end<D>(sm.v[s][0], sm.v[s][1], kv_len - blk * kFaKeys, (int)threadIdx.x - 64, kFaThreads - 64);
             }
             // P is in shared memory (visible to the tensor cores' proxy) and S has been read: the MMA thread may go on
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -709,6 +735,12 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);  // the other tile's turn
+                if ((j + 1) * kFaKeys > kv_len) {  // the block holds the sequence's end: see zero_values_beyond_end
+                    const int g = kv_base + j, s = g % PairStages<D>::value;  // (both tiles may do this: they write the same zeros)
+                    if (mbar_wait(&sm.kv_full[s], (g / PairStages<D>::value) & 1, abort_flag))
+                        zero_values_beyond_end<D>(sm.v[s][0], sm.v[s][1], kv_len - j * kFaKeys, quarter * 32 + lane, 128);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
                 // P is in tensor memory and S has been read: the MMA thread may go on
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
