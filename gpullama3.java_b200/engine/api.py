@@ -41,6 +41,27 @@ def resolve_max_length(config: ModelConfig, cache_tokens: int, asked: int | None
     return cache_tokens if limit is None else min(cache_tokens, int(limit))
 
 
+def read_stop_ids(model_dir: str | Path, config: ModelConfig) -> tuple[int, ...]:
+    """Stop token ids of a model folder: ``eos_token_id`` (an integer or a list) of generation_config.json when
+    that file has one, else the configuration's own.  The reference takes them from its chat format
+    (model/format/LlamaChatFormat.java:30 of the reference project); a model folder states them in these files."""
+    import json
+
+    path = Path(model_dir) / "generation_config.json"
+    if path.is_file():
+        try:
+            eos = json.loads(path.read_text()).get("eos_token_id")
+        except (json.JSONDecodeError, AttributeError) as e:
+            raise ValueError(f"{path} is not a JSON object: {e}") from e
+        if isinstance(eos, int) and not isinstance(eos, bool):
+            return (eos,)
+        if isinstance(eos, list) and eos and all(isinstance(t, int) and not isinstance(t, bool) for t in eos):
+            return tuple(eos)
+        if eos is not None:
+            raise ValueError(f"{path}: eos_token_id must be an integer or a list of integers, got {eos!r}")
+    return tuple(config.stop_token_ids)
+
+
 class _LoopStep:
     """The step function as the generation loop uses it: the loop samples from a step's logits before it runs
     the next step, so the logits need not be copied; decode steps may come back as drawn tokens directly, and may be launched
@@ -64,6 +85,7 @@ class Engine:
         self.cache = model.new_cache(max_tokens, max_slots=max(max_batch, 1))
         self.step_fn = StepFunction(model, self.cache)
         self.max_length = resolve_max_length(self.config, self.cache.n_pages * PAGE_TOKENS, max_length)
+        self.stop_ids: tuple[int, ...] = tuple(self.config.stop_token_ids)
         self.generator = Generator(_LoopStep(self.step_fn), self.cache, Sampler, max_batch=max_batch,
                                    max_length=self.max_length)
 
@@ -74,7 +96,9 @@ class Engine:
         arch = architecture_of(d)
         model = arch.model_factory(arch.config_class.from_dict(d), _resolve_dtype(dtype), device)
         model.load_folder(model_dir)
-        return cls(model, **kw)
+        engine = cls(model, **kw)
+        engine.stop_ids = read_stop_ids(model_dir, engine.config)
+        return engine
 
     @classmethod
     def from_random(cls, config: ModelConfig | dict, seed: int = 0, *, dtype="bfloat16", device="cuda",
@@ -94,7 +118,7 @@ class Engine:
                  return_results: bool = False):
         """Generated token ids per prompt (the stop token included when one ended the sequence)."""
         if stop_ids is None:
-            stop_ids = self.config.stop_token_ids
+            stop_ids = self.stop_ids
         results = self.generator.generate([list(p) for p in prompts], max_new_tokens,
                                           SamplingParams(temperature, top_p, seed), stop_ids, on_token)
         return results if return_results else [r.tokens for r in results]

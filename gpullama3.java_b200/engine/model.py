@@ -114,8 +114,8 @@ class CausalLM:
         self.load_tensors(tensors)
 
     def load_random(self, seed: int, *, norm_std: float = 0.0, store_dtype: torch.dtype = torch.bfloat16) -> None:
-        """Random weights generated on the device (same values as the folder the random-weights
-        mode writes on a CPU would only be guaranteed per device type; use folders to compare)."""
+        """Random weights made on the model's device: the same bits as the folder that the random-weights mode
+        writes from this seed (``write_random_model(config, seed, dir, norm_std=..., dtype=store_dtype)``)."""
         from ..weights.random_init import random_tensor
 
         specs = self.checkpoint_specs()

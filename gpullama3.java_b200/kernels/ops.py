@@ -62,6 +62,7 @@ _SIGNATURES = {
     "b200_attention_prefill_tc": ("attention_prefill_tcgen05", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                                                 c_int, c_int, c_int, c_int]),
+    "b200_random_fill": ("random_init", [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, c_float, c_float]),
     "b200_argmax_rows": ("sampling", [c_void_p, c_int, c_void_p, c_int, c_int]),
     "b200_sample_rows": ("sampling", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p]),
 }
@@ -83,10 +84,39 @@ def _fn(name: str):
         def checked(*args, _f=f, _n=n_args, _name=name):
             if len(args) != _n:  # ctypes lets extra arguments through, which shifts the stream pointer
                 raise TypeError(f"{_name} takes {_n} arguments, got {len(args)}")
-            return _f(*args)
+            if _profile is None:
+                return _f(*args)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            status = _f(*args)
+            e1.record()
+            _profile.append((_name, e0, e1))
+            return status
 
         f = _functions[name] = checked
     return f
+
+
+_profile: list | None = None   # (function, start event, end event) per launch while profiling is on
+
+
+def profile_start() -> None:
+    """From now on every launch issued through these functions is bracketed by CUDA events on its stream.  Launches
+    replayed from a CUDA graph are not seen: profile with graphs off."""
+    global _profile
+    _profile = []
+
+
+def profile_stop() -> dict[str, tuple[int, float]]:
+    """Ends profiling; ``{function: (launches, total device ms)}``."""
+    global _profile
+    rows, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out: dict[str, tuple[int, float]] = {}
+    for name, e0, e1 in rows:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + e0.elapsed_time(e1))
+    return out
 
 
 _launches = 0
@@ -479,6 +509,16 @@ def attention_prefill_tc_status() -> int:
     lib = library("attention_prefill_tcgen05")
     lib.b200_attention_prefill_tc_status.restype = c_int
     return int(lib.b200_attention_prefill_tc_status())
+
+
+# --------------------------------------------------------------------------- random weights
+def random_fill(out: torch.Tensor, key: int, scale: float, offset: float) -> None:
+    """out.flat[i] = offset + scale * (sum of sixteen 16-bit fields of the splitmix64 sequence of ``key`` at 4i..4i+3,
+    centred): the numbers ``weights.random_init.random_values`` makes on the CPU, bit for bit."""
+    _dev(out)
+    assert out.is_contiguous()
+    _check(_fn("b200_random_fill")(out.data_ptr(), dtype_code(out.dtype), out.numel(), key & ((1 << 64) - 1),
+                                   float(scale), float(offset), _stream()), "random_fill")
 
 
 # --------------------------------------------------------------------------- sampling

@@ -72,3 +72,47 @@ def test_show_command_prints_what_would_run_and_stops(tmp_path, capsys):
     assert shown["cache_tokens"] == 128 and shown["max_batch"] == 2
     rc = cli.main(["-m", "x", "-p", "1", "--cache-tokens", "4096", "--show-command"])
     assert rc == 0 and json.loads(capsys.readouterr().out)["cache_tokens"] == 4096
+
+
+def test_position_cap_profile_and_bench_switches_exist():
+    a = parse("-m", "m", "-p", "1", "--max-len", "300", "--profile", "--bench", "--norm-std", "0.1")
+    assert a.max_len == 300 and a.profile and a.bench and a.norm_std == pytest.approx(0.1)
+    b = parse("-m", "m", "-p", "1")
+    assert b.max_len is None and not b.profile and not b.bench and not b.show_config
+
+
+def test_show_config_prints_the_typed_configuration(tmp_path, capsys):
+    from conftest import TINY_B
+
+    (tmp_path / "config.json").write_text(json.dumps(TINY_B))
+    assert cli.main(["-m", str(tmp_path), "-p", "1", "--show-config"]) == 0
+    shown = json.loads(capsys.readouterr().out)
+    assert shown["config"]["num_key_value_heads"] == 1 and shown["config"]["rope_scaling"]["factor"] == 8.0
+    assert shown["q_dim"] == 96 and shown["kv_dim"] == 32 and shown["layers"] == 3
+    assert shown["parameters"] == 369312                     # the count BASELINE's Tiny B implies
+    assert shown["max_sequence_length"] == 256 and shown["stop_token_ids"] == [3, 5]
+    assert cli.main(["--config", str(tmp_path / "config.json"), "--random-weights", "1", "-p", "1", "--show-config"]) == 0
+
+
+def test_stop_ids_come_from_generation_config_when_it_has_them(tmp_path):
+    from conftest import TINY_A
+    from gpullama3.java_b200.config import config_from_dict
+    from gpullama3.java_b200.engine.api import read_stop_ids
+
+    cfg = config_from_dict(TINY_A)
+    assert read_stop_ids(tmp_path, cfg) == (7,)                                  # config.json's eos_token_id
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.6}))
+    assert read_stop_ids(tmp_path, cfg) == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [11, 12, 13]}))
+    assert read_stop_ids(tmp_path, cfg) == (11, 12, 13)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 9}))
+    assert read_stop_ids(tmp_path, cfg) == (9,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(ValueError):
+        read_stop_ids(tmp_path, cfg)
+
+
+def test_profile_table_lists_the_longest_first():
+    table = cli.format_profile({"b200_rmsnorm": (4, 0.02), "b200_gemm_generic": (10, 1.5)})
+    lines = table.splitlines()
+    assert lines[1].startswith("b200_gemm_generic") and lines[2].startswith("b200_rmsnorm") and "98.7%" in lines[1]

@@ -315,3 +315,27 @@ def test_steps_in_flight_are_forgotten_when_the_loop_fails():
     assert step.in_flight == [] and cache.live_slots() == []
     res = gen.generate([[1, 2, 3]], 4, SamplingParams())   # the next request is not served a stale step's tokens
     assert res[0].tokens == expected_tokens([1, 2, 3], 4)
+
+
+def test_generation_stops_at_the_configurations_context_length():
+    """The longest sequence is the smaller of what the cache holds and the configuration's own context length (the
+    reference caps every run at it, inference/InferenceEngine.java:75-77 of the reference project); an explicit
+    limit wins.  A prompt beyond it is refused, and a sequence that reaches it ends with the reason "context"."""
+    from conftest import TINY_A
+    from gpullama3.java_b200.config import config_from_dict
+    from gpullama3.java_b200.engine.api import resolve_max_length
+    from gpullama3.java_b200.engine.generate import FINISH_CONTEXT
+
+    cfg = config_from_dict(dict(TINY_A, max_position_embeddings=20))
+    assert resolve_max_length(cfg, 64 * 8) == 20
+    assert resolve_max_length(cfg, 16) == 16
+    assert resolve_max_length(cfg, 64 * 8, asked=300) == 300
+    with pytest.raises(ValueError):
+        resolve_max_length(cfg, 64, asked=0)
+    gen, step, cache = make(max_length=resolve_max_length(cfg, 64 * 8))
+    with pytest.raises(GenerationError, match="exceeds the longest sequence"):
+        gen.generate([[1] * 21], 4, SamplingParams())
+    res = gen.generate([[1] * 17, [2] * 3], 10, SamplingParams())
+    assert res[0].finish_reason == FINISH_CONTEXT and len(res[0].tokens) == 3     # 17 + 3 = 20 positions
+    assert res[1].finish_reason == FINISH_LENGTH and len(res[1].tokens) == 10
+    assert cache.live_slots() == []

@@ -85,8 +85,28 @@ def test_temperature_sampling_follows_the_uniform_numbers(session_tmp):
     one = alone.generator.generate([prompts[2]], 16, __import__("gpullama3.java_b200.sampling", fromlist=["SamplingParams"])
                                    .SamplingParams(0.8, 1.0, 1234), (), request_ids=[2])
     assert one[0].tokens == got[2]                                   # same draws alone as in the batch
+    # Nucleus sampling through the same loop (the draw recorded with the step): every token is the one the plain
+    # sampler takes for the same uniform number (inference/sampler/ToppSampler.java:110-156 of the reference project),
+    # or its neighbour in the sorted order when the number falls within rounding of the boundary between them.
+    V = cfg["vocab_size"]
     nucleus = engine.generate(prompts, max_new_tokens=8, temperature=0.8, top_p=0.9, seed=5, stop_ids=())
-    assert all(len(x) == 8 and all(0 <= t < cfg["vocab_size"] for t in x) for x in nucleus)
+    assert engine.step_fn.last_d2h_bytes > 0                          # the recorded path was taken
+    for i, (p, g) in enumerate(zip(prompts, nucleus)):
+        assert len(g) == 8
+        seq = list(p)
+        for n, tok in enumerate(g):
+            probs = P.temperature_softmax(P.forward(cfg, w, seq)[-1], 0.8)
+            u = uniform(5, i, n)
+            want = P.sample_top_p(probs, 0.9, u)
+            if tok != want:
+                pl = probs.tolist()
+                order = sorted(range(V), key=lambda t: (-pl[t], t))
+                csum = torch.cumsum(probs[order].double(), 0)
+                kept = int((csum <= 0.9).sum()) + 1
+                r, j = u * float(csum[kept - 1]), order.index(tok)
+                assert j < kept and min(abs(r - float(csum[j])), abs(r - (float(csum[j - 1]) if j else 0.0))) < 1e-5, \
+                    (i, n, tok, want, u)
+            seq.append(tok)
 
 
 @pytest.mark.parametrize("sampling", [dict(), dict(temperature=0.7, seed=3), dict(temperature=0.9, top_p=0.8, seed=4)],
@@ -100,7 +120,8 @@ def test_step_and_draw_recorded_together_give_the_tokens_of_step_then_draw(sessi
     from gpullama3.java_b200.engine.api import Engine
 
     cfg_json, norm_std = TINY["A"]
-    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0})
+    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0},
+                       max_position_embeddings=1024)        # generation stops at the configuration's context length
     cfg, _ = plain_inputs(d)
     prompts = random_prompts(cfg["vocab_size"], [3, 70, 9, 33], seed=6)
     engine = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 16, max_batch=4)
@@ -163,6 +184,14 @@ def test_command_line(session_tmp, tmp_path):
     p = subprocess.run([str(ROOT / "bin" / "llama-b200"), "--config", str(tmp_path / "config.json"), "--random-weights", "3",
                         "--prompt", "1 2 3", "-n", "4", "--seed", "1"], capture_output=True, text=True, env=env, timeout=600)
     assert p.returncode == 0 and len(p.stdout.split()) == 4, p.stderr[-2000:]
+    # a position cap, the kernel table and the timing line
+    p = subprocess.run(cmd[:-2] + ["--max-len", "8", "--profile", "--bench"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [list(map(int, l.split())) for l in p.stdout.strip().splitlines() if l.strip()]
+    assert lines == [P.generate_greedy(cfg, w, [3, 1, 4, 1, 5], 3), P.generate_greedy(cfg, w, [9, 2, 6], 5)]   # 8 positions each
+    assert "b200_gemm_generic" in p.stderr and "b200_attention_paged" in p.stderr and "mean us" in p.stderr
+    timing = [json.loads(l) for l in p.stderr.splitlines() if l.startswith("{")]
+    assert timing and timing[0]["prompt_tokens"] == 8 and timing[0]["generated_tokens"] == 8 and timing[0]["decode_tokens_per_s"] > 0
 
 
 def test_steps_launched_ahead_keep_their_tokens_when_the_page_tables_grow(session_tmp):
@@ -172,7 +201,8 @@ def test_steps_launched_ahead_keep_their_tokens_when_the_page_tables_grow(sessio
     from gpullama3.java_b200.engine.api import Engine
 
     cfg_json, norm_std = TINY["A"]
-    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0})
+    d = make_model_dir(session_tmp, cfg_json, seed=23, norm_std=norm_std, scale={"lm_head": 20.0},
+                       max_position_embeddings=1024)
     prompts = random_prompts(cfg_json["vocab_size"], [3, 200, 40], seed=6)
     ahead = Engine.from_folder(d, dtype="bfloat16", max_tokens=64 * 32, max_batch=4)
     got = ahead.generate(prompts, max_new_tokens=330, stop_ids=(), temperature=0.7, seed=3)

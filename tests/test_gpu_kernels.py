@@ -637,6 +637,15 @@ def test_kernels_refuse_what_they_cannot_do():
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(KernelError, match="unsupported size"):
         o.attention_paged(q, 72, out, z, z, z.reshape(1, 1), pool, pool.transpose(2, 3).contiguous(), 1, 1, 24, 0)   # head size not a step of 16
+    # decode attention reads queries, keys and values 16 bytes at a time: a pointer off that grid is refused
+    qb = torch.zeros(2, 3 * 64 + 8, dtype=torch.bfloat16, device="cuda")
+    ob = torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda")
+    kb = torch.zeros(1, 1, 64, 64, dtype=torch.bfloat16, device="cuda")
+    one = torch.ones(2, dtype=torch.int32, device="cuda")
+    tab = torch.zeros(2, 1, dtype=torch.int32, device="cuda")
+    o.attention_decode(qb, qb.shape[1], ob, one, tab, kb, kb.transpose(2, 3).contiguous(), 1, 1, 64, 0, 1)   # aligned: runs
+    with pytest.raises(KernelError, match="unsupported size"):
+        o.attention_decode(qb[:, 1:], qb.shape[1], ob, one, tab, kb, kb.transpose(2, 3).contiguous(), 1, 1, 64, 0, 1)
     with pytest.raises(KernelError):
         o.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4))   # CPU tensors
     with pytest.raises(KernelError, match="bad argument"):

