@@ -302,6 +302,8 @@ def decode_record(cfg, el, lengths, times, peaks, launches=None):
 
 
 def prefill_record(cfg, lengths, ms, peak_tflops):
+    if ms != ms:  # not timed
+        return {"tokens_per_s": None, "tokens": sum(lengths), "ms": None, "tflops": None, "frac": None}
     flops = prefill_flops(cfg, lengths)
     tf = flops / (ms / 1e3) / 1e12
     return {"tokens_per_s": round(sum(lengths) / (ms / 1e3), 1), "tokens": sum(lengths), "ms": round(ms, 3),
@@ -315,34 +317,35 @@ def unequal_lengths(n=8, lo=64, hi=2048, seed=0):
     return torch.randint(lo, hi + 1, (n,), generator=g).tolist()
 
 
-def run_3b(peaks, layers, warmup):
+def run_3b(peaks, layers, warmup, steps=256, prefill=True):
     """BASELINE.json configs[3]: unequal batch of 8 prompts of 64 to 2,048 tokens in one prompt step, 256 decode steps."""
     cfg, full = model_config("3b", layers)
     lengths = unequal_lengths()
-    engine = make_engine(cfg, "bfloat16", sum(-(-(n + 256 + warmup + 8) // 64) * 64 for n in lengths) + 64, 8)
+    engine = make_engine(cfg, "bfloat16", sum(-(-(n + steps + warmup + 8) // 64) * 64 for n in lengths) + 64, 8)
     try:
-        pre = prefill_record(cfg, lengths, time_prefill(engine, lengths), peaks["bf16_tflops"])
-        times, launches, _ = time_decode(engine, lengths, 256, warmup)
+        pre = prefill_record(cfg, lengths, time_prefill(engine, lengths) if prefill else float("nan"), peaks["bf16_tflops"])
+        times, launches, _ = time_decode(engine, lengths, steps, warmup)
         dec = decode_record(cfg, 2, [n + warmup for n in lengths], times, peaks, launches)
     finally:
         drop(engine)
-    log(f"3B unequal b8 (prompts {lengths}): prefill {pre['ms']} ms ({pre['tokens_per_s']:.0f} tok/s, frac {pre['frac']}); "
+    log(f"3B unequal b8 (prompts {lengths}): prefill {pre['ms']} ms ({pre['tokens_per_s']} tok/s, frac {pre['frac']}); "
         f"decode {dec['ms_per_step']} ms/step ({dec['tokens_per_s']:.0f} tok/s, frac {dec['frac']})")
     return {"layers": cfg["num_hidden_layers"], "layers_full": full, "prompt_lengths": lengths, "prefill": pre, "decode": dec}
 
 
-def run_8b(peaks, layers, warmup):
+def run_8b(peaks, layers, warmup, steps=512, prefill=True):
     """BASELINE.json configs[4]: 64 prompts of 512 tokens in one prompt step, 512 decode steps."""
     cfg, full = model_config("8b", layers)
     lengths = [512] * 64
-    engine = make_engine(cfg, "bfloat16", 64 * (-(-(512 + 512 + warmup + 8) // 64) * 64) + 64, 64)
+    engine = make_engine(cfg, "bfloat16", 64 * (-(-(512 + steps + warmup + 8) // 64) * 64) + 64, 64)
     try:
-        pre = prefill_record(cfg, lengths, time_prefill(engine, lengths, repeats=1), peaks["bf16_tflops_sustained"])
-        times, launches, _ = time_decode(engine, lengths, 512, warmup)
+        pre = prefill_record(cfg, lengths, time_prefill(engine, lengths, repeats=1) if prefill else float("nan"),
+                             peaks["bf16_tflops_sustained"])
+        times, launches, _ = time_decode(engine, lengths, steps, warmup)
         dec = decode_record(cfg, 2, [n + warmup for n in lengths], times, peaks, launches)
     finally:
         drop(engine)
-    log(f"8B 64 x 512: prefill {pre['ms']} ms ({pre['tokens_per_s']:.0f} tok/s, frac {pre['frac']} of the sustained peak); "
+    log(f"8B 64 x 512: prefill {pre['ms']} ms ({pre['tokens_per_s']} tok/s, frac {pre['frac']} of the sustained peak); "
         f"decode {dec['ms_per_step']} ms/step ({dec['tokens_per_s']:.0f} tok/s, frac {dec['frac']})")
     return {"layers": cfg["num_hidden_layers"], "layers_full": full, "prefill": pre, "decode": dec}
 
@@ -367,7 +370,8 @@ def run_1b_f32(peaks, layers, warmup, context, batch):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed decode steps (default: 32 for the 1B headline, 256 for --model 3b, 512 for --model 8b)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="1b", choices=sorted(SHAPES), help="whose workload is the line's headline")
@@ -379,6 +383,7 @@ def main() -> int:
                     help="all: also time the other sizes of BASELINE.json (3B unequal batch, 8B 64 x 512, 1B float32)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="--model 3b/8b: skip the timed prompt step (launch lists of decode steps)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -390,6 +395,9 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    headline_steps = args.steps
+    if args.steps is None:
+        args.steps = 32
 
     import torch  # noqa: F401
     from gpullama3.java_b200.kernels import ops  # noqa: F401
@@ -399,7 +407,7 @@ def main() -> int:
     clocks.start()
     time.sleep(0.3)
     if args.model != "1b" or args.dtype != "bfloat16":
-        return other_headline(args, peaks, peak_source, clocks)
+        return other_headline(args, peaks, peak_source, clocks, headline_steps)
 
     cfg, full_layers = model_config("1b", args.layers)
     max_batch = args.batch if args.no_points else max(args.batch, 64)
@@ -477,7 +485,7 @@ def main() -> int:
     return 0
 
 
-def other_headline(args, peaks, peak_source, clocks) -> int:
+def other_headline(args, peaks, peak_source, clocks, headline_steps=None) -> int:
     """``--model 3b``, ``--model 8b`` or ``--dtype float32``: that workload as the line's headline."""
     t0 = time.time()
     if args.dtype == "float32":
@@ -488,11 +496,13 @@ def other_headline(args, peaks, peak_source, clocks) -> int:
             f"Llama-3.2-1B shape in float32, batch {args.batch}, context {args.context}"
         batch, seq = args.batch, args.context
     elif args.model == "3b":
-        r, what, batch, seq = run_3b(peaks, args.layers, args.warmup), \
-            "Llama-3.2-3B shape, unequal batch of 8 prompts of 64..2048 tokens, 256 decode steps", 8, 2048 + 256
+        steps = headline_steps or 256
+        r, what, batch, seq = run_3b(peaks, args.layers, args.warmup, steps, not args.no_prefill), \
+            f"Llama-3.2-3B shape, unequal batch of 8 prompts of 64..2048 tokens, {steps} decode steps", 8, 2048 + steps
     else:
-        r, what, batch, seq = run_8b(peaks, args.layers, args.warmup), \
-            "Llama-3.1-8B shape, 64 prompts of 512 tokens, 512 decode steps", 64, 1024
+        steps = headline_steps or 512
+        r, what, batch, seq = run_8b(peaks, args.layers, args.warmup, steps, not args.no_prefill), \
+            f"Llama-3.1-8B shape, 64 prompts of 512 tokens, {steps} decode steps", 64, 512 + steps
     clock_summary = clocks.summary(t0, time.time())
     clocks.stop()
     s = SHAPES[args.model]

@@ -47,6 +47,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the same with rows 8..15 of the first operand absent (zero): only the two sums of row g are kept
+__device__ __forceinline__ void mma16816_lo(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float junk2, junk3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+                 : "+f"(d0), "+f"(d1), "=f"(junk2), "=f"(junk3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -69,20 +76,21 @@ struct RopeArgs {            // what the fused variant needs beyond the plain on
     int write_cache;         // 0: the layer reads a cache another layer wrote in this step (queries are still rotated)
 };
 
-// rotated element d of a head's vector x (raw, bfloat16) at position pos
-__device__ __forceinline__ float rotate_elem(const __nv_bfloat16* x, int d, int D, int pos, const float* inv_freq, int pairing) {
+// rotated element d of a head's vector x (raw, bfloat16); cs, sn: cosine and sine of the position's angle per pair
+__device__ __forceinline__ float rotate_elem(const __nv_bfloat16* x, int d, int D, const float* cs_tab, const float* sn_tab, int pairing) {
     const int half = D / 2;
     int j, d0, d1;
     bool first;
     if (pairing == 0) { j = d >> 1; d0 = d & ~1; d1 = d0 + 1; first = (d & 1) == 0; }
     else { j = d < half ? d : d - half; d0 = j; d1 = j + half; first = d < half; }
-    float sn, cs;
-    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    const float sn = sn_tab[j], cs = cs_tab[j];
     const float v0 = __bfloat162float(x[d0]), v1 = __bfloat162float(x[d1]);
     return first ? v0 * cs - v1 * sn : v0 * sn + v1 * cs;
 }
 
-template <int KB, bool FUSED>  // head_dim / 32; rotation and cache write of the step done here
+// KB: head_dim / 32.  FUSED: rotation and cache write of the step done here.  HI: the group has more than 8 heads,
+// so rows 8..15 of the tiles exist (without them a lane keeps half the sums, and more CTAs fit an SM).
+template <int KB, bool FUSED, bool HI>
 __global__ void __launch_bounds__(kAttnDecodeThreads)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ kv_lens, const int* __restrict__ page_table, int table_stride,
@@ -92,12 +100,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     constexpr int D = KB * 32;
     constexpr int NJ = D / 8;  // output tiles of 8 dims
     constexpr int SLOTS = kAttnDecodeWarps + (FUSED ? 1 : 0);  // partials merged per CTA: the warps, and the new key
-    extern __shared__ float smem[];  // [SLOTS][16][D] outputs, [SLOTS][16][2] (m, l); fused: q [16][D], k [D], v [D]
+    extern __shared__ float smem[];  // [SLOTS][16][D] outputs, [SLOTS][16][2] (m, l); fused: q [16][D], k [D], v [D], cos [D/2], sin [D/2]
     float* o_s = smem;
     float* ml_s = smem + SLOTS * 16 * D;
     float* q_s = ml_s + SLOTS * 16 * 2;
     float* k_s = q_s + 16 * D;
     float* v_s = k_s + D;
+    float* cs_s = v_s + D;       // fused: cosine and sine of the step's position for each of the D/2 pairs
+    float* sn_s = cs_s + D / 2;
 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -118,15 +128,22 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     const size_t head_off = (size_t)kvh * kPageTokens * D;
 
     const int first_page = blk_begin + warp < blk_end ? pages[(blk_begin + warp) * 32 / kPageTokens] : 0;
+    if (FUSED) {
+        // The angles of the step's position, once per CTA and before the wait (they need only the length and the
+        // frequencies): a lane that evaluated the sines and cosines of its own sixteen dimensions spent more
+        // instructions there than on its keys.
+        for (int j = threadIdx.x; j < D / 2; j += kAttnDecodeThreads) sincosf((float)(kv_len - 1) * rope.inv_freq[j], &sn_s[j], &cs_s[j]);
+        __syncthreads();
+    }
     pdl_wait();
     // query fragments: rows = the heads of this group (rows >= group are zero)
-    uint4 ql[KB], qh[KB];
+    uint4 ql[KB], qh[HI ? KB : 1];
     {
         const __nv_bfloat16* qrow = q + (size_t)seq * q_row_stride + (size_t)kvh * group * D;
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
             ql[kb] = g < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)g * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
-            qh[kb] = g + 8 < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+            if (HI) qh[kb] = g + 8 < group ? *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * D + kb * 32 + t * 8) : make_uint4(0, 0, 0, 0);
         }
         if (FUSED) {
             // rotate in registers.  A lane holds dims 32 kb + 8 t .. + 7 of its rows: interleaved partners sit
@@ -140,10 +157,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                 for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        float sn, cs;
-                        sincosf((float)pos * rope.inv_freq[(kb * 32 + t * 8) / 2 + e], &sn, &cs);
+                        const float sn = sn_s[(kb * 32 + t * 8) / 2 + e], cs = cs_s[(kb * 32 + t * 8) / 2 + e];
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < (HI ? 2 : 1); ++h) {
                             uint32_t* w = (h ? hi32 : lo32) + kb * 4 + e;
                             float v0, v1;
                             unpack(*w, v0, v1);
@@ -155,11 +171,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                 for (int kb = 0; kb < KB / 2; ++kb)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        float sn[2], cs[2];
-                        sincosf((float)pos * rope.inv_freq[kb * 32 + t * 8 + 2 * e], &sn[0], &cs[0]);
-                        sincosf((float)pos * rope.inv_freq[kb * 32 + t * 8 + 2 * e + 1], &sn[1], &cs[1]);
+                        const float sn[2] = {sn_s[kb * 32 + t * 8 + 2 * e], sn_s[kb * 32 + t * 8 + 2 * e + 1]};
+                        const float cs[2] = {cs_s[kb * 32 + t * 8 + 2 * e], cs_s[kb * 32 + t * 8 + 2 * e + 1]};
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < (HI ? 2 : 1); ++h) {
                             uint32_t* wa = (h ? hi32 : lo32) + kb * 4 + e;               // dims d, d + 1
                             uint32_t* wb = (h ? hi32 : lo32) + (kb + KB / 2) * 4 + e;    // dims d + D/2, d + D/2 + 1
                             float a0, a1, b0, b1;
@@ -207,8 +222,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             for (int c = 0; c < 4; ++c) s[i][c] = 0.f;
 #pragma unroll
             for (int kb = 0; kb < KB; ++kb) {
-                mma16816(s[i], ql[kb].x, qh[kb].x, ql[kb].y, qh[kb].y, kf[i][kb].x, kf[i][kb].y);
-                mma16816(s[i], ql[kb].z, qh[kb].z, ql[kb].w, qh[kb].w, kf[i][kb].z, kf[i][kb].w);
+                if (HI) {
+                    mma16816(s[i], ql[kb].x, qh[kb].x, ql[kb].y, qh[kb].y, kf[i][kb].x, kf[i][kb].y);
+                    mma16816(s[i], ql[kb].z, qh[kb].z, ql[kb].w, qh[kb].w, kf[i][kb].z, kf[i][kb].w);
+                } else {
+                    mma16816_lo(s[i][0], s[i][1], ql[kb].x, ql[kb].y, kf[i][kb].x, kf[i][kb].y);
+                    mma16816_lo(s[i][0], s[i][1], ql[kb].z, ql[kb].w, kf[i][kb].z, kf[i][kb].w);
+                }
             }
         }
         // lane t's columns of tile i are keys base + 8t + 2i and + 2i + 1
@@ -220,60 +240,81 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                 const int key = base + 8 * t + 2 * i + e;
                 const bool ok = key >= lo && key < n_cached;
                 s[i][e] = ok ? s[i][e] / sqrt_d : -INFINITY;
-                s[i][2 + e] = ok ? s[i][2 + e] / sqrt_d : -INFINITY;
                 bm_lo = fmaxf(bm_lo, s[i][e]);
-                bm_hi = fmaxf(bm_hi, s[i][2 + e]);
+                if (HI) {
+                    s[i][2 + e] = ok ? s[i][2 + e] / sqrt_d : -INFINITY;
+                    bm_hi = fmaxf(bm_hi, s[i][2 + e]);
+                }
             }
         bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));
         bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 2));
-        bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
-        bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
-        const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
+        if (HI) {
+            bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
+            bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
+        }
+        const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = HI ? fmaxf(m_hi, bm_hi) : 0.f;
         // a block always holds at least one valid key (blocks run from lo/32 to (n_cached-1)/32), so mn is finite
-        const float c_lo = expf(m_lo - mn_lo), c_hi = expf(m_hi - mn_hi);
+        const float c_lo = expf(m_lo - mn_lo), c_hi = HI ? expf(m_hi - mn_hi) : 0.f;
         m_lo = mn_lo;
         m_hi = mn_hi;
         l_lo *= c_lo;
         l_hi *= c_hi;
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) { o[j][0] *= c_lo; o[j][1] *= c_lo; o[j][2] *= c_hi; o[j][3] *= c_hi; }
+        for (int j = 0; j < NJ; ++j) {
+            o[j][0] *= c_lo;
+            o[j][1] *= c_lo;
+            if (HI) { o[j][2] *= c_hi; o[j][3] *= c_hi; }
+        }
         uint32_t pa[4][2];  // per tile: packed probabilities of rows g and g + 8
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float p0 = expf(s[i][0] - mn_lo), p1 = expf(s[i][1] - mn_lo);
-            const float p2 = expf(s[i][2] - mn_hi), p3 = expf(s[i][3] - mn_hi);
             l_lo += p0 + p1;
-            l_hi += p2 + p3;
             pa[i][0] = pack_bf16(p0, p1);
-            pa[i][1] = pack_bf16(p2, p3);
+            if (HI) {
+                const float p2 = expf(s[i][2] - mn_hi), p3 = expf(s[i][3] - mn_hi);
+                l_hi += p2 + p3;
+                pa[i][1] = pack_bf16(p2, p3);
+            }
         }
         const int n_valid = n_cached - (base + 8 * t);  // keys of this lane's V slice that exist
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const uint4 v = n_valid >= 8 ? vf[j] : keep_first(vf[j], max(n_valid, 0));
-            mma16816(o[j], pa[0][0], pa[0][1], pa[1][0], pa[1][1], v.x, v.y);
-            mma16816(o[j], pa[2][0], pa[2][1], pa[3][0], pa[3][1], v.z, v.w);
+            if (HI) {
+                mma16816(o[j], pa[0][0], pa[0][1], pa[1][0], pa[1][1], v.x, v.y);
+                mma16816(o[j], pa[2][0], pa[2][1], pa[3][0], pa[3][1], v.z, v.w);
+            } else {
+                mma16816_lo(o[j][0], o[j][1], pa[0][0], pa[1][0], v.x, v.y);
+                mma16816_lo(o[j][0], o[j][1], pa[2][0], pa[3][0], v.z, v.w);
+            }
         }
     }
 
     // the lanes of a row share l; then the warps of the CTA are merged through shared memory
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (HI) {
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    }
     float* ow = o_s + (size_t)warp * 16 * D;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         ow[g * D + 8 * j + 2 * t] = o[j][0];
         ow[g * D + 8 * j + 2 * t + 1] = o[j][1];
-        ow[(g + 8) * D + 8 * j + 2 * t] = o[j][2];
-        ow[(g + 8) * D + 8 * j + 2 * t + 1] = o[j][3];
+        if (HI) {   // (without these rows the merge below never reads them: it stops at the group's last head)
+            ow[(g + 8) * D + 8 * j + 2 * t] = o[j][2];
+            ow[(g + 8) * D + 8 * j + 2 * t + 1] = o[j][3];
+        }
     }
     if (t == 0) {
         ml_s[(warp * 16 + g) * 2] = m_lo;
         ml_s[(warp * 16 + g) * 2 + 1] = l_lo;
-        ml_s[(warp * 16 + g + 8) * 2] = m_hi;
-        ml_s[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+        if (HI) {
+            ml_s[(warp * 16 + g + 8) * 2] = m_hi;
+            ml_s[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+        }
     }
     if (FUSED) {
         // The step's own key and value.  The CTA of the last span stores them at the sequence's last position
@@ -286,7 +327,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             const __nv_bfloat16* v_raw = k_raw + (size_t)n_kv_heads * D;
             const size_t page_base = (size_t)pages[pos / kPageTokens] * page_stride + head_off;
             for (int d = threadIdx.x; d < D; d += kAttnDecodeThreads) {
-                const __nv_bfloat16 kr = __float2bfloat16_rn(rotate_elem(k_raw, d, D, pos, rope.inv_freq, rope.pairing));
+                const __nv_bfloat16 kr = __float2bfloat16_rn(rotate_elem(k_raw, d, D, cs_s, sn_s, rope.pairing));
                 k_pool[page_base + (size_t)(pos % kPageTokens) * D + d] = kr;
                 v_pool[page_base + (size_t)d * kPageTokens + (pos % kPageTokens)] = v_raw[d];
                 k_s[d] = __bfloat162float(kr);
@@ -302,8 +343,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                         const int d = kb * 32 + t * 8 + 2 * e;
                         q_s[g * D + d] = __uint_as_float(lo32[kb * 4 + e] << 16);
                         q_s[g * D + d + 1] = __uint_as_float(lo32[kb * 4 + e] & 0xffff0000u);
-                        q_s[(g + 8) * D + d] = __uint_as_float(hi32[kb * 4 + e] << 16);
-                        q_s[(g + 8) * D + d + 1] = __uint_as_float(hi32[kb * 4 + e] & 0xffff0000u);
+                        if (HI) {
+                            q_s[(g + 8) * D + d] = __uint_as_float(hi32[kb * 4 + e] << 16);
+                            q_s[(g + 8) * D + d + 1] = __uint_as_float(hi32[kb * 4 + e] & 0xffff0000u);
+                        }
                     }
             }
         }
@@ -416,15 +459,16 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     float* part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * head_dim;
     dim3 grid(n_splits, n_kv_heads, n_seqs);
     const int slots = kAttnDecodeWarps + (fused ? 1 : 0);
-    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 18 * head_dim : 0));
+    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 19 * head_dim : 0));
     auto qq = (const __nv_bfloat16*)q;
     auto kk = (__nv_bfloat16*)k_pool;
     auto vv = (__nv_bfloat16*)v_pool;
     auto oo = (__nv_bfloat16*)out;
     int st = 0;
-#define B200_LAUNCH(KB, F)                                                                                          \
+#define B200_LAUNCH(KB, F) do { if (group > 8) B200_LAUNCH_H(KB, F, true); else B200_LAUNCH_H(KB, F, false); } while (0)
+#define B200_LAUNCH_H(KB, F, HI)                                                                                    \
     do {                                                                                                            \
-        auto kernel = attention_decode_kernel<KB, F>;                                                               \
+        auto kernel = attention_decode_kernel<KB, F, HI>;                                                             \
         if (smem > 48 * 1024) {                                                                                     \
             static bool configured = false;                                                                         \
             if (!configured) {                                                                                      \
@@ -446,6 +490,7 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     }
 #undef B200_PICK
 #undef B200_LAUNCH
+#undef B200_LAUNCH_H
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
                       (const float*)part_o, (const float*)part_ml, oo, n_splits, head_dim);
