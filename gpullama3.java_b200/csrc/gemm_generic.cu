@@ -2,7 +2,8 @@
 //
 // A is [M, K] (activations, row-major, row stride lda), W is [N, K] (a weight as the reference
 // stores it: one row per output, core/model/tensor/FloatTensor.java:98-100 of the reference
-// project).  This is the kernel of the true 32-bit path (no tensor cores, no reduced-precision
+// project).  Two kernels: tiles of 64 x 64 for prompts, and a weight-streaming one for a decode step's few rows
+// (further down).  This is the kernel of the true 32-bit path (no tensor cores, no reduced-precision
 // matrix mode) and the fallback of the bfloat16 path for sizes or storage types the tensor-core
 // kernels refuse.  Epilogues:
 //   0  store         C[M, N] = acc                       (C of type TC)
@@ -76,6 +77,82 @@ gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product for a decode step's few rows (M <= 16): tiles of 64 tokens would leave the FMA units idle and
+// read every weight through shared memory for nothing.  Here a warp owns two consecutive weight rows (a gate/up
+// pair of the gated epilogue) and streams them 16 bytes per lane, every element meeting all M tokens' activations
+// (which stay in L1); the lanes' sums are added in a fixed tree.  Still plain 32-bit FMA.
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16),
+                       __uint_as_float(v.y & 0xffff0000u));
+}
+
+constexpr int kFewWarps = 8, kFewThreads = kFewWarps * 32;
+
+template <typename TA, typename TW, typename TC, int MT>
+__global__ void __launch_bounds__(kFewThreads)
+gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
+                    int M, int N, int K, int epilogue) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * kFewWarps + warp) * 2;
+    if (n0 >= N) return;
+    const TW* w0 = W + (size_t)n0 * ldw;
+    const TW* w1 = W + (size_t)min(n0 + 1, N - 1) * ldw;
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) { acc0[m] = 0.f; acc1[m] = 0.f; }
+#pragma unroll 2
+    for (int k = lane * 4; k < K; k += 128) {
+        const float4 a0 = load4<TW>(w0 + k), a1 = load4<TW>(w1 + k);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < M) {
+                const float4 x = load4<TA>(A + (size_t)m * lda + k);
+                acc0[m] = fmaf(a0.w, x.w, fmaf(a0.z, x.z, fmaf(a0.y, x.y, fmaf(a0.x, x.x, acc0[m]))));
+                acc1[m] = fmaf(a1.w, x.w, fmaf(a1.z, x.z, fmaf(a1.y, x.y, fmaf(a1.x, x.x, acc1[m]))));
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], off);
+            acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], off);
+        }
+    // lane m stores token m's two sums
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        if (lane != m || m >= M) continue;
+        if (epilogue == 2) {
+            if (n0 + 1 < N) C[(size_t)m * ldc + n0 / 2] = from_f32<TC>((acc0[m] / (1.0f + expf(-acc0[m]))) * acc1[m]);
+        } else {
+            TC* c = C + (size_t)m * ldc + n0;
+            if (epilogue == 1) {
+                c[0] = from_f32<TC>(to_f32<TC>(c[0]) + acc0[m]);
+                if (n0 + 1 < N) c[1] = from_f32<TC>(to_f32<TC>(c[1]) + acc1[m]);
+            } else {
+                c[0] = from_f32<TC>(acc0[m]);
+                if (n0 + 1 < N) c[1] = from_f32<TC>(acc1[m]);
+            }
+        }
+    }
+}
+
+template <typename TA, typename TW, typename TC>
+static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epilogue,
+                          cudaStream_t stream) {
+    const dim3 grid((N + 2 * kFewWarps - 1) / (2 * kFewWarps));
+    if (M <= 8)
+        gemm_fewrows_kernel<TA, TW, TC, 8><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue);
+    else
+        gemm_fewrows_kernel<TA, TW, TC, 16><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue);
+    return launch_status();
+}
+
 }  // namespace b200
 
 extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void* W, int w_dtype, int ldw, void* C,
@@ -84,6 +161,12 @@ extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void
     if (K <= 0 || epilogue < 0 || epilogue > 2) return b200::kErrBadArgument;
     if (epilogue == 1 && c_dtype != b200::kF32) return b200::kErrBadArgument;
     if (epilogue == 2 && (N & 1)) return b200::kErrBadArgument;
+    // a decode step's few rows: rows of 4 elements at a time, when the rows start on such a boundary
+    const size_t a_el = a_dtype == b200::kF32 ? 4 : 2, w_el = w_dtype == b200::kF32 ? 4 : 2;
+    if (M <= 16 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)A % (4 * a_el)) == 0 && ((uintptr_t)W % (4 * w_el)) == 0) {
+        B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
+            return b200::launch_fewrows<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream))));
+    }
     dim3 grid((N + b200::kTileN - 1) / b200::kTileN, (M + b200::kTileM - 1) / b200::kTileM);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;
     B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,

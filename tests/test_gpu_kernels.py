@@ -205,8 +205,11 @@ def test_rope_and_cache_write_for_prompts(dtype, pairing, H, KVH, D):
 
 @pytest.mark.parametrize("a_dtype, w_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                               (torch.bfloat16, torch.float32)])
-@pytest.mark.parametrize("M, N, K", [(1, 40, 24), (7, 130, 100), (65, 64, 17), (200, 258, 1030)])
+@pytest.mark.parametrize("M, N, K", [(1, 40, 24), (7, 130, 100), (65, 64, 17), (200, 258, 1030),
+                                     (16, 1002, 2048), (9, 36, 8192), (3, 50, 1022), (17, 30, 64)])
 def test_gemm_generic_and_its_epilogues(a_dtype, w_dtype, M, N, K):
+    """The plain product in its two forms: at most 16 rows with rows that start on 4-element boundaries stream the
+    weights (a last CTA with one pair of rows, K of one pass per lane and of sixty-four); everything else is tiled."""
     o = ops()
     g = torch.Generator().manual_seed(M + N)
     a = torch.randn(M, K, generator=g).to(a_dtype).cuda()
