@@ -135,13 +135,15 @@ class CausalLM:
         logits [len(logit_rows), vocab] (None when no row is wanted)."""
         if not self.loaded:
             raise WeightError("the model has no weights yet (load_folder / load_random / load_tensors)")
-        residual = self.embedding.forward(ctx.tokens)  # float32 [T, hidden]
+        ws = ctx.workspace
+        residual = self.embedding.forward(ctx.tokens, ctx.empty)  # float32 [T, hidden]; lives for the whole pass
         # a block may leave the first norm of the block that runs next to that block's first product
         # (parts/base.py, ScaledRows); blocks that do not offer this are called the plain way
         handed = None
         for k, entry in enumerate(self.schedule):
             view = cache.view(entry.cache) if entry.cache is not None else None
             block = self.blocks[entry.layer]
+            mark = ws.mark() if ws is not None else 0
             if block.takes_scaled_rows(ctx):
                 nxt = self.blocks[self.schedule[k + 1].layer] if k + 1 < len(self.schedule) else None
                 then = nxt.first_norm() if nxt is not None and nxt.takes_scaled_rows(ctx) else None
@@ -149,9 +151,11 @@ class CausalLM:
             else:
                 block.forward(residual, ctx, view, entry.writes_cache)
                 handed = None
+            if ws is not None:
+                ws.release(mark)   # the block's intermediate tensors; what it hands on does not come from there
         if logit_rows is None or logit_rows.numel() == 0:
             return None
-        x = self.final_norm.forward(residual, ctx.dtype, rows=logit_rows)
+        x = self.final_norm.forward(residual, ctx.dtype, rows=logit_rows, alloc=ctx.empty)
         return self.head.forward(x)
 
 

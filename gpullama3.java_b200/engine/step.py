@@ -16,6 +16,7 @@ import torch
 from ..cache.pages import PAGE_TOKENS
 from ..cache.sequence_cache import SequenceCache
 from ..parts.base import StepContext
+from .workspace import Workspace
 
 
 class StepError(ValueError):
@@ -69,8 +70,9 @@ def _context_over(dev: torch.Tensor, sizes, table_shapes, dtype, device, slots, 
 
 
 def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_pos: list[int],
-                  token_lists: list, logit_rows: list[int]) -> tuple[StepContext, torch.Tensor | None]:
-    """Pack one pass into a StepContext.  All integers go to the device in one copy."""
+                  token_lists: list, logit_rows: list[int], workspace=None) -> tuple[StepContext, torch.Tensor | None]:
+    """Pack one pass into a StepContext.  All integers go to the device in one copy.  ``workspace``: where the
+    pass takes its intermediate tensors from (it is reset here)."""
     pieces, q_lens, table_shapes = _pack(cache, slots, start_pos, token_lists, logit_rows)
     host = torch.from_numpy(np.concatenate(pieces))
     if device.type == "cuda":
@@ -78,6 +80,9 @@ def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_p
     dev = host.to(device, non_blocking=True)
     ctx, rows = _context_over(dev, [p.size for p in pieces], table_shapes, dtype, device, slots, start_pos, q_lens)
     ctx.extras["host_buffer"] = host  # keep the pinned source alive until the copy has run
+    if workspace is not None:
+        workspace.reset()
+        ctx.workspace = workspace
     return ctx, (rows if logit_rows else None)
 
 
@@ -241,6 +246,9 @@ class StepFunction:
         self._drawn: dict[int, torch.Tensor] = {}   # per number of sequences: where every recorded draw leaves its tokens
         self._in_flight: list[DecodeGraph] = []     # steps launched by decode_ahead, oldest first, not yet collected
         self._fed_turn = 0
+        # intermediate tensors of passes that are issued launch by launch (prompts, mixed steps); recorded decode
+        # steps keep theirs in the graph's own memory
+        self.workspace = Workspace(model.device) if model.device.type == "cuda" else None
 
     def _graph_for(self, slots: list[int], start: list[int], sampler=None, variant: int = 0) -> DecodeGraph:
         """The recorded step that fits these sequences: table widths are powers of two of at least 4 pages.
@@ -400,7 +408,7 @@ class StepFunction:
                         rows.append(base + (w - done))
                         dest.append(out_offsets[i] + j)
                 base += len(t)
-            ctx, rows_dev = build_context(model.dtype, model.device, cache, slots, start, toks, rows)
+            ctx, rows_dev = build_context(model.dtype, model.device, cache, slots, start, toks, rows, self.workspace)
             self.last_h2d_bytes = ctx.extras["host_buffer"].numel() * 4
             logits = model.forward(ctx, cache, rows_dev)
             for (_, s), t in zip(part, toks):

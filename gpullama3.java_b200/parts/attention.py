@@ -70,9 +70,9 @@ class GroupedQueryAttention(Mixer):
         return ctx.all_decode and self.qkv.links_with(ctx.n_tokens, ctx.dtype)
 
     def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True, then_norm=None):
-        qkv = self.qkv.store(x, ctx.dtype)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
+        qkv = self.qkv.store(x, ctx.dtype, ctx.empty)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
         table = ctx.page_tables[cache.group]
-        out = torch.empty((x.shape[0], self.q_dim), dtype=ctx.dtype, device=x.device)
+        out = ctx.empty((x.shape[0], self.q_dim), ctx.dtype)
         if not fast.try_decode_attention_with_rope(qkv, out, ctx, table, cache, self, writes_cache):
             ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
                                  cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,

@@ -48,6 +48,15 @@ class StepContext:
     # the sequences, so a part that shapes its launch by length (spans of keys) shapes it for this number.
     kv_capacity: list[int] = field(default_factory=list)
     extras: dict = field(default_factory=dict)  # scratch a part may keep for the duration of a step
+    workspace: object = None         # where intermediate tensors of this pass come from (None: the allocator)
+
+    def empty(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """An uninitialised device tensor that lives until the block that asked for it has run (the model gives
+        a block's pieces back after it); what must live longer (logits, anything handed to the next block) is
+        taken from ``torch.empty``."""
+        if self.workspace is not None:
+            return self.workspace.take(shape, dtype)
+        return torch.empty(tuple(shape), dtype=dtype, device=self.device)
 
     def capacity(self, group: int) -> int:
         return self.kv_capacity[group] if group < len(self.kv_capacity) else self.max_kv_len
@@ -97,8 +106,9 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
-        """x: float32 residual stream [T, dim] -> normalised rows in ``out_dtype``; ``rows`` picks rows."""
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: torch.Tensor | None = None, alloc=None) -> torch.Tensor:
+        """x: float32 residual stream [T, dim] -> normalised rows in ``out_dtype``; ``rows`` picks rows.
+        ``alloc(shape, dtype)``: where the result comes from (a step's ``ctx.empty``; default: the allocator)."""
         raise NotImplementedError
 
     def row_factor_form(self):

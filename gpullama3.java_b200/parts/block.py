@@ -26,7 +26,7 @@ class PreNormBlock(Block):
         residual stream before a norm (the mixer's, or the previous block's, last product) leaves the norm's
         rows one factor short, and the product after it applies the factor (ScaledRows).  Parts that do not
         offer this are called the plain way."""
-        x = x_in if x_in is not None else self.mixer_norm.forward(residual, ctx.dtype)
+        x = x_in if x_in is not None else self.mixer_norm.forward(residual, ctx.dtype, alloc=ctx.empty)
         h = None
         if self.mixer.takes_scaled_rows(ctx):
             ffn_links = self.feed_forward.takes_scaled_rows(ctx)
@@ -35,7 +35,7 @@ class PreNormBlock(Block):
         else:
             self.mixer.forward(x, ctx, cache, residual, writes_cache)
         if h is None:
-            h = self.feed_forward_norm.forward(residual, ctx.dtype)
+            h = self.feed_forward_norm.forward(residual, ctx.dtype, alloc=ctx.empty)
         if self.feed_forward.takes_scaled_rows(ctx):
             return self.feed_forward.forward(h, ctx, residual, then_norm=then_norm)
         self.feed_forward.forward(h, ctx, residual)

@@ -28,8 +28,9 @@ class TokenEmbedding(Part):
         t = tensors["table"].to(device)
         self.table = t.to(torch.float32 if dtype == torch.float32 else t.dtype).contiguous()
 
-    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
-        out = torch.empty((tokens.numel(), self.hidden_size), dtype=torch.float32, device=tokens.device)
+    def forward(self, tokens: torch.Tensor, alloc=None) -> torch.Tensor:
+        shape = (tokens.numel(), self.hidden_size)
+        out = alloc(shape, torch.float32) if alloc is not None else torch.empty(shape, dtype=torch.float32, device=tokens.device)
         ops.embed_gather(self.table, tokens, out)
         return out
 

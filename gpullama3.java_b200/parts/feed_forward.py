@@ -36,7 +36,7 @@ class SwiGLUFeedForward(FeedForward):
         return ctx.all_decode and self.gate_up.links_with(ctx.n_tokens, ctx.dtype)
 
     def forward(self, x, ctx: StepContext, residual, then_norm=None):
-        h = self.gate_up.gated_silu(x, ctx.dtype)  # [T, intermediate]
+        h = self.gate_up.gated_silu(x, ctx.dtype, ctx.empty)  # [T, intermediate]
         return self.down.add_to(h, residual, then_norm)
 
 

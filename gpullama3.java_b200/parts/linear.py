@@ -29,9 +29,10 @@ class Linear:
         """Whether this product can be one half of a split norm for ``n_rows`` rows of ``dtype``."""
         return dtype == torch.bfloat16 and ops.gemm_decode_links(n_rows, self.weight)
 
-    def store(self, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-        """a @ W.T as a new [T, out] tensor."""
-        c = torch.empty((a.shape[0], self.out_features), dtype=out_dtype, device=a.device)
+    def store(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None) -> torch.Tensor:
+        """a @ W.T as a new [T, out] tensor (from ``alloc(shape, dtype)`` when given, a step's ``ctx.empty``)."""
+        shape = (a.shape[0], self.out_features)
+        c = alloc(shape, out_dtype) if alloc is not None else torch.empty(shape, dtype=out_dtype, device=a.device)
         self._run(a, c, ops.EPILOGUE_STORE)
         return c
 
@@ -50,8 +51,9 @@ class Linear:
         self._run(a, residual, ops.EPILOGUE_RESIDUAL_ADD)
         return None
 
-    def gated_silu(self, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    def gated_silu(self, a: torch.Tensor, out_dtype: torch.dtype, alloc=None) -> torch.Tensor:
         """W holds gate and up rows interleaved; returns silu(gate) * up as [T, out/2]."""
-        c = torch.empty((a.shape[0], self.out_features // 2), dtype=out_dtype, device=a.device)
+        shape = (a.shape[0], self.out_features // 2)
+        c = alloc(shape, out_dtype) if alloc is not None else torch.empty(shape, dtype=out_dtype, device=a.device)
         self._run(a, c, ops.EPILOGUE_GATED_SILU)
         return c

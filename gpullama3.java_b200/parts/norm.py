@@ -28,9 +28,9 @@ class RMSNorm(Norm):
     def row_factor_form(self):
         return self.weight, self.eps, self.dim
 
-    def forward(self, x, out_dtype, rows=None):
+    def forward(self, x, out_dtype, rows=None, alloc=None):
         n = x.shape[0] if rows is None else rows.numel()
-        out = torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
+        out = alloc((n, self.dim), out_dtype) if alloc is not None else torch.empty((n, self.dim), dtype=out_dtype, device=x.device)
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
 

@@ -112,8 +112,13 @@ def test_feed_forward_part_alone(dtype):
 
 
 class _Dummy:
+    """What the feed-forward asks of a step's context: the run's precision and where tensors come from."""
+
     def __init__(self, dtype):
         self.dtype = dtype
+
+    def empty(self, shape, dtype):
+        return torch.empty(tuple(shape), dtype=dtype, device=DEV)
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
