@@ -16,6 +16,11 @@
 //   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns at a time, then one of
 //                      0 store (bfloat16 or float32), 1 residual add into float32 C,
 //                      2 silu(gate) * up on interleaved gate/up columns (bfloat16 out, N/2 wide).
+//                      The residual add leaves the SM as a bulk tensor reduction: a warp puts its 32 x 32
+//                      sums into shared memory and one cp.reduce.async.bulk.tensor (.add, float32) lets the
+//                      L2 add them to C; the SM never reads the residual stream, and nothing is strided (a
+//                      thread per row would touch 32 rows with every access).  Each element is added once.
+//                      (Stores of bfloat16 results through such boxes were measured and gained nothing.)
 // Edges: TMA zero-fills rows and K beyond the tensors, stores are bounds-checked, so any M, N and
 // any K that keeps rows 16-byte aligned (K % 8 == 0) are accepted.
 // Every mbarrier wait is bounded: when a wait gives up, the kernel records a code in a status
@@ -41,6 +46,17 @@ struct GemmSmem {
     int abort_flag;
 };
 
+// What the residual epilogue adds beside the ring: one 32 x 32 float32 box per epilogue warp (128-byte swizzle).
+struct ResidualStage {
+    alignas(1024) float box[4][32 * 32];
+};
+
+// C[box at (col, row)] += the 32 x 32 float32 box in shared memory, done by the L2 (rows and columns beyond C are clipped)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int col, int row, const void* src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(col), "r"(row), "r"(smem_u32(src)) : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -51,9 +67,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kGemmTcThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    TC* __restrict__ C, int ldc, int M, int N, int K) {
+                    const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K) {
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // (the residual epilogue's boxes follow the ring; the launch asks for them only when reduce_c is set)
+    ResidualStage& cs = *reinterpret_cast<ResidualStage*>(reinterpret_cast<uint8_t*>(&sm) + ((sizeof(GemmSmem<BN, STAGES>) + 1023) & ~(size_t)1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM, n_tiles = tiles_n * tiles_m;
     const int k_iters = (K + BK - 1) / BK;
@@ -65,6 +83,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        if (EPI == 1 && reduce_c) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {  // tensor memory for two accumulators of BN columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(2 * BN) : "memory");
@@ -141,6 +160,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (n0 + c0 >= N) break;  // uniform: whole chunk beyond the matrix
                 float v[32];
                 tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
+                if (EPI == 1 && reduce_c) {
+                    // the box is free once the reduction before has read it; row `lane` of the box, its eight
+                    // 16-byte pieces at piece ^ (row % 8): the layout the tensor map's 128-byte swizzle expects
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+                    float* box_row = cs.box[quarter] + lane * 32;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(box_row + ((j ^ (lane & 7)) << 2)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {   // (columns of the box beyond C are clipped by the reduction, and so are rows beyond M)
+                        tma_reduce_add_2d(&map_c, n0 + c0, m0 + quarter * 32, cs.box[quarter]);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    continue;
+                }
                 if (row >= M) continue;
                 const int col = n0 + c0;
                 if (EPI == 2) {
@@ -199,6 +235,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
         }
+        // the reductions this thread issued are complete (their sums are in C) before the kernel ends
+        if (EPI == 1 && reduce_c && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
@@ -407,11 +445,27 @@ static int tile_width_for(int M, int N) {
     return best;
 }
 
+// float32 C [rows, cols] with row stride ld (elements) as boxes of 32 x 32, 128-byte swizzle: what the residual
+// epilogue's bulk reductions address.  False when C does not lie on the 16-byte grid a tensor map needs.
+static bool make_map_c(CUtensorMap* map, const void* base, int rows, int cols, int ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || ((uintptr_t)base & 15) != 0 || ld % 4 != 0) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int STAGES, int EPI, typename TC>
 static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
-    CUtensorMap ma, mw;
+    CUtensorMap ma, mw, mc = {};
     if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;
-    const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+    // the residual sum as bulk reductions where C allows a tensor map (else thread by thread, as the other epilogues)
+    const int reduce_c = (EPI == 1 && make_map_c(&mc, C, M, N, ldc)) ? 1 : 0;
+    const size_t smem = ((sizeof(GemmSmem<BN, STAGES>) + 1023) & ~(size_t)1023) + (EPI == 1 ? sizeof(ResidualStage) : 0) + 1024;
     static bool configured = false;
     auto kernel = gemm_tcgen05_kernel<BN, STAGES, EPI, TC>;
     if (!configured) {
@@ -422,7 +476,7 @@ static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, in
     const int n_sms = sm_count();
     const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(n_tiles < n_sms ? n_tiles : n_sms));
-    return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, (TC*)C, ldc, M, N, K);
+    return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K);
 }
 
 template <int BN, int STAGES>
