@@ -89,12 +89,65 @@ rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __rest
     }
 }
 
+// One warp per row for the usual widths (dim = 128 * KEEP): the whole row sits in the warp's registers after one
+// round of 16-byte loads that are all in flight together, the sum of squares is a shuffle tree, and no barrier is
+// needed; a CTA of eight warps takes eight rows.
+constexpr int kNormWarps = 8;
+
+template <typename TW, typename TO, int KEEP>
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_warp_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                    const int* __restrict__ rows, int n_rows, float eps) {
+    constexpr int dim = KEEP * 128;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
+    if (r >= n_rows) return;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+    float keep[KEEP][4];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) load4<float>(xr + (k * 32 + lane) * 4, keep[k]);
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += keep[k][e] * keep[k][e];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float scale = 1.0f / sqrtf(ss / (float)dim + eps);
+    TO* o = out + (size_t)r * dim;
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+        float wv[4], y[4];
+        load4<TW>(w + (k * 32 + lane) * 4, wv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = wv[e] * (scale * keep[k][e]);
+        store4<TO>(o + (k * 32 + lane) * 4, y);
+    }
+}
+
+template <typename TW, typename TO, int KEEP>
+static int launch_norm_warp(const float* x, const void* w, void* out, const int* rows, int n_rows, float eps, cudaStream_t stream) {
+    return launch_pdl(rmsnorm_warp_kernel<TW, TO, KEEP>, dim3((n_rows + kNormWarps - 1) / kNormWarps), dim3(kNormWarps * 32), 0,
+                      stream, x, (const TW*)w, (TO*)out, rows, n_rows, eps);
+}
+
 }  // namespace b200
 
 extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
                             const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const bool vec = dim % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0;
+    if (vec && n_rows >= 64 && dim % 1024 == 0 && dim <= 4096) {   // many rows of a usual width: a warp per row
+        B200_DISPATCH_DTYPE(w_dtype, TW, B200_DISPATCH_DTYPE2(out_dtype, TO,
+            switch (dim / 1024) {
+                case 1: return b200::launch_norm_warp<TW, TO, 8>(x, w, out, rows, n_rows, eps, stream);
+                case 2: return b200::launch_norm_warp<TW, TO, 16>(x, w, out, rows, n_rows, eps, stream);
+                case 3: return b200::launch_norm_warp<TW, TO, 24>(x, w, out, rows, n_rows, eps, stream);
+                default: return b200::launch_norm_warp<TW, TO, 32>(x, w, out, rows, n_rows, eps, stream);
+            }));
+    }
     B200_DISPATCH_DTYPE(w_dtype, TW, B200_DISPATCH_DTYPE2(out_dtype, TO,
         return vec ? b200::launch_pdl(b200::rmsnorm_kernel<TW, TO, true>, dim3(n_rows), dim3(b200::kNormThreads), 0, stream, x,
                                       (const TW*)w, (TO*)out, rows, dim, eps)

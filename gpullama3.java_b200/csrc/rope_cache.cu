@@ -135,40 +135,59 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
     const int vec_per_head = pairing == 0 ? head_dim / VEC : half / VEC;
     const int units_per_token = (n_heads + (write_cache ? n_kv_heads : 0)) * vec_per_head;
     const size_t head_stride = (size_t)kPageTokens * head_dim;
-    for (int u = threadIdx.x; u < n_here * units_per_token; u += kRopeThreads) {
-        const int i = u / units_per_token, w = u % units_per_token;
-        const int h = w / vec_per_head, v = w % vec_per_head;
-        T* src = qkv + (size_t)(t0 + i) * row_len + (size_t)h * head_dim;  // query heads, then key heads: contiguous
-        T* dst = src;
-        if (h >= n_heads)
-            dst = k_pool + ((size_t)page_s[i] * n_kv_heads * kPageTokens + (pos_s[i] % kPageTokens)) * head_dim +
-                  (size_t)(h - n_heads) * head_stride;
-        const float* sn = sin_s + i * half;
-        const float* cs = cos_s + i * half;
-        if (pairing == 0) {
-            uint4 raw = *reinterpret_cast<const uint4*>(src + v * VEC);
-            T* e = reinterpret_cast<T*>(&raw);
+    // Four units per thread are read before the first is rotated and written: a unit is a dependent read, rotate,
+    // write, and one at a time the kernel waits for memory four times as often.
+    constexpr int kBatch = 4;
+    const int n_units = n_here * units_per_token;
+    for (int u0 = threadIdx.x; u0 < n_units; u0 += kRopeThreads * kBatch) {
+        uint4 lo[kBatch], hi[kBatch];
+        T* dst[kBatch];
+        int tok[kBatch], vec[kBatch];
 #pragma unroll
-            for (int k = 0; k < VEC; k += 2) {
-                const int j = (v * VEC + k) / 2;
-                const float v0 = to_f32<T>(e[k]), v1 = to_f32<T>(e[k + 1]);
-                e[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
-                e[k + 1] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
-            }
-            *reinterpret_cast<uint4*>(dst + v * VEC) = raw;
-        } else {
-            uint4 lo = *reinterpret_cast<const uint4*>(src + v * VEC), hi = *reinterpret_cast<const uint4*>(src + half + v * VEC);
-            T* a = reinterpret_cast<T*>(&lo);
-            T* b = reinterpret_cast<T*>(&hi);
+        for (int b = 0; b < kBatch; ++b) {
+            const int u = u0 + b * kRopeThreads;
+            if (u >= n_units) { dst[b] = nullptr; continue; }
+            const int i = u / units_per_token, w = u % units_per_token;
+            const int h = w / vec_per_head, v = w % vec_per_head;
+            T* src = qkv + (size_t)(t0 + i) * row_len + (size_t)h * head_dim;  // query heads, then key heads: contiguous
+            dst[b] = src;
+            if (h >= n_heads)
+                dst[b] = k_pool + ((size_t)page_s[i] * n_kv_heads * kPageTokens + (pos_s[i] % kPageTokens)) * head_dim +
+                         (size_t)(h - n_heads) * head_stride;
+            tok[b] = i;
+            vec[b] = v;
+            lo[b] = *reinterpret_cast<const uint4*>(src + v * VEC);
+            if (pairing != 0) hi[b] = *reinterpret_cast<const uint4*>(src + half + v * VEC);
+        }
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                const int j = v * VEC + k;
-                const float v0 = to_f32<T>(a[k]), v1 = to_f32<T>(b[k]);
-                a[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
-                b[k] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
+        for (int b = 0; b < kBatch; ++b) {
+            if (dst[b] == nullptr) continue;
+            const float* sn = sin_s + tok[b] * half;
+            const float* cs = cos_s + tok[b] * half;
+            const int v = vec[b];
+            if (pairing == 0) {
+                T* e = reinterpret_cast<T*>(&lo[b]);
+#pragma unroll
+                for (int k = 0; k < VEC; k += 2) {
+                    const int j = (v * VEC + k) / 2;
+                    const float v0 = to_f32<T>(e[k]), v1 = to_f32<T>(e[k + 1]);
+                    e[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
+                    e[k + 1] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
+                }
+                *reinterpret_cast<uint4*>(dst[b] + v * VEC) = lo[b];
+            } else {
+                T* a = reinterpret_cast<T*>(&lo[b]);
+                T* c = reinterpret_cast<T*>(&hi[b]);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const int j = v * VEC + k;
+                    const float v0 = to_f32<T>(a[k]), v1 = to_f32<T>(c[k]);
+                    a[k] = from_f32<T>(v0 * cs[j] - v1 * sn[j]);
+                    c[k] = from_f32<T>(v0 * sn[j] + v1 * cs[j]);
+                }
+                *reinterpret_cast<uint4*>(dst[b] + v * VEC) = lo[b];
+                *reinterpret_cast<uint4*>(dst[b] + half + v * VEC) = hi[b];
             }
-            *reinterpret_cast<uint4*>(dst + v * VEC) = lo;
-            *reinterpret_cast<uint4*>(dst + half + v * VEC) = hi;
         }
     }
     if (!write_cache) return;
