@@ -61,8 +61,102 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Persistent: CTA c computes tiles c, c + gridDim.x, ...; tiles are numbered with n fastest so that CTAs running at
-// the same time share rows of A and sweep W, which the L2 then serves.  Two accumulators of BN columns live in tensor
+// The epilogue of one 128 x BN accumulator (TMEM columns acc .. acc + BN) by one of the four epilogue warps: warp
+// `quarter` reads TMEM lanes 32 * quarter .. + 31, which are rows m0 + 32 * quarter .. of C; a thread holds one row, 32
+// columns at a time.  `box` is the warp's 32 x 32 float32 staging box for the bulk reduction (EPI 1 with reduce_c).
+template <int BN, int EPI, typename TC>
+__device__ __forceinline__ void epilogue_tile(uint32_t acc, int quarter, int lane, int m0, int n0, int M, int N,
+                                              TC* __restrict__ C, int ldc, int reduce_c, const CUtensorMap* map_c, float* box) {
+    const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= N) break;  // uniform: whole chunk beyond the matrix
+        float v[32];
+        tmem_ld32(acc + ((uint32_t)(quarter * 32) << 16) + c0, v);
+        if (EPI == 1 && reduce_c) {
+            // the box is free once the reduction before has read it; row `lane` of the box, its eight
+            // 16-byte pieces at piece ^ (row % 8): the layout the tensor map's 128-byte swizzle expects
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+            float* box_row = box + lane * 32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(box_row + ((j ^ (lane & 7)) << 2)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {   // (columns of the box beyond C are clipped by the reduction, and so are rows beyond M)
+                tma_reduce_add_2d(map_c, n0 + c0, m0 + quarter * 32, box);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            continue;
+        }
+        if (row >= M) continue;
+        const int col = n0 + c0;
+        if (EPI == 2) {
+            TC* dst = C + (size_t)row * ldc + (col >> 1);
+            if (col + 32 <= N && ((uintptr_t)dst & 15) == 0 && sizeof(TC) == 2) {
+                uint32_t pk[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
+                    __nv_bfloat162 h = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                uint4* d = reinterpret_cast<uint4*>(dst);
+                d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>((v[2 * j] / (1.0f + expf(-v[2 * j]))) * v[2 * j + 1]);
+            }
+        } else {
+            TC* dst = C + (size_t)row * ldc + col;
+            const bool whole = col + 32 <= N && ((uintptr_t)dst & 15) == 0;
+            if (EPI == 1) {  // C is the float32 residual stream
+                float* d = reinterpret_cast<float*>(dst);
+                if (whole) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 r = *reinterpret_cast<float4*>(d + j);
+                        r.x += v[j]; r.y += v[j + 1]; r.z += v[j + 2]; r.w += v[j + 3];
+                        *reinterpret_cast<float4*>(d + j) = r;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) if (col + j < N) d[j] += v[j];
+                }
+            } else if (sizeof(TC) == 2 && whole) {
+                uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                    __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                    __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                    d[j] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                      *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) if (col + j < N) dst[j] = from_f32<TC>(v[j]);
+            }
+        }
+    }
+}
+
+// The order of tiles: bands of kBandTiles rows of tiles, and inside a band down the rows first.  The CTAs that run at
+// the same time then share a few blocks of W and the band's blocks of A, and W comes from memory once per band instead
+// of once per row of tiles (a W larger than the L2 would otherwise stream from memory again and again).
+constexpr int kBandTiles = 8;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int band = tile / (kBandTiles * tiles_n), within = tile - band * kBandTiles * tiles_n;
+    const int rows = min(kBandTiles, tiles_m - band * kBandTiles);
+    tn = within / rows;
+    tm = band * kBandTiles + (within - tn * rows);
+}
+
+// Persistent: CTA c computes tiles c, c + gridDim.x, ... in that order.  Two accumulators of BN columns live in tensor
 // memory: while the epilogue warps read tile i out of one, the MMA thread already fills the other with tile i + 1.
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kGemmTcThreads, 1)
@@ -104,7 +198,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
@@ -148,88 +244,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int local = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1;
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-            const int row = m0 + quarter * 32 + lane;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             bool ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1, abort_flag);
             if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (3 << 8) | quarter); }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= N) break;  // uniform: whole chunk beyond the matrix
-                float v[32];
-                tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, v);
-                if (EPI == 1 && reduce_c) {
-                    // the box is free once the reduction before has read it; row `lane` of the box, its eight
-                    // 16-byte pieces at piece ^ (row % 8): the layout the tensor map's 128-byte swizzle expects
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    __syncwarp();
-                    float* box_row = cs.box[quarter] + lane * 32;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4*>(box_row + ((j ^ (lane & 7)) << 2)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) {   // (columns of the box beyond C are clipped by the reduction, and so are rows beyond M)
-                        tma_reduce_add_2d(&map_c, n0 + c0, m0 + quarter * 32, cs.box[quarter]);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                    continue;
-                }
-                if (row >= M) continue;
-                const int col = n0 + c0;
-                if (EPI == 2) {
-                    TC* dst = C + (size_t)row * ldc + (col >> 1);
-                    if (col + 32 <= N && ((uintptr_t)dst & 15) == 0 && sizeof(TC) == 2) {
-                        uint32_t pk[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                            __nv_bfloat162 h = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
-                            pk[j] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                        uint4* d = reinterpret_cast<uint4*>(dst);
-                        d[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        d[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (col + 2 * j + 1 < N) dst[j] = from_f32<TC>((v[2 * j] / (1.0f + expf(-v[2 * j]))) * v[2 * j + 1]);
-                    }
-                } else {
-                    TC* dst = C + (size_t)row * ldc + col;
-                    const bool whole = col + 32 <= N && ((uintptr_t)dst & 15) == 0;
-                    if (EPI == 1) {  // C is the float32 residual stream
-                        float* d = reinterpret_cast<float*>(dst);
-                        if (whole) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 r = *reinterpret_cast<float4*>(d + j);
-                                r.x += v[j]; r.y += v[j + 1]; r.z += v[j + 2]; r.w += v[j + 3];
-                                *reinterpret_cast<float4*>(d + j) = r;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) if (col + j < N) d[j] += v[j];
-                        }
-                    } else if (sizeof(TC) == 2 && whole) {
-                        uint4* d = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                            d[j] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
-                                              *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) if (col + j < N) dst[j] = from_f32<TC>(v[j]);
-                    }
-                }
-            }
+            epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter]);
             // this warp has read its lanes of the accumulator out: once all four have, the MMA thread may reuse it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -243,6 +266,180 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same product by pairs of CTAs (tcgen05 cta_group::2).  The single-CTA kernel above is bound by the rate at which
+// an SM can ask for operand rows (a 128 x 256 tile wants 384 rows of 128 bytes per k-step), not by its tensor core.
+// Here the two CTAs of a cluster share one 256 x BN tile: each loads its own 128 rows of A and only half of the W
+// stage (BN / 2 rows), the leader's MMA thread issues M = 256 instructions that read both CTAs' shared memory, and
+// each CTA's tensor memory receives the 128 rows of the tile that belong to its rows of A.  Per flop an SM asks for a
+// third fewer rows.  No operand is multicast: every load is an ordinary TMA load of the CTA's own box.
+//   full[s]       on the leader, 2 arrivals: each CTA's producer announces its bytes there (the peer remotely) and
+//                 both CTAs' loads complete on it, so one wait tells the MMA thread that the stage is whole
+//   empty[s]      in each CTA, signalled by the leader's tcgen05.commit (to both CTAs at once)
+//   acc_full[b]   in each CTA, likewise; acc_empty[b] on the leader, 8 arrivals (four epilogue warps of each CTA)
+template <int BN, int STAGES>
+struct PairSmem {
+    alignas(1024) __nv_bfloat16 a[STAGES][BM * BK];
+    alignas(1024) __nv_bfloat16 b[STAGES][(BN / 2) * BK];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// an arrival (with bytes to expect) on an mbarrier given by its address in the cluster's shared window.  Relaxed: it
+// publishes nothing the thread wrote (a release at cluster scope costs most of a microsecond, every k-step).
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion is counted on an mbarrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, int accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the MMAs issued so far are complete, on the mbarrier at this address in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+
+template <int BN, int STAGES, int EPI, typename TC>
+__global__ void __launch_bounds__(kGemmTcThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K) {
+    using Smem = PairSmem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    auto& sm = *reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    ResidualStage& cs = *reinterpret_cast<ResidualStage*>(reinterpret_cast<uint8_t*>(&sm) + ((sizeof(Smem) + 1023) & ~(size_t)1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_rank();          // 0: the leader, which issues the MMAs
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + 2 * BM - 1) / (2 * BM), n_tiles = tiles_n * tiles_m;
+    const int k_iters = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 2); mbar_init(&sm.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 8); }
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        if (EPI == 1 && reduce_c) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+    }
+    if (warp == 1) {  // two accumulators of BN columns in both CTAs' tensor memory: one warp of each CTA asks
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before either signals the other
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sm.tmem_base;
+    volatile int* abort_flag = &sm.abort_flag;
+    // one MMA writes both CTAs' tensor memory at the same address: the two allocations must agree
+    if (threadIdx.x == 0) {
+        uint32_t other;
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(other) : "r"(cluster_peer_address(&sm.tmem_base, rank ^ 1)));
+        if (other != tmem) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (8 << 8) | rank); }
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer of this CTA's half of every stage
+        int it = 0;
+        bool ok = !*abort_flag;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * 2 * BM + rank * BM, n0 = tn * BN + rank * (BN / 2);
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(&sm.empty[s], ((it / STAGES) - 1) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (9 << 8) | s); ok = false; break;
+                }
+                const uint32_t full = cluster_peer_address(&sm.full[s], 0);
+                if (rank == 0) mbar_expect_tx(&sm.full[s], (BM + BN / 2) * BK * 2);
+                else mbar_expect_tx_cluster(full, (BM + BN / 2) * BK * 2);
+                tma_load_2d_pair(sm.a[s], &map_a, k * BK, m0, full);
+                tma_load_2d_pair(sm.b[s], &map_w, k * BK, n0, full);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA issuer of the pair
+        constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+        int it = 0, local = 0;
+        bool ok = !*abort_flag;
+        for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
+            const int buf = local & 1;
+            if (!mbar_wait(&sm.acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) {
+                *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (12 << 8) | buf); break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + buf * BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait(&sm.full[s], (it / STAGES) & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (10 << 8) | s); ok = false; break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ad = umma_desc(sm.a[s]), bd = umma_desc(sm.b[s]);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; ++kk)
+                    umma_bf16_pair(acc, ad + 2 * kk, bd + 2 * kk, idesc, (k | kk) != 0);
+                umma_commit_pair(&sm.empty[s]);
+            }
+            if (ok) umma_commit_pair(&sm.acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue of this CTA's 128 rows of every tile
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++local) {
+            const int buf = local & 1;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * 2 * BM + rank * BM, n0 = tn * BN;
+            bool ok = mbar_wait(&sm.acc_full[buf], (local >> 1) & 1, abort_flag);
+            if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_status, 0, (11 << 8) | quarter); }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (m0 < M) epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter]);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_peer_address(&sm.acc_empty[buf], 0));
+        }
+        if (EPI == 1 && reduce_c && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    cluster_sync_all();  // neither CTA leaves, or gives its tensor memory back, while the other may still signal it or compute into it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
     }
 }
 
@@ -488,6 +685,52 @@ static int launch_width(const void* A, int lda, const void* W, int ldw, void* C,
     return launch_tc<BN, STAGES, 0, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
 }
 
+// How many CTA pairs can run at once (a pair needs two SMs that can form a cluster; each CTA fills its SM).
+template <typename Kernel>
+static int resident_pairs(Kernel kernel, size_t smem) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(kGemmTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+template <int BN, int STAGES, int EPI, typename TC>
+static int launch_pair(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+    CUtensorMap ma, mw, mc = {};
+    if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN / 2)) return kErrUnsupportedSize;
+    const int reduce_c = (EPI == 1 && make_map_c(&mc, C, M, N, ldc)) ? 1 : 0;
+    const size_t smem = ((sizeof(PairSmem<BN, STAGES>) + 1023) & ~(size_t)1023) + (EPI == 1 ? sizeof(ResidualStage) : 0) + 1024;
+    static int pairs = -1;
+    auto kernel = gemm_tcgen05_pair_kernel<BN, STAGES, EPI, TC>;
+    if (pairs < 0) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return (int)cudaGetLastError();
+        pairs = resident_pairs(kernel, smem);
+    }
+    if (pairs <= 0) return kErrUnsupportedSize;
+    const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+    const unsigned n_pairs = (unsigned)(n_tiles < pairs ? n_tiles : pairs);
+    return launch_pdl_cluster(kernel, dim3(2 * n_pairs), dim3(kGemmTcThreads), smem, stream, dim3(2, 1, 1), true,
+                              ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K);
+}
+
+template <int BN, int STAGES>
+static int launch_pair_width(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M, int N, int K,
+                             int epilogue, cudaStream_t stream) {
+    if (epilogue == 2) return launch_pair<BN, STAGES, 2, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    if (epilogue == 1) return launch_pair<BN, STAGES, 1, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    if (c_dtype == kF32) return launch_pair<BN, STAGES, 0, float>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+    return launch_pair<BN, STAGES, 0, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream);
+}
+
 // Spans of K per tile for the cluster kernel (1: the plain kernel).  Worth it when the 128 x 128 tiles times the spans
 // still fit the SMs, a span keeps 8 k-steps or more, and the estimate (k-steps of a span plus 12 for the cluster's
 // barriers and the second pass over the tile, in the units of tile_width_for) beats the plain kernel's.
@@ -547,8 +790,9 @@ extern "C" int b200_gemm_tcgen05_k_spans(int M, int N, int K) {
 // tile_width: 256, 128 or 64 output columns per tile; 0 lets the product's shape decide.
 // k_spans: 2 or 4 cuts K among the CTAs of a cluster (128-column tiles; tile_width is then ignored), 1 never does,
 // 0 lets the shape decide.
+// cta_pair: 1 computes 256-row tiles by pairs of CTAs (tile_width 256 or 128), -1 never does, 0 lets the shape decide.
 extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw, void* C, int c_dtype, int ldc, int M,
-                                 int N, int K, int epilogue, int tile_width, int k_spans, cudaStream_t stream) {
+                                 int N, int K, int epilogue, int tile_width, int k_spans, int cta_pair, cudaStream_t stream) {
     using namespace b200;
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || (((uintptr_t)A | (uintptr_t)W) & 15)) return kErrUnsupportedSize;
@@ -556,6 +800,18 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
         return kErrBadArgument;
     if (c_dtype != kF32 && c_dtype != kBF16) return kErrBadArgument;
     if (k_spans != 0 && k_spans != 1 && k_spans != 2 && k_spans != 4) return kErrBadArgument;
+    if (cta_pair > 0) {
+        if (tile_width == 128) return launch_pair_width<128, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+        if (tile_width == 256 || tile_width == 0) return launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+        return kErrBadArgument;
+    }
+    // left the choice: pairs of CTAs as soon as their 256 x 256 tiles occupy two thirds of the SMs (measured: from there on
+    // the pair kernel is the faster one at every shape tried, by 5 to 25 %)
+    if (cta_pair == 0 && tile_width == 0 && k_spans == 0) {
+        const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+        if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2)
+            return launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+    }
     const int spans = k_spans > 0 ? k_spans : (tile_width > 0 ? 1 : k_spans_for(M, N, K));
     if (spans > 1) {
         if ((K + BK - 1) / BK < spans) return kErrBadArgument;

@@ -139,7 +139,7 @@ extern "C" int b200_rmsnorm(const float* x, const void* w, int w_dtype, void* ou
                             const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const bool vec = dim % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0;
-    if (vec && n_rows >= 64 && dim % 1024 == 0 && dim <= 4096) {   // many rows of a usual width: a warp per row
+    if (vec && n_rows >= 1024 && dim % 1024 == 0 && dim <= 4096) {   // rows for every SM several times over, of a usual width: a warp per row
         B200_DISPATCH_DTYPE(w_dtype, TW, B200_DISPATCH_DTYPE2(out_dtype, TO,
             switch (dim / 1024) {
                 case 1: return b200::launch_norm_warp<TW, TO, 8>(x, w, out, rows, n_rows, eps, stream);

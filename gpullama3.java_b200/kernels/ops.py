@@ -48,7 +48,7 @@ _SIGNATURES = {
                                                 c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                           c_int, c_int, c_int]),
+                                           c_int, c_int, c_int, c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -313,11 +313,13 @@ def gemm_decode_linked(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilog
 
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
-                 tile_width: int = 0, k_spans: int = 0) -> bool:
+                 tile_width: int = 0, k_spans: int = 0, cta_pair: int = 0) -> bool:
     """The prefill matrix product on tcgen05 tensor cores (bfloat16 operands, rows 16-byte aligned).
     ``tile_width``: 256, 128 or 64 output columns per tile; 0 lets the shape decide (narrower tiles when the
     widest would leave SMs without one).  ``k_spans``: 2 or 4 cuts K among the CTAs of a cluster, which add their
-    partial tiles in a fixed order (few tiles, long K); 1 never; 0 lets the shape decide.
+    partial tiles in a fixed order (few tiles, long K); 1 never; 0 lets the shape decide.  ``cta_pair``: 1 computes
+    tiles of 256 rows by pairs of CTAs that each load half of the weight stage (tile_width 256 or 128); -1 never;
+    0 lets the shape decide.
     Returns False, having done nothing, for operands it does not take."""
     M, K = a.shape
     lda, a_inner = a.stride()
@@ -333,7 +335,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     ldc, c_inner = c.stride()
     assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
     _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
-                                    tile_width, k_spans, _stream()), "gemm_tcgen05")
+                                    tile_width, k_spans, cta_pair, _stream()), "gemm_tcgen05")
     return True
 
 

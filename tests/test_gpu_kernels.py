@@ -355,6 +355,23 @@ def test_gemm_tcgen05_and_its_epilogues(M, N, K, width):
         assert not o.gemm_tcgen05(a[:, 4:], w[:, 4:], torch.empty(M, N, device="cuda"))
 
 
+@pytest.mark.parametrize("M, N, K", [(256, 256, 64), (256, 256, 512), (1, 8, 8), (100, 300, 72), (129, 257, 200), (257, 130, 136),
+                                     (300, 1030, 2048), (2048, 512, 1024), (2048, 3072, 2048), (1000, 20000, 256)])
+@pytest.mark.parametrize("width", [256, 128])
+def test_gemm_tcgen05_by_pairs_of_ctas(M, N, K, width):
+    """Tiles of 256 rows computed by two CTAs that each load their rows of the activations and half of the weight
+    stage: exact tiles, ragged edges (a second CTA with few rows, or none; a half of the weight stage beyond N),
+    several waves of tiles, more k-steps than stages, every epilogue.  Run twice: the same bits."""
+    import functools
+    o = ops()
+    a, w = _check_gemm_tcgen05(functools.partial(o.gemm_tcgen05, tile_width=width, cta_pair=1), M, N, K)
+    c1 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    c2 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    assert o.gemm_tcgen05(a, w, c1, tile_width=width, cta_pair=1) and o.gemm_tcgen05(a, w, c2, tile_width=width, cta_pair=-1)
+    assert torch.equal(c1, c2)      # the same sums in the same order as the single-CTA kernel
+    assert o.gemm_tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("M, N, K, spans", [(128, 128, 128, 2), (100, 300, 328, 4), (300, 1030, 2048, 2), (256, 2048, 8192, 4),
                                             (129, 130, 320, 4), (512, 2048, 8192, 0), (256, 1024, 4096, 0)])
 def test_gemm_tcgen05_with_k_cut_among_a_cluster(M, N, K, spans):
