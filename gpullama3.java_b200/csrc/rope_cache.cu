@@ -120,13 +120,19 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
     }
     for (int u = threadIdx.x; u < n_here * half; u += kRopeThreads)
         sincosf((float)pos_s[u / half] * inv_freq[u % half], &sin_s[u], &cos_s[u]);
+    // The columns of a tile are cut among the CTAs of grid.y, so that a prompt of a few thousand tokens still gives
+    // every SM several CTAs: this one takes units [w_lo, w_hi) of every token and value columns [c_lo, c_hi).
+    const int slice = blockIdx.y, n_slices = gridDim.y;
+    const int c_lo = (int)((long long)(kv_dim / VEC) * slice / n_slices) * VEC;
+    const int c_hi = (int)((long long)(kv_dim / VEC) * (slice + 1) / n_slices) * VEC;
+    const int c_n = c_hi - c_lo;
     // values of the tile into shared memory, 16 bytes at a time
     if (write_cache) {
-        const int vecs = kv_dim / VEC;
+        const int vecs = c_n / VEC;
         for (int u = threadIdx.x; u < n_here * vecs; u += kRopeThreads) {
             const int i = u / vecs, v = u % vecs;
-            *reinterpret_cast<uint4*>(v_s + (size_t)i * kv_dim + v * VEC) =
-                *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + i) * row_len + q_dim + kv_dim + v * VEC);
+            *reinterpret_cast<uint4*>(v_s + (size_t)i * c_n + v * VEC) =
+                *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + i) * row_len + q_dim + kv_dim + c_lo + v * VEC);
         }
     }
     __syncthreads();
@@ -138,7 +144,9 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
     // Four units per thread are read before the first is rotated and written: a unit is a dependent read, rotate,
     // write, and one at a time the kernel waits for memory four times as often.
     constexpr int kBatch = 4;
-    const int n_units = n_here * units_per_token;
+    const int w_lo = (int)((long long)units_per_token * slice / n_slices);
+    const int w_n = (int)((long long)units_per_token * (slice + 1) / n_slices) - w_lo;
+    const int n_units = n_here * w_n;
     for (int u0 = threadIdx.x; u0 < n_units; u0 += kRopeThreads * kBatch) {
         uint4 lo[kBatch], hi[kBatch];
         T* dst[kBatch];
@@ -147,7 +155,7 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
         for (int b = 0; b < kBatch; ++b) {
             const int u = u0 + b * kRopeThreads;
             if (u >= n_units) { dst[b] = nullptr; continue; }
-            const int i = u / units_per_token, w = u % units_per_token;
+            const int i = u / w_n, w = w_lo + u % w_n;
             const int h = w / vec_per_head, v = w % vec_per_head;
             T* src = qkv + (size_t)(t0 + i) * row_len + (size_t)h * head_dim;  // query heads, then key heads: contiguous
             dst[b] = src;
@@ -194,18 +202,18 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
     // values, transposed: row (kv head, dim) of the page gets the tile's positions
     if (aligned_s) {
         const size_t base = (size_t)page_s[0] * n_kv_heads * head_stride + (pos_s[0] % kPageTokens);
-        for (int u = threadIdx.x; u < kv_dim; u += kRopeThreads) {
-            const int g = u / head_dim, d = u % head_dim;
+        for (int u = threadIdx.x; u < c_n; u += kRopeThreads) {
+            const int g = (c_lo + u) / head_dim, d = (c_lo + u) % head_dim;
             alignas(16) T run[kRopeTile];
 #pragma unroll
-            for (int i = 0; i < kRopeTile; ++i) run[i] = v_s[(size_t)i * kv_dim + u];
+            for (int i = 0; i < kRopeTile; ++i) run[i] = v_s[(size_t)i * c_n + u];
             uint4* dst = reinterpret_cast<uint4*>(v_pool + base + g * head_stride + (size_t)d * kPageTokens);
 #pragma unroll
             for (int q = 0; q < (int)(kRopeTile * sizeof(T) / 16); ++q) dst[q] = reinterpret_cast<const uint4*>(run)[q];
         }
     } else {
-        for (int u = threadIdx.x; u < n_here * kv_dim; u += kRopeThreads) {
-            const int i = u / kv_dim, w = u % kv_dim, g = w / head_dim, d = w % head_dim;
+        for (int u = threadIdx.x; u < n_here * c_n; u += kRopeThreads) {
+            const int i = u / c_n, w = c_lo + u % c_n, g = w / head_dim, d = w % head_dim;
             v_pool[(size_t)page_s[i] * n_kv_heads * head_stride + g * head_stride + (size_t)d * kPageTokens +
                    (pos_s[i] % kPageTokens)] = v_s[u];
         }
@@ -232,8 +240,16 @@ extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions,
                           (((uintptr_t)qkv | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
         if (n_tokens >= 4 * b200::kRopeTile && fits) {
             const int grid = (n_tokens + b200::kRopeTile - 1) / b200::kRopeTile;
+            // two CTAs of this kernel fit an SM (registers): cut the columns so that one wave of CTAs covers the prompt
+            static int n_sms = 0;
+            if (n_sms == 0) {
+                int dev = 0;
+                if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms <= 0)
+                    n_sms = 148;
+            }
+            const int slices = grid >= 2 * n_sms ? 1 : (2 * n_sms / grid > 8 ? 8 : 2 * n_sms / grid);
             B200_DISPATCH_DTYPE(dtype, T,
-                return b200::launch_pdl(b200::rope_cache_write_tiled_kernel<T>, dim3(grid), dim3(b200::kRopeThreads),
+                return b200::launch_pdl(b200::rope_cache_write_tiled_kernel<T>, dim3(grid, slices), dim3(b200::kRopeThreads),
                                         (size_t)smem, stream, (T*)qkv, positions, seq_ids, page_table, table_stride, inv_freq,
                                         (T*)k_pool, (T*)v_pool, n_tokens, n_heads, n_kv_heads, head_dim, pairing, write_cache));
         }

@@ -53,6 +53,25 @@ def test_rmsnorm(w_dtype, out_dtype, dim, eps):
     assert torch.equal(out2, out[rows.long()])
 
 
+@pytest.mark.parametrize("w_dtype", DTYPES)
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("n_rows, dim", [(1024, 1024), (1027, 2048), (1500, 3072), (1030, 4096), (1024, 5120)])
+def test_rmsnorm_of_many_rows(w_dtype, out_dtype, n_rows, dim):
+    """A prompt's worth of rows takes the warp-per-row kernel at the usual widths (1024-wide steps up to 4096; 5120
+    does not): a count of rows that does not fill the last CTA, each row with a scale of its own, and a selection."""
+    g = torch.Generator().manual_seed(n_rows + dim)
+    x = (torch.randn(n_rows, dim, generator=g) * (0.1 + 5 * torch.rand(n_rows, 1, generator=g))).cuda()
+    w = (1 + 0.1 * torch.randn(dim, generator=g)).cuda().to(w_dtype)
+    out = torch.full((n_rows, dim), 7.0, device="cuda", dtype=out_dtype)
+    ops().rmsnorm(x, w, out, 1e-5)
+    ref = P.rmsnorm(x.cpu(), w.float().cpu(), 1e-5)
+    torch.testing.assert_close(out.float().cpu(), ref.to(out_dtype).float(), **tol(out_dtype, ref))
+    rows = torch.randperm(n_rows, generator=g)[:1024].to(torch.int32).cuda()
+    out2 = torch.empty(1024, dim, device="cuda", dtype=out_dtype)
+    ops().rmsnorm(x, w, out2, 1e-5, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
 def _paged_setup(dtype, n_seqs, kv_lens, KVH, D, n_pages, seed=0):
     """Random keys/values laid out in scattered pages; returns pools, the page table and the dense
     per-sequence keys/values."""
