@@ -26,6 +26,7 @@ class Workspace:
         self.capacity = 0
         self._buf: torch.Tensor | None = None
         self._top = 0
+        self._typed: dict = {}    # per dtype: the aligned block seen as that type, and the type's size in bytes
         self._wanted = 0          # the most a pass would have held had everything fitted
         self.overflowed = 0       # tensors that came from the allocator instead (tests and diagnostics)
         if capacity:
@@ -33,6 +34,7 @@ class Workspace:
 
     def _allocate(self, nbytes: int) -> None:
         self._buf = None   # let the old block go first
+        self._typed = {}
         self._buf = torch.empty(nbytes + _ALIGN, dtype=torch.uint8, device=self.device)
         self._base = (-self._buf.data_ptr()) % _ALIGN   # the first aligned byte of the block
         self.capacity = nbytes
@@ -54,12 +56,19 @@ class Workspace:
 
     def take(self, shape, dtype: torch.dtype) -> torch.Tensor:
         shape = tuple(int(s) for s in shape)
-        nbytes = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+        seen = self._typed.get(dtype)
+        if seen is None:   # (pieces start on 256-byte boundaries, so every element type divides their offsets)
+            size = torch.empty((), dtype=dtype).element_size()
+            block = self._buf[self._base:self._base + self.capacity // size * size].view(dtype) if self._buf is not None else None
+            seen = self._typed[dtype] = (block, size)
+        block, size = seen
+        numel = math.prod(shape)
         start = (self._top + _ALIGN - 1) // _ALIGN * _ALIGN
-        end = start + nbytes
+        end = start + numel * size
         self._top = end
-        self._wanted = max(self._wanted, end)
-        if end > self.capacity or nbytes == 0:
+        if end > self._wanted:
+            self._wanted = end
+        if end > self.capacity or numel == 0:
             self.overflowed += 1
             return torch.empty(shape, dtype=dtype, device=self.device)
-        return self._buf[self._base + start:self._base + end].view(dtype).view(shape)
+        return block.narrow(0, start // size, numel).view(shape)
