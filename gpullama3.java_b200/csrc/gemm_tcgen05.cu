@@ -61,12 +61,129 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// What the fused-projection epilogue (EPI 3) needs: the product is the query, key and value projection of T tokens
+// ([T, (heads + 2 kv_heads) head_dim], heads of head_dim 64 or 128 lying whole inside a 256-column tile), and its
+// epilogue does what a kernel of its own does otherwise (inference/InferenceCore.java:83-101 of the reference project):
+// queries are rotated and stored to C, keys are rotated and stored at their position in the cache pages, values are
+// stored there transposed.  Every sum is first rounded to bfloat16, as the stored projection would be, then rotated in
+// float32 with the angles of the token's position (cosine and sine per pair, made once per pass) and rounded again:
+// the same bits as the two kernels one after the other.
+struct RopeEpilogue {
+    const int* positions;      // [T]
+    const int* seq_ids;        // [T]
+    const int* page_table;     // [n_seqs][table_stride]
+    int table_stride;
+    const float2* angles;      // [head_dim / 2][T]: (cos, sin) of position * frequency (a warp's 32 tokens read neighbours)
+    int n_tokens;              // T
+    __nv_bfloat16* k_pool;     // [page][kv_head][64][head_dim]
+    __nv_bfloat16* v_pool;     // [page][kv_head][head_dim][64]
+    int n_heads, n_kv_heads, head_dim;
+    int pairing;               // 0: (2j, 2j+1); 1: (j, j + head_dim/2)
+    int write_cache;           // 0: keys and values are dropped (the layer reads a cache another layer writes)
+};
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32]) {   // dst 16-byte aligned
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+        d[j] = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                          *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+    }
+}
+
+// One warp's 32 rows of a tile that holds whole heads.  Row = token; a head's columns are taken 32 at a time (with the
+// half pairing together with the 32 columns head_dim / 2 further on, where the partners are).
+template <int BN>
+__device__ __forceinline__ void epilogue_qkv_rope(uint32_t acc, int quarter, int lane, int m0, int n0, int M, int N,
+                                                  __nv_bfloat16* __restrict__ C, int ldc, const RopeEpilogue& rp) {
+    const int row = m0 + quarter * 32 + lane;
+    const bool live = row < M;
+    const int D = rp.head_dim, half = D / 2;
+    const int q_dim = rp.n_heads * D, kv_dim = rp.n_kv_heads * D;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int pos = live ? rp.positions[row] : 0;
+    const float2* ang = rp.angles + (live ? row : 0);   // pair i of this token: ang[i * T]
+    const size_t T = (size_t)rp.n_tokens;
+    size_t page = 0;
+    if (live && rp.write_cache && n0 + BN > q_dim) page = (size_t)rp.page_table[(size_t)rp.seq_ids[row] * rp.table_stride + pos / 64];
+    const int in_page = pos % 64;
+#pragma unroll 1
+    for (int h0 = 0; h0 < BN; h0 += D) {
+        const int n = n0 + h0;            // first column of the head: a whole head of queries, keys or values
+        if (n >= N) break;
+        if (n >= q_dim + kv_dim) {        // values: transposed into the page, one element per dimension
+            if (!rp.write_cache) continue;
+            const int kvh = (n - q_dim - kv_dim) / D;
+            __nv_bfloat16* dst = rp.v_pool + ((page * rp.n_kv_heads + kvh) * D) * 64 + in_page;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float v[32];
+                tmem_ld32(acc + lane_base + h0 + c0, v);
+                if (live) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) dst[(size_t)(c0 + j) * 64] = __float2bfloat16_rn(v[j]);
+                }
+            }
+            continue;
+        }
+        __nv_bfloat16* dst;               // where the rotated head goes
+        if (n < q_dim) {
+            dst = C + (size_t)(live ? row : 0) * ldc + n;
+        } else {
+            if (!rp.write_cache) continue;
+            const int kvh = (n - q_dim) / D;
+            dst = rp.k_pool + ((page * rp.n_kv_heads + kvh) * 64 + in_page) * D;
+        }
+        if (rp.pairing == 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                float v[32];
+                tmem_ld32(acc + lane_base + h0 + c0, v);
+                if (!live) continue;
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float2 a = ang[(size_t)((c0 + j) / 2) * T];
+                    const float v0 = round_bf16(v[j]), v1 = round_bf16(v[j + 1]);
+                    v[j] = v0 * a.x - v1 * a.y;
+                    v[j + 1] = v0 * a.y + v1 * a.x;
+                }
+                store_bf16x32(dst + c0, v);
+            }
+        } else {
+#pragma unroll 1
+            for (int c0 = 0; c0 < half; c0 += 32) {
+                float lo[32], hi[32];
+                tmem_ld32(acc + lane_base + h0 + c0, lo);
+                tmem_ld32(acc + lane_base + h0 + half + c0, hi);
+                if (!live) continue;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float2 a = ang[(size_t)(c0 + j) * T];
+                    const float v0 = round_bf16(lo[j]), v1 = round_bf16(hi[j]);
+                    lo[j] = v0 * a.x - v1 * a.y;
+                    hi[j] = v0 * a.y + v1 * a.x;
+                }
+                store_bf16x32(dst + c0, lo);
+                store_bf16x32(dst + half + c0, hi);
+            }
+        }
+    }
+}
+
 // The epilogue of one 128 x BN accumulator (TMEM columns acc .. acc + BN) by one of the four epilogue warps: warp
 // `quarter` reads TMEM lanes 32 * quarter .. + 31, which are rows m0 + 32 * quarter .. of C; a thread holds one row, 32
 // columns at a time.  `box` is the warp's 32 x 32 float32 staging box for the bulk reduction (EPI 1 with reduce_c).
 template <int BN, int EPI, typename TC>
 __device__ __forceinline__ void epilogue_tile(uint32_t acc, int quarter, int lane, int m0, int n0, int M, int N,
-                                              TC* __restrict__ C, int ldc, int reduce_c, const CUtensorMap* map_c, float* box) {
+                                              TC* __restrict__ C, int ldc, int reduce_c, const CUtensorMap* map_c, float* box,
+                                              const RopeEpilogue& rope) {
+    if constexpr (EPI == 3) {
+        epilogue_qkv_rope<BN>(acc, quarter, lane, m0, n0, M, N, reinterpret_cast<__nv_bfloat16*>(C), ldc, rope);
+        return;
+    }
     const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -161,7 +278,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kGemmTcThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K) {
+                    const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K,
+                    const RopeEpilogue rope) {
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<GemmSmem<BN, STAGES>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // (the residual epilogue's boxes follow the ring; the launch asks for them only when reduce_c is set)
@@ -252,7 +370,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter]);
+            epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter], rope);
             // this warp has read its lanes of the accumulator out: once all four have, the MMA thread may reuse it
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -327,7 +445,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 template <int BN, int STAGES, int EPI, typename TC>
 __global__ void __launch_bounds__(kGemmTcThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                         const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K) {
+                         const __grid_constant__ CUtensorMap map_c, int reduce_c, TC* __restrict__ C, int ldc, int M, int N, int K,
+                         const RopeEpilogue rope) {
     using Smem = PairSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     auto& sm = *reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -427,7 +546,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (m0 < M) epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter]);
+            if (m0 < M) epilogue_tile<BN, EPI, TC>(tmem + buf * BN, quarter, lane, m0, n0, M, N, C, ldc, reduce_c, &map_c, cs.box[quarter], rope);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(cluster_peer_address(&sm.acc_empty[buf], 0));
@@ -657,7 +776,8 @@ static bool make_map_c(CUtensorMap* map, const void* base, int rows, int cols, i
 }
 
 template <int BN, int STAGES, int EPI, typename TC>
-static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream,
+                     const RopeEpilogue& rope = RopeEpilogue{}) {
     CUtensorMap ma, mw, mc = {};
     if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN)) return kErrUnsupportedSize;
     // the residual sum as bulk reductions where C allows a tensor map (else thread by thread, as the other epilogues)
@@ -673,7 +793,7 @@ static int launch_tc(const void* A, int lda, const void* W, int ldw, void* C, in
     const int n_sms = sm_count();
     const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(n_tiles < n_sms ? n_tiles : n_sms));
-    return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K);
+    return launch_pdl(kernel, dim3(grid), dim3(kGemmTcThreads), smem, stream, ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K, rope);
 }
 
 template <int BN, int STAGES>
@@ -703,7 +823,8 @@ static int resident_pairs(Kernel kernel, size_t smem) {
 }
 
 template <int BN, int STAGES, int EPI, typename TC>
-static int launch_pair(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream) {
+static int launch_pair(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, cudaStream_t stream,
+                       const RopeEpilogue& rope = RopeEpilogue{}) {
     CUtensorMap ma, mw, mc = {};
     if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mw, W, N, K, ldw, BN / 2)) return kErrUnsupportedSize;
     const int reduce_c = (EPI == 1 && make_map_c(&mc, C, M, N, ldc)) ? 1 : 0;
@@ -719,7 +840,7 @@ static int launch_pair(const void* A, int lda, const void* W, int ldw, void* C, 
     const long long n_tiles = (long long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
     const unsigned n_pairs = (unsigned)(n_tiles < pairs ? n_tiles : pairs);
     return launch_pdl_cluster(kernel, dim3(2 * n_pairs), dim3(kGemmTcThreads), smem, stream, dim3(2, 1, 1), true,
-                              ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K);
+                              ma, mw, mc, reduce_c, (TC*)C, ldc, M, N, K, rope);
 }
 
 template <int BN, int STAGES>
@@ -826,4 +947,37 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     if (width == 128) return launch_width<128, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
     if (width == 64) return launch_width<64, 8>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
     return kErrBadArgument;
+}
+
+// The query, key and value projection of a prompt pass with rotation and cache write in its epilogue (see RopeEpilogue).
+// A [M, K] activations, W [(n_heads + 2 n_kv_heads) head_dim, K], C [M, ldc] receives the rotated queries (its key and
+// value columns are left untouched).  Taken when the heads are 64 or 128 wide and the shape is one for 256-column tiles
+// (pairs of CTAs, or single CTAs whose wide tiles fill the SMs); kErrUnsupportedSize otherwise, and the caller runs the
+// product and the rotation kernel one after the other.
+extern "C" int b200_gemm_tcgen05_qkv_rope(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int K,
+                                          const int* positions, const int* seq_ids, const int* page_table, int table_stride,
+                                          const float* angles, void* k_pool, void* v_pool, int n_heads, int n_kv_heads,
+                                          int head_dim, int pairing, int write_cache, cudaStream_t stream) {
+    using namespace b200;
+    if (M <= 0) return 0;
+    if (K < 8 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ldc % 8 != 0 ||
+        (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) || ((uintptr_t)angles & 7))
+        return kErrUnsupportedSize;
+    if ((head_dim != 64 && head_dim != 128) || n_heads <= 0 || n_kv_heads <= 0 || (pairing != 0 && pairing != 1))
+        return kErrUnsupportedSize;
+    if (write_cache && (k_pool == nullptr || v_pool == nullptr)) return kErrBadArgument;
+    const int N = (n_heads + 2 * n_kv_heads) * head_dim;
+    RopeEpilogue rope;
+    rope.positions = positions; rope.seq_ids = seq_ids; rope.page_table = page_table; rope.table_stride = table_stride;
+    rope.angles = reinterpret_cast<const float2*>(angles);
+    rope.n_tokens = M;
+    rope.k_pool = (__nv_bfloat16*)k_pool; rope.v_pool = (__nv_bfloat16*)v_pool;
+    rope.n_heads = n_heads; rope.n_kv_heads = n_kv_heads; rope.head_dim = head_dim; rope.pairing = pairing;
+    rope.write_cache = write_cache ? 1 : 0;
+    const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
+    if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2)
+        return launch_pair<256, 6, 3, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, rope);
+    if (k_spans_for(M, N, K) == 1 && tile_width_for(M, N) == 256)
+        return launch_tc<256, 4, 3, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, rope);
+    return kErrUnsupportedSize;
 }

@@ -220,7 +220,29 @@ rope_cache_write_tiled_kernel(T* __restrict__ qkv, const int* __restrict__ posit
     }
 }
 
+// Cosine and sine of position * frequency for every token of a pass and every pair of a head: what a product that
+// rotates in its own epilogue reads instead of evaluating them once per head.  The same expression as in the kernels above.
+__global__ void rope_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                   float2* __restrict__ out, int n_tokens, int half) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int u = blockIdx.x * blockDim.x + threadIdx.x;   // pair-major: out[pair][token]
+    if (u >= n_tokens * half) return;
+    float sn, cs;
+    sincosf((float)positions[u % n_tokens] * inv_freq[u / n_tokens], &sn, &cs);
+    out[u] = make_float2(cs, sn);
+}
+
 }  // namespace b200
+
+// out [half][n_tokens] pairs (cos, sin), float32
+extern "C" int b200_rope_angles(const int* positions, const float* inv_freq, float* out, int n_tokens, int half,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0 || half <= 0) return 0;
+    const long long n = (long long)n_tokens * half;
+    return b200::launch_pdl(b200::rope_angles_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, positions, inv_freq,
+                            reinterpret_cast<float2*>(out), n_tokens, half);
+}
 
 extern "C" int b200_rope_cache_write(void* qkv, int dtype, const int* positions, const int* seq_ids,
                                      const int* page_table, int table_stride, const float* inv_freq, void* k_pool,

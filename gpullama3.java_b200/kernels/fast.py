@@ -24,6 +24,21 @@ def try_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int) -
     return ops.gemm_tcgen05(a, w, c, epilogue)
 
 
+def try_projection_with_rope(x: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, ctx, page_table, cache, mixer,
+                             writes_cache: bool) -> bool:
+    """A prompt pass's query/key/value projection with rotation and cache write in the product's epilogue, where the
+    sizes allow (whole heads of 64 or 128 in 256-column tiles, a position encoding that offers its angles per pass)."""
+    pos = mixer.position
+    if (ctx.all_decode or x.dtype != torch.bfloat16 or pos.rotary_dim != mixer.head_dim or mixer.head_dim not in (64, 128)
+            or not hasattr(pos, "angles")):
+        return False
+    if ops.gemm_tcgen05_k_spans(x.shape[0], w.shape[0], x.shape[1]) != 1:
+        return False
+    return ops.gemm_tcgen05_qkv_rope(x, w, qkv, ctx.positions, ctx.seq_ids, page_table, pos.angles(ctx),
+                                     cache.k if writes_cache else None, cache.v if writes_cache else None,
+                                     mixer.n_heads, mixer.n_kv_heads, mixer.head_dim, pos.pairing, writes_cache)
+
+
 def try_decode_attention_with_rope(qkv, out, ctx, page_table, cache, mixer, writes_cache: bool) -> bool:
     """A decode step's rotation, cache write and attention in one kernel, where the sizes allow."""
     pos = mixer.position

@@ -49,6 +49,10 @@ _SIGNATURES = {
                                                 c_int, c_void_p]),
     "b200_gemm_tcgen05": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                            c_int, c_int, c_int, c_int]),
+    "b200_gemm_tcgen05_qkv_rope": ("gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                    c_int, c_int, c_int]),
+    "b200_rope_angles": ("rope_cache", [c_void_p, c_void_p, c_void_p, c_int, c_int]),
     "b200_gemm_skinny": ("gemm_skinny_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                  c_int, c_int, c_int]),
     "b200_attention_decode": ("attention_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -336,6 +340,55 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
     assert Kw == K and c_inner == 1 and c.shape == (M, N // 2 if epilogue == EPILOGUE_GATED_SILU else N)
     _check(_fn("b200_gemm_tcgen05")(pa, lda, pw, ldw, c.data_ptr(), dtype_code(c.dtype), ldc, M, N, K, epilogue,
                                     tile_width, k_spans, cta_pair, _stream()), "gemm_tcgen05")
+    return True
+
+
+def rope_angles(positions: torch.Tensor, inv_freq: torch.Tensor, half: int) -> torch.Tensor:
+    """float32 [half, T, 2]: cosine and sine of position * frequency for every pair of a head and every token of a
+    pass, evaluated as the rotation kernels evaluate them (pair-major: the tokens of a warp read neighbours)."""
+    _dev(positions, inv_freq)
+    assert positions.dtype == torch.int32 and inv_freq.dtype == torch.float32 and inv_freq.numel() >= half > 0
+    out = torch.empty((half, positions.numel(), 2), dtype=torch.float32, device=positions.device)
+    _check(_fn("b200_rope_angles")(positions.data_ptr(), inv_freq.data_ptr(), out.data_ptr(), positions.numel(), half, _stream()),
+           "rope_angles")
+    return out
+
+
+_UNSUPPORTED = 10002   # kErrUnsupportedSize: the kernel leaves these operands to another one
+
+
+def gemm_tcgen05_qkv_rope(a: torch.Tensor, w: torch.Tensor, qkv: torch.Tensor, positions: torch.Tensor,
+                          seq_ids: torch.Tensor, page_table: torch.Tensor, angles: torch.Tensor,
+                          k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, n_heads: int, n_kv_heads: int,
+                          head_dim: int, pairing: int, write_cache: bool = True) -> bool:
+    """The query/key/value projection of a prompt pass on tcgen05 tensor cores with the rotation and the cache
+    write in its epilogue: ``qkv`` [T, (H + 2 KVH) D] receives the rotated queries (its key and value columns stay
+    unwritten), rotated keys and the values go to the cache pages of their positions.  ``angles``: ``rope_angles`` of
+    the pass.  Returns False, having done nothing, for shapes it does not take (head sizes other than 64 and 128, a
+    product of few tiles): the caller then runs the product and ``rope_cache_write``."""
+    M, K = a.shape
+    N = (n_heads + 2 * n_kv_heads) * head_dim
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or qkv.dtype != torch.bfloat16 or head_dim not in (64, 128)
+            or K % 8 or K < 8 or a.stride(1) != 1 or w.stride(1) != 1 or a.stride(0) % 8 or w.stride(0) % 8
+            or qkv.stride(0) % 8 or (a.data_ptr() | w.data_ptr() | qkv.data_ptr()) & 15):
+        return False
+    _dev(a, w, qkv, positions, seq_ids, page_table, angles, k_pool, v_pool)
+    assert tuple(w.shape) == (N, K) and tuple(qkv.shape) == (M, N) and qkv.stride(1) == 1
+    assert positions.dtype == seq_ids.dtype == page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.is_contiguous()
+    assert positions.numel() == M and seq_ids.numel() == M
+    assert angles.dtype == torch.float32 and angles.is_contiguous() and tuple(angles.shape) == (head_dim // 2, M, 2)
+    if write_cache:
+        assert k_pool.dtype == v_pool.dtype == torch.bfloat16 and k_pool.is_contiguous() and v_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
+        assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    status = _fn("b200_gemm_tcgen05_qkv_rope")(
+        a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), qkv.data_ptr(), qkv.stride(0), M, K, positions.data_ptr(),
+        seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], angles.data_ptr(),
+        k_pool.data_ptr() if write_cache else None, v_pool.data_ptr() if write_cache else None, n_heads, n_kv_heads,
+        head_dim, pairing, 1 if write_cache else 0, _stream())
+    if status == _UNSUPPORTED:
+        return False
+    _check(status, "gemm_tcgen05_qkv_rope")
     return True
 
 

@@ -70,16 +70,28 @@ class GroupedQueryAttention(Mixer):
         return ctx.all_decode and self.qkv.links_with(ctx.n_tokens, ctx.dtype)
 
     def forward(self, x, ctx: StepContext, cache: KVView, residual, writes_cache=True, then_norm=None):
-        qkv = self.qkv.store(x, ctx.dtype, ctx.empty)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
         table = ctx.page_tables[cache.group]
         out = ctx.empty((x.shape[0], self.q_dim), ctx.dtype)
-        if not fast.try_decode_attention_with_rope(qkv, out, ctx, table, cache, self, writes_cache):
-            ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
-                                 cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
-                                 self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
-            if not fast.try_attention(qkv, out, ctx, table, cache, self):
-                ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
-                                    self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
+        attended = False
+        if isinstance(x, torch.Tensor) and not ctx.all_decode:
+            # a prompt pass: projection, rotation and cache write as one product where its epilogue can do all three
+            qkv = ctx.empty((x.shape[0], self.qkv.out_features), ctx.dtype)
+            if not fast.try_projection_with_rope(x, self.qkv.weight, qkv, ctx, table, cache, self, writes_cache):
+                self.qkv.into(x, qkv)
+                ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
+                                     cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                                     self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
+        else:
+            qkv = self.qkv.store(x, ctx.dtype, ctx.empty)  # [T, q_dim + 2 kv_dim]; queries are rotated in place below
+            # a decode step: one kernel rotates, writes the cache and attends, where the sizes allow
+            attended = fast.try_decode_attention_with_rope(qkv, out, ctx, table, cache, self, writes_cache)
+            if not attended:
+                ops.rope_cache_write(qkv, ctx.positions, ctx.seq_ids, table, self.position.inverse_frequencies(x.device),
+                                     cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
+                                     self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
+        if not attended and not fast.try_attention(qkv, out, ctx, table, cache, self):
+            ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
+                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
         return self.o.add_to(out, residual, then_norm)
 
 

@@ -36,6 +36,10 @@ class Linear:
         self._run(a, c, ops.EPILOGUE_STORE)
         return c
 
+    def into(self, a: torch.Tensor, c: torch.Tensor) -> None:
+        """c = a @ W.T into a tensor the caller brings."""
+        self._run(a, c, ops.EPILOGUE_STORE)
+
     def add_to(self, a: torch.Tensor, residual: torch.Tensor, then_norm=None) -> ScaledRows | None:
         """residual += a @ W.T, the sum kept in float32.  With ``then_norm`` (a norm that has a row-factor form)
         and a product that links, the same kernel also leaves that norm of the new residual as ScaledRows."""

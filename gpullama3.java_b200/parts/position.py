@@ -74,6 +74,18 @@ class RotaryPositionEncoding(PositionEncoding):
         return t
 
 
+    def angles(self, ctx) -> torch.Tensor:
+        """float32 [rotary_dim / 2, T, 2]: cosine and sine of every token's angle in this pass, made once per pass
+        and shared by all layers whose frequencies are these (a product that rotates in its own epilogue reads them)."""
+        from ..kernels import ops
+
+        key = ("rotary angles", self.rotary_dim, self.theta, repr(self.scaling))
+        table = ctx.extras.get(key)
+        if table is None:
+            table = ctx.extras[key] = ops.rope_angles(ctx.positions, self.inverse_frequencies(ctx.device), self.rotary_dim // 2)
+        return table
+
+
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
 

@@ -391,6 +391,79 @@ def test_gemm_tcgen05_by_pairs_of_ctas(M, N, K, width):
     assert o.gemm_tcgen05_status() == 0
 
 
+@pytest.mark.parametrize("H, KVH, D, M, K", [(32, 8, 64, 1300, 512), (32, 8, 64, 900, 512), (8, 2, 128, 2100, 256),
+                                            (24, 8, 128, 700, 384), (5, 1, 64, 6500, 64)])
+@pytest.mark.parametrize("pairing", [0, 1], ids=["interleaved", "half"])
+@pytest.mark.parametrize("write_cache", [True, False], ids=["writes", "reads_only"])
+def test_projection_with_rotation_and_cache_write_in_its_epilogue(H, KVH, D, M, K, pairing, write_cache):
+    """The query/key/value product that rotates and writes the cache itself against the product followed by the rotation
+    kernel: the same bits in the queries and in every page, nothing else touched.  Three sequences packed into one
+    pass, one of them continuing at a position that is no multiple of anything, pages scattered; shapes that take
+    the pairs of CTAs and shapes that take single CTAs; both pairings; a layer that only reads the cache."""
+    o = ops()
+    g = torch.Generator().manual_seed(H * D + M + pairing)
+    N = (H + 2 * KVH) * D
+    lens = [M // 2, M // 3, M - M // 2 - M // 3]
+    starts = [0, 77, 0]
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(torch.int32).cuda()
+    seq_ids = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).to(torch.int32).cuda()
+    width = max(-(-(s + n) // 64) for s, n in zip(starts, lens))
+    n_pages = 3 * width + 5
+    table = torch.randperm(n_pages, generator=g)[:3 * width].to(torch.int32).reshape(3, width).cuda()
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).cuda()
+    k0 = torch.randn(n_pages, KVH, 64, D, generator=g).to(torch.bfloat16).cuda()
+    v0 = torch.randn(n_pages, KVH, D, 64, generator=g).to(torch.bfloat16).cuda()
+    # the two kernels one after the other
+    qkv_ref = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    assert o.gemm_tcgen05(a, w, qkv_ref, o.EPILOGUE_STORE)
+    k_ref, v_ref = k0.clone(), v0.clone()
+    o.rope_cache_write(qkv_ref, positions, seq_ids, table, inv_freq, k_ref if write_cache else None,
+                       v_ref if write_cache else None, H, KVH, D, D, pairing, write_cache=write_cache)
+    # the one product
+    angles = o.rope_angles(positions, inv_freq, D // 2)
+    ref_angle = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+    torch.testing.assert_close(angles[..., 0].cpu().t(), torch.cos(ref_angle), rtol=0, atol=2e-6)
+    torch.testing.assert_close(angles[..., 1].cpu().t(), torch.sin(ref_angle), rtol=0, atol=2e-6)
+    qkv = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    k_got, v_got = k0.clone(), v0.clone()
+    assert o.gemm_tcgen05_qkv_rope(a, w, qkv, positions, seq_ids, table, angles, k_got if write_cache else None,
+                                   v_got if write_cache else None, H, KVH, D, pairing, write_cache)
+    assert o.gemm_tcgen05_status() == 0
+    assert torch.equal(qkv[:, :H * D], qkv_ref[:, :H * D])
+    assert torch.equal(k_got, k_ref) and torch.equal(v_got, v_ref)
+    assert bool((qkv[:, H * D:] == 7.0).all())          # key and value columns of the projection buffer are not written
+    if write_cache:                                     # and the pages hold what the plain formulas give
+        kv = (a.float().cpu().double() @ w.float().cpu().double().t()).float().to(torch.bfloat16).float()
+        i = M // 2 + 5                                  # a token of the continuing sequence
+        pos, page = int(positions[i]), int(table[1, int(positions[i]) // 64])
+        want_v = kv[i, (H + KVH) * D:].view(KVH, D)
+        torch.testing.assert_close(v_got[page, :, :, pos % 64].float().cpu(), want_v, rtol=2.0 ** -7, atol=2.0 ** -7)
+        cs, sn = torch.cos(ref_angle[i]), torch.sin(ref_angle[i])
+        kk = kv[i, H * D:(H + KVH) * D].view(KVH, D)
+        x0, x1 = (kk[:, 0::2], kk[:, 1::2]) if pairing == 0 else (kk[:, :D // 2], kk[:, D // 2:])
+        r0, r1 = x0 * cs - x1 * sn, x0 * sn + x1 * cs
+        want_k = torch.stack([r0, r1], dim=-1).reshape(KVH, D) if pairing == 0 else torch.cat([r0, r1], dim=-1)
+        torch.testing.assert_close(k_got[page, :, pos % 64, :].float().cpu(), want_k, rtol=2.0 ** -6, atol=2.0 ** -6)
+
+
+def test_projection_with_rotation_declines_what_it_does_not_take():
+    o = ops()
+    H, KVH, K = 4, 2, 64
+    for D, M in [(32, 3000), (64, 40), (96, 3000)]:
+        N = (H + 2 * KVH) * D
+        a = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda")
+        w = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+        qkv = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        pos = torch.arange(M, dtype=torch.int32, device="cuda")
+        table = torch.arange(-(-M // 64), dtype=torch.int32, device="cuda").reshape(1, -1)
+        angles = torch.zeros(D // 2, M, 2, device="cuda")
+        kp = torch.zeros(table.numel(), KVH, 64, D, dtype=torch.bfloat16, device="cuda")
+        vp = torch.zeros(table.numel(), KVH, D, 64, dtype=torch.bfloat16, device="cuda")
+        assert not o.gemm_tcgen05_qkv_rope(a, w, qkv, pos, torch.zeros_like(pos), table, angles, kp, vp, H, KVH, D, 0, True)
+
+
 @pytest.mark.parametrize("M, N, K, spans", [(128, 128, 128, 2), (100, 300, 328, 4), (300, 1030, 2048, 2), (256, 2048, 8192, 4),
                                             (129, 130, 320, 4), (512, 2048, 8192, 0), (256, 1024, 4096, 0)])
 def test_gemm_tcgen05_with_k_cut_among_a_cluster(M, N, K, spans):

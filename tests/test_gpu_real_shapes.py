@@ -176,6 +176,8 @@ def test_replay_cuts_at_real_layer_sizes(sized, tmp_path, dtype, cut):
         assert {"gemm_tcgen05", "attention_prefill_tc"} <= ran, ran
         if cut != "whole":
             assert {"attention_decode_rope", "gemm_decode_linked"} <= ran, ran
+        else:   # the long prompts rotate and fill the cache in the projection's epilogue, the short ones in a kernel of its own
+            assert {"gemm_tcgen05_qkv_rope", "rope_angles", "rope_cache_write"} <= ran, ran
         hidden, inner = cfg["hidden_size"], cfg["intermediate_size"]
         rows_of_passes = [sum(len(e["tokens"]) for e in s["entries"]) for s in steps]
         if cut == "tail32":     # prompts of 13 to 1,568 tokens alone: some of them are few tiles with a long K
