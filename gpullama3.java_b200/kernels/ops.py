@@ -447,7 +447,8 @@ def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int
 
 
 def resident_ctas(device) -> int:
-    """How many CTAs of the decode attention kernel the GPU holds at once (four per SM)."""
+    """The number of CTAs the spans of decode attention are planned for: four per SM, which is what the kernel
+    for heads of 64 holds at once.  (Heads of 128 hold two; planning for two or three changed no step time.)"""
     return 4 * _sm_count(torch.device(device))
 
 
