@@ -17,6 +17,8 @@
 // Roles (320 threads): warp 0 lane 0 issues TMA; warp 1 lane 0 issues MMAs (warp 1 owns the 256 TMEM
 // columns: S 128, O head_dim); warps 2-9 are the softmax (two threads per query row) and the epilogue.  Every mbarrier wait is bounded;
 // a wait that gives up sets a status word and all roles fall through to the common exit.
+#include <type_traits>
+
 #include "tcgen05.cuh"
 
 namespace b200 {
@@ -358,8 +360,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 // 2 x 128 of S, 2 x 64 of O, 2 x 64 of P; shared memory: Q 32 KB, four stages of K and V 128 KB).
 // stages of K and V: what fits beside the two Q tiles (head_dim 64: 32 KB + 4 x 32 KB; 128: 64 KB + 2 x 64 KB)
 template <int D> struct PairStages { static constexpr int value = D == 64 ? 4 : 2; };
-constexpr int kPairThreads = 352;                       // TMA warp, MMA warp of tile 0, eight softmax warps, MMA warp of tile 1
-constexpr int kPairMmaWarp1 = kPairThreads / 32 - 1;
+// Three warpgroups: the softmax warps of tile 0, those of tile 1, and the warps that only issue (TMA, one MMA warp per
+// tile, one idle).  The issuing warpgroup hands most of its registers back and the two softmax warpgroups take them
+// (setmaxnreg): a softmax thread holds its row's 128 scores and wants more than the 168 registers an even split gives.
+constexpr int kPairThreads = 384;
+constexpr int kPairTmaWarp = 8, kPairMmaWarp0 = 9, kPairMmaWarp1 = 10;
+constexpr int kPairRegsIssuers = 56, kPairRegsSoftmax = 224;   // 128 x 56 + 256 x 224 = 64,512 of the SM's 65,536
 
 template <int D>
 struct PairSmem {
@@ -473,7 +479,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
-    if (warp == 1) {
+    if (warp == kPairMmaWarp0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -490,7 +496,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     // The exponentials of a block keep the special-function units busy; reading S, the maximum and the hand-over
     // do not.  So the two tiles' softmax threads alternate: a tile computes its exponentials only while it holds
     // the turn, and the other tile's remaining work runs meanwhile.  Tile 0 has the first turn.
-    if (warp >= 6 && warp < 10 && lane == 0) mbar_arrive_fa(&sm.exp_turn[0]);
+    if (warp >= 4 && warp < 8 && lane == 0) mbar_arrive_fa(&sm.exp_turn[0]);
 
     // The CTA stays and takes one unit of work after another from a counter: a unit is (pair of tiles, head,
     // sequence), the pairs with the most keys first, so that the SMs finish together.  The barriers are never
@@ -502,296 +508,308 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
     int tile_blocks[2] = {0, 0};   // phases of s_full[t], s_free[t], p_full[t] and pv_done[t]
     int kv_ready = 0;  // MMA threads: blocks (counted over all units) whose K and V this thread knows to have landed
 
-    for (;;) {
-        __syncthreads();  // the unit before is finished everywhere: tensor memory, Q and the unit number are free
-        if (threadIdx.x == 0) sm.unit = (int)atomicAdd(&g_pair_ctl[counter], 1u);
-        __syncthreads();
-        const int unit = sm.unit;
-        if (unit >= total_units || *abort_flag) break;
-        const int pair = n_pairs - 1 - unit / (n_heads * n_seqs);
-        const int seq = (unit % (n_heads * n_seqs)) / n_heads, head = unit % n_heads;
-        const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
-        const int q0 = pair * 2 * kFaRows;
-        if (q0 >= q_len) continue;  // this sequence has no such rows
-        const int kvh = head / (n_heads / n_kv_heads);
-        const int kv_len = kv_lens[seq], start = kv_len - q_len;
-        // tile t: rows q0 + 128 t .. ; its key blocks are 0 .. nb[t] - 1 (causal), nb[1] = 0 when the tile has no rows
-        const int rows0 = min(kFaRows, q_len - q0), rows1 = max(0, min(kFaRows, q_len - q0 - kFaRows));
-        const int nb0 = (start + q0 + rows0 - 1) / kFaKeys + 1;
-        const int nb1 = rows1 > 0 ? (start + q0 + kFaRows + rows1 - 1) / kFaKeys + 1 : 0;
-        const int nb = max(nb0, nb1);
+    // The unit loop exists twice, once for the softmax warpgroups and once for the issuing warpgroup, each behind its own
+    // register reallocation: the compiler then gives each copy the registers its warps really have.
+    auto run_units = [&](auto role) {
+        constexpr int ROLE = decltype(role)::value;   // 1: softmax warps, 0: TMA and MMA warps (and the idle one)
+        for (;;) {
+            __syncthreads();  // the unit before is finished everywhere: tensor memory, Q and the unit number are free
+            if (threadIdx.x == 0) sm.unit = (int)atomicAdd(&g_pair_ctl[counter], 1u);
+            __syncthreads();
+            const int unit = sm.unit;
+            if (unit >= total_units || *abort_flag) break;
+            const int pair = n_pairs - 1 - unit / (n_heads * n_seqs);
+            const int seq = (unit % (n_heads * n_seqs)) / n_heads, head = unit % n_heads;
+            const int tok0 = cu_seqlens[seq], q_len = cu_seqlens[seq + 1] - tok0;
+            const int q0 = pair * 2 * kFaRows;
+            if (q0 >= q_len) continue;  // this sequence has no such rows
+            const int kvh = head / (n_heads / n_kv_heads);
+            const int kv_len = kv_lens[seq], start = kv_len - q_len;
+            // tile t: rows q0 + 128 t .. ; its key blocks are 0 .. nb[t] - 1 (causal), nb[1] = 0 when the tile has no rows
+            const int rows0 = min(kFaRows, q_len - q0), rows1 = max(0, min(kFaRows, q_len - q0 - kFaRows));
+            const int nb0 = (start + q0 + rows0 - 1) / kFaKeys + 1;
+            const int nb1 = rows1 > 0 ? (start + q0 + kFaRows + rows1 - 1) / kFaKeys + 1 : 0;
+            const int nb = max(nb0, nb1);
 
-        if (warp == 0 && lane == 0) {
-            // ---- producer: both Q tiles, then per block two K pages and two V^T pages
-            const int* pages = page_table + (size_t)seq * table_stride;
-            const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
-            mbar_expect_tx(&sm.q_full, (rows1 > 0 ? 2 : 1) * kFaRows * D * 2);
-#pragma unroll
-            for (int a = 0; a < kAtoms; ++a) {  // an operand tile is stored as atoms of 64 dims (one swizzle span)
-                tma_load_2d(sm.q[0] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0, &sm.q_full);
-                if (rows1 > 0) tma_load_2d(sm.q[1] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0 + kFaRows, &sm.q_full);
-            }
-            for (int j = 0; j < nb; ++j) {
-                const int g = kv_base + j, s = g % PairStages<D>::value;
-                if (g >= PairStages<D>::value && !mbar_wait(&sm.kv_empty[s], ((g / PairStages<D>::value) - 1) & 1, abort_flag)) {
-                    *abort_flag = 1; atomicCAS(&g_fa_status, 0, (11 << 8) | s); break;
+            if (ROLE == 0 && warp == kPairTmaWarp && lane == 0) {
+                // ---- producer: both Q tiles, then per block two K pages and two V^T pages
+                const int* pages = page_table + (size_t)seq * table_stride;
+                const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
+                mbar_expect_tx(&sm.q_full, (rows1 > 0 ? 2 : 1) * kFaRows * D * 2);
+    #pragma unroll
+                for (int a = 0; a < kAtoms; ++a) {  // an operand tile is stored as atoms of 64 dims (one swizzle span)
+                    tma_load_2d(sm.q[0] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0, &sm.q_full);
+                    if (rows1 > 0) tma_load_2d(sm.q[1] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0 + kFaRows, &sm.q_full);
                 }
-                mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int lp = j * 2 + h;  // logical page; pages the sequence does not have are read as zeros
-                    const bool have = lp < n_pages_seq;
-                    const int page = have ? pages[lp] : 0;
-#pragma unroll
-                    for (int a = 0; a < kAtoms; ++a)
-                        tma_load_2d(sm.k[s] + a * kFaKeys * 64 + h * 64 * 64, &map_k, a * 64,
-                                    have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
-                    tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
-                }
-            }
-        } else if ((warp == 1 || warp == kPairMmaWarp1) && lane == 0) {
-            // ---- MMA issuers, one thread per tile (t = 0: warp 1, t = 1: the last warp).  A tile's next scores
-            // S(i+1) only need its S columns free, which its softmax threads report as soon as they hold block
-            // i's scores in registers (s_free); its outputs O += P(i) V(i) need the probabilities (p_full).  So
-            // per block the thread issues S(i+1), then PV(i): the tensor cores form the next scores while the
-            // softmax of the current ones runs, and the two tiles' threads keep the pipe fed between them.
-            const int t = warp == 1 ? 0 : 1;
-            const int nbt = t == 0 ? nb0 : nb1, nb_other = t == 0 ? nb1 : nb0;
-            constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
-            constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, D);
-            bool ok = nbt > 0;
-            kv_ready = max(kv_ready, kv_base);  // blocks of earlier units this tile never read are not waited for now
-            if (ok && !mbar_wait(&sm.q_full, units_done & 1, abort_flag)) {
-                *abort_flag = 1; atomicCAS(&g_fa_status, 0, 12 << 8); ok = false;
-            }
-            auto need_block = [&](int j) {
-                while (ok && kv_ready <= kv_base + j) {
-                    const int s = kv_ready % PairStages<D>::value;
-                    if (!mbar_wait(&sm.kv_full[s], (kv_ready / PairStages<D>::value) & 1, abort_flag)) {
-                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (13 << 8) | s); ok = false;
-                    } else {
-                        ++kv_ready;
+                for (int j = 0; j < nb; ++j) {
+                    const int g = kv_base + j, s = g % PairStages<D>::value;
+                    if (g >= PairStages<D>::value && !mbar_wait(&sm.kv_empty[s], ((g / PairStages<D>::value) - 1) & 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (11 << 8) | s); break;
+                    }
+                    mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
+    #pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int lp = j * 2 + h;  // logical page; pages the sequence does not have are read as zeros
+                        const bool have = lp < n_pages_seq;
+                        const int page = have ? pages[lp] : 0;
+    #pragma unroll
+                        for (int a = 0; a < kAtoms; ++a)
+                            tma_load_2d(sm.k[s] + a * kFaKeys * 64 + h * 64 * 64, &map_k, a * 64,
+                                        have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
+                        tma_load_2d(sm.v[s][h], &map_v, 0, have ? (page * n_kv_heads + kvh) * D : v_rows_total, &sm.kv_full[s]);
                     }
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            };
-            // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
-            auto scores = [&](int j) {  // S = Q K_j^T
-                const __nv_bfloat16* kt = sm.k[(kv_base + j) % PairStages<D>::value];
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    umma_bf16(tmem + 128 * t, umma_desc(sm.q[t] + (kk / 4) * kFaRows * 64) + 2 * (kk % 4),
-                              umma_desc(kt + (kk / 4) * kFaKeys * 64) + 2 * (kk % 4), idesc_s, kk != 0);
-                umma_commit(&sm.s_full[t]);
-            };
-            if (ok) {
-                need_block(0);
-                if (ok) scores(0);
-            }
-            for (int i = 0; i < nbt && ok; ++i) {
-                if (kEarlyScores && i + 1 < nbt) {
-                    if (!mbar_wait(&sm.s_free[t], (tile_blocks[t] + i) & 1, abort_flag)) {
-                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (17 << 8) | t); ok = false; break;
+            } else if (ROLE == 0 && (warp == kPairMmaWarp0 || warp == kPairMmaWarp1) && lane == 0) {
+                // ---- MMA issuers, one thread per tile.  A tile's next scores
+                // S(i+1) only need its S columns free, which its softmax threads report as soon as they hold block
+                // i's scores in registers (s_free); its outputs O += P(i) V(i) need the probabilities (p_full).  So
+                // per block the thread issues S(i+1), then PV(i): the tensor cores form the next scores while the
+                // softmax of the current ones runs, and the two tiles' threads keep the pipe fed between them.
+                const int t = warp == kPairMmaWarp0 ? 0 : 1;
+                const int nbt = t == 0 ? nb0 : nb1, nb_other = t == 0 ? nb1 : nb0;
+                constexpr uint32_t idesc_s = umma_idesc_bf16(kFaRows, kFaKeys);
+                constexpr uint32_t idesc_o = umma_idesc_bf16(kFaRows, D);
+                bool ok = nbt > 0;
+                kv_ready = max(kv_ready, kv_base);  // blocks of earlier units this tile never read are not waited for now
+                if (ok && !mbar_wait(&sm.q_full, units_done & 1, abort_flag)) {
+                    *abort_flag = 1; atomicCAS(&g_fa_status, 0, 12 << 8); ok = false;
+                }
+                auto need_block = [&](int j) {
+                    while (ok && kv_ready <= kv_base + j) {
+                        const int s = kv_ready % PairStages<D>::value;
+                        if (!mbar_wait(&sm.kv_full[s], (kv_ready / PairStages<D>::value) & 1, abort_flag)) {
+                            *abort_flag = 1; atomicCAS(&g_fa_status, 0, (13 << 8) | s); ok = false;
+                        } else {
+                            ++kv_ready;
+                        }
                     }
-                    need_block(i + 1);
-                    if (!ok) break;
-                    scores(i + 1);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                };
+                // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
+                auto scores = [&](int j) {  // S = Q K_j^T
+                    const __nv_bfloat16* kt = sm.k[(kv_base + j) % PairStages<D>::value];
+    #pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)
+                        umma_bf16(tmem + 128 * t, umma_desc(sm.q[t] + (kk / 4) * kFaRows * 64) + 2 * (kk % 4),
+                                  umma_desc(kt + (kk / 4) * kFaKeys * 64) + 2 * (kk % 4), idesc_s, kk != 0);
+                    umma_commit(&sm.s_full[t]);
+                };
+                if (ok) {
+                    need_block(0);
+                    if (ok) scores(0);
                 }
-                if (!mbar_wait(&sm.p_full[t], (tile_blocks[t] + i) & 1, abort_flag)) {
-                    *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; break;
+                for (int i = 0; i < nbt && ok; ++i) {
+                    if (kEarlyScores && i + 1 < nbt) {
+                        if (!mbar_wait(&sm.s_free[t], (tile_blocks[t] + i) & 1, abort_flag)) {
+                            *abort_flag = 1; atomicCAS(&g_fa_status, 0, (17 << 8) | t); ok = false; break;
+                        }
+                        need_block(i + 1);
+                        if (!ok) break;
+                        scores(i + 1);
+                    }
+                    if (!mbar_wait(&sm.p_full[t], (tile_blocks[t] + i) & 1, abort_flag)) {
+                        *abort_flag = 1; atomicCAS(&g_fa_status, 0, (14 << 8) | t); ok = false; break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int s = (kv_base + i) % PairStages<D>::value;
+                    const uint64_t vd0 = umma_desc(sm.v[s][0]), vd1 = umma_desc(sm.v[s][1]);
+    #pragma unroll
+                    for (int kk = 0; kk < kFaKeys / 16; ++kk)  // O += P V_i; 16 keys = 8 columns of P
+                        umma_bf16_a_tmem(tmem + 256 + D * t, tmem + (D == 64 ? 384 + 64 * t : 128 * t) + 8 * kk,
+                                         (kk < 4 ? vd0 : vd1) + 2 * (kk % 4), idesc_o, (i | kk) != 0);
+                    umma_commit(&sm.pv_done[t]);
+                    if (!kEarlyScores && i + 1 < nbt) {  // P lies where the next scores go: they follow the product that reads it
+                        need_block(i + 1);
+                        if (!ok) break;
+                        scores(i + 1);
+                    }
+                    // a stage is free after two arrivals: one from each tile that reads the block, two from a lone reader
+                    umma_commit(&sm.kv_empty[s]);
+                    if (i >= nb_other) umma_commit(&sm.kv_empty[s]);
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int s = (kv_base + i) % PairStages<D>::value;
-                const uint64_t vd0 = umma_desc(sm.v[s][0]), vd1 = umma_desc(sm.v[s][1]);
-#pragma unroll
-                for (int kk = 0; kk < kFaKeys / 16; ++kk)  // O += P V_i; 16 keys = 8 columns of P
-                    umma_bf16_a_tmem(tmem + 256 + D * t, tmem + (D == 64 ? 384 + 64 * t : 128 * t) + 8 * kk,
-                                     (kk < 4 ? vd0 : vd1) + 2 * (kk % 4), idesc_o, (i | kk) != 0);
-                umma_commit(&sm.pv_done[t]);
-                if (!kEarlyScores && i + 1 < nbt) {  // P lies where the next scores go: they follow the product that reads it
-                    need_block(i + 1);
-                    if (!ok) break;
-                    scores(i + 1);
-                }
-                // a stage is free after two arrivals: one from each tile that reads the block, two from a lone reader
-                umma_commit(&sm.kv_empty[s]);
-                if (i >= nb_other) umma_commit(&sm.kv_empty[s]);
-            }
-        } else if (warp >= 2 && warp < kPairMmaWarp1) {
-            // ---- softmax and epilogue: warpgroup t = (warp - 2) / 4 serves tile t, thread = query row = TMEM lane
-            const int t = (warp - 2) >> 2, quarter = warp & 3;
-            const int r = quarter * 32 + lane;
-            const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-            const int rows_t = t == 0 ? rows0 : rows1, nbt = t == 0 ? nb0 : nb1;
-            const int p_first = start + q0 + kFaRows * t;
-            const int pos = p_first + min(r, max(rows_t, 1) - 1);  // rows past the end mirror the last one (never stored)
-            const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);
-            const uint32_t tmem_s = tmem + 128 * t, tmem_o = tmem + 256 + D * t, tmem_p = D == 64 ? tmem + 384 + 64 * t : tmem_s;
-            float m_ref = -INFINITY, l = 0.f;
-            bool ok = true;
-            for (int j = 0; j < nbt; ++j) {
-                ok = mbar_wait(&sm.s_full[t], (tile_blocks[t] + j) & 1, abort_flag);
-                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (15 << 8) | (t * 4 + quarter)); }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t sr[4][32];  // this row's 128 scores
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + lane_base + c * 32, sr[c]);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tie32(sr[c]);
-                // the scores are in registers: the next block's scores may be formed
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive_fa(&sm.s_free[t]);
-                const int base = j * kFaKeys;
-                const bool masked = base + kFaKeys - 1 > p_first;  // the block reaches beyond the tile's first row
-                float m_blk = -INFINITY;
-                if (masked) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (base + c * 32 + i <= pos) m_blk = fmaxf(m_blk, __uint_as_float(sr[c][i]));
-                } else {
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
-                    m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-                }
-                // the block before must have left P and O alone before either is touched (it has, long ago, as a rule)
-                if (j > 0) {
-                    ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + j - 1) & 1, abort_flag);
-                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (18 << 8) | (t * 4 + quarter)); }
+            } else if (ROLE == 1) {
+                // ---- softmax and epilogue: warpgroup t = warp / 4 serves tile t, thread = query row = TMEM lane
+                const int t = warp >> 2, quarter = warp & 3;
+                const int r = quarter * 32 + lane;
+                const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+                const int rows_t = t == 0 ? rows0 : rows1, nbt = t == 0 ? nb0 : nb1;
+                const int p_first = start + q0 + kFaRows * t;
+                const int pos = p_first + min(r, max(rows_t, 1) - 1);  // rows past the end mirror the last one (never stored)
+                const float scale_log2 = 1.4426950408889634f / sqrtf((float)D);
+                const uint32_t tmem_s = tmem + 128 * t, tmem_o = tmem + 256 + D * t, tmem_p = D == 64 ? tmem + 384 + 64 * t : tmem_s;
+                float m_ref = -INFINITY, l = 0.f;
+                bool ok = true;
+                for (int j = 0; j < nbt; ++j) {
+                    ok = mbar_wait(&sm.s_full[t], (tile_blocks[t] + j) & 1, abort_flag);
+                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (15 << 8) | (t * 4 + quarter)); }
                     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint32_t sr[4][32];  // this row's 128 scores
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + lane_base + c * 32, sr[c]);
+                    tmem_ld_wait();
+    #pragma unroll
+                    for (int c = 0; c < 4; ++c) tie32(sr[c]);
+                    // the scores are in registers: the next block's scores may be formed
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_fa(&sm.s_free[t]);
+                    const int base = j * kFaKeys;
+                    const bool masked = base + kFaKeys - 1 > p_first;  // the block reaches beyond the tile's first row
+                    float m_blk = -INFINITY;
+                    if (masked) {
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c)
+    #pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (base + c * 32 + i <= pos) m_blk = fmaxf(m_blk, __uint_as_float(sr[c][i]));
+                    } else {
+                        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c)
+    #pragma unroll
+                            for (int i = 0; i < 32; i += 2)
+                                m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+                        m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+                    }
+                    // the block before must have left P and O alone before either is touched (it has, long ago, as a rule)
+                    if (j > 0) {
+                        ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + j - 1) & 1, abort_flag);
+                        if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (18 << 8) | (t * 4 + quarter)); }
+                        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    }
+                    // the reference maximum moves only when the block exceeds it by more than 2^8 after scaling
+                    const bool move = m_blk > m_ref && (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > 8.f);
+                    if (__any_sync(0xffffffffu, move)) {
+                        const float m_new = move ? m_blk : m_ref;
+                        const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
+                        l *= corr;
+                        if (j > 0) {  // O holds earlier blocks: rescale this row (whole warps take part in the TMEM access)
+    #pragma unroll 1
+                            for (int c0 = 0; c0 < D; c0 += 32) {
+                                float o[32];
+                                tmem_ld32(tmem_o + lane_base + c0, o);
+    #pragma unroll
+                                for (int i = 0; i < 32; ++i) o[i] *= corr;
+                                tmem_st32(tmem_o + lane_base + c0, o);
+                            }
+                        }
+                        m_ref = m_new;
+                    }
+                    const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
+                    ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
+                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (19 << 8) | (t * 4 + quarter)); }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    // probabilities as bfloat16 pairs into this row's lane of P: key k of the block in column k / 2
+                    float l4[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (masked) {  // the few blocks on the diagonal: every key is compared with the row's position
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t pk[16];
+    #pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const int key = base + c * 32 + i;
+                                const float p0 = key <= pos ? ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled)) : 0.f;
+                                const float p1 = key + 1 <= pos ? ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, -m_scaled)) : 0.f;
+                                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                                l4[c] += p0 + p1;
+                                pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            tmem_st16(tmem_p + lane_base + 16 * c, pk);
+                        }
+                    } else {       // two keys per multiply-add and per addition
+                        const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-m_scaled, -m_scaled);
+    #pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t pk[16];
+                            unsigned long long sum2 = pack2(0.f, 0.f);
+    #pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float x0, x1;
+                                unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, shift2), x0, x1);
+                                const float p0 = ex2(x0), p1 = ex2(x1);
+                                __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                                sum2 = add2(sum2, pack2(p0, p1));
+                                pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            float s0, s1;
+                            unpack2(sum2, s0, s1);
+                            l4[c] = s0 + s1;
+                            tmem_st16(tmem_p + lane_base + 16 * c, pk);
+                        }
+                    }
+                    l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);  // the other tile's turn
+                    if ((j + 1) * kFaKeys > kv_len) {  // the block holds the sequence's end: see zero_values_beyond_end
+                        const int g = kv_base + j, s = g % PairStages<D>::value;  // (both tiles may do this: they write the same zeros)
+                        if (mbar_wait(&sm.kv_full[s], (g / PairStages<D>::value) & 1, abort_flag))
+                            zero_values_beyond_end<D>(sm.v[s][0], sm.v[s][1], kv_len - j * kFaKeys, quarter * 32 + lane, 128);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    }
+                    // P is in tensor memory and S has been read: the MMA thread may go on
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_fa(&sm.p_full[t]);
                 }
-                // the reference maximum moves only when the block exceeds it by more than 2^8 after scaling
-                const bool move = m_blk > m_ref && (m_ref == -INFINITY || (m_blk - m_ref) * scale_log2 > 8.f);
-                if (__any_sync(0xffffffffu, move)) {
-                    const float m_new = move ? m_blk : m_ref;
-                    const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
-                    l *= corr;
-                    if (j > 0) {  // O holds earlier blocks: rescale this row (whole warps take part in the TMEM access)
-#pragma unroll 1
+                for (int j = nbt; j < nb && ok; ++j) {  // rounds in which only the other tile has a block: pass the turn on
+                    ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
+                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (20 << 8) | (t * 4 + quarter)); }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    __syncwarp();
+                    if (ok && lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);
+                }
+                if (ok && nbt > 0) {
+                    ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + nbt - 1) & 1, abort_flag);
+                    if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (16 << 8) | (t * 4 + quarter)); }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (ok) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const float inv_l = 1.0f / l;
+                        __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + kFaRows * t + r) * n_heads + head) * D;
+    #pragma unroll 1
                         for (int c0 = 0; c0 < D; c0 += 32) {
                             float o[32];
                             tmem_ld32(tmem_o + lane_base + c0, o);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] *= corr;
-                            tmem_st32(tmem_o + lane_base + c0, o);
-                        }
-                    }
-                    m_ref = m_new;
-                }
-                const float m_scaled = m_ref == -INFINITY ? 0.f : m_ref * scale_log2;
-                ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
-                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (19 << 8) | (t * 4 + quarter)); }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
-                // probabilities as bfloat16 pairs into this row's lane of P: key k of the block in column k / 2
-                float l4[4] = {0.f, 0.f, 0.f, 0.f};
-                if (masked) {  // the few blocks on the diagonal: every key is compared with the row's position
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const int key = base + c * 32 + i;
-                            const float p0 = key <= pos ? ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled)) : 0.f;
-                            const float p1 = key + 1 <= pos ? ex2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, -m_scaled)) : 0.f;
-                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            l4[c] += p0 + p1;
-                            pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                        tmem_st16(tmem_p + lane_base + 16 * c, pk);
-                    }
-                } else {       // two keys per multiply-add and per addition
-                    const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-m_scaled, -m_scaled);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t pk[16];
-                        unsigned long long sum2 = pack2(0.f, 0.f);
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float x0, x1;
-                            unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, shift2), x0, x1);
-                            const float p0 = ex2(x0), p1 = ex2(x1);
-                            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                            sum2 = add2(sum2, pack2(p0, p1));
-                            pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                        float s0, s1;
-                        unpack2(sum2, s0, s1);
-                        l4[c] = s0 + s1;
-                        tmem_st16(tmem_p + lane_base + 16 * c, pk);
-                    }
-                }
-                l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-                __syncwarp();
-                if (lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);  // the other tile's turn
-                if ((j + 1) * kFaKeys > kv_len) {  // the block holds the sequence's end: see zero_values_beyond_end
-                    const int g = kv_base + j, s = g % PairStages<D>::value;  // (both tiles may do this: they write the same zeros)
-                    if (mbar_wait(&sm.kv_full[s], (g / PairStages<D>::value) & 1, abort_flag))
-                        zero_values_beyond_end<D>(sm.v[s][0], sm.v[s][1], kv_len - j * kFaKeys, quarter * 32 + lane, 128);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
-                // P is in tensor memory and S has been read: the MMA thread may go on
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive_fa(&sm.p_full[t]);
-            }
-            for (int j = nbt; j < nb && ok; ++j) {  // rounds in which only the other tile has a block: pass the turn on
-                ok = mbar_wait(&sm.exp_turn[t], (kv_base + j) & 1, abort_flag);
-                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (20 << 8) | (t * 4 + quarter)); }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                __syncwarp();
-                if (ok && lane == 0) mbar_arrive_fa(&sm.exp_turn[1 - t]);
-            }
-            if (ok && nbt > 0) {
-                ok = mbar_wait(&sm.pv_done[t], (tile_blocks[t] + nbt - 1) & 1, abort_flag);
-                if (!ok && lane == 0) { *abort_flag = 1; atomicCAS(&g_fa_status, 0, (16 << 8) | (t * 4 + quarter)); }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (ok) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const float inv_l = 1.0f / l;
-                    __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + kFaRows * t + r) * n_heads + head) * D;
-#pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        float o[32];
-                        tmem_ld32(tmem_o + lane_base + c0, o);
-                        if (r < rows_t) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * i] * inv_l, o[8 * i + 1] * inv_l);
-                                __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
-                                __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
-                                __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
-                                *reinterpret_cast<uint4*>(orow + c0 + 8 * i) =
-                                    make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
-                                               *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                            if (r < rows_t) {
+    #pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * i] * inv_l, o[8 * i + 1] * inv_l);
+                                    __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
+                                    __nv_bfloat162 c = __floats2bfloat162_rn(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
+                                    __nv_bfloat162 d = __floats2bfloat162_rn(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
+                                    *reinterpret_cast<uint4*>(orow + c0 + 8 * i) =
+                                        make_uint4(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b),
+                                                   *reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+                                }
                             }
                         }
                     }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            // the same bookkeeping in every thread
+            ++units_done;
+            kv_base += nb;
+            tile_blocks[0] += nb0;
+            tile_blocks[1] += nb1;
         }
-        // the same bookkeeping in every thread
-        ++units_done;
-        kv_base += nb;
-        tile_blocks[0] += nb0;
-        tile_blocks[1] += nb1;
+    };
+    if (warp < 8) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kPairRegsSoftmax));
+        run_units(std::integral_constant<int, 1>{});
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kPairRegsIssuers));
+        run_units(std::integral_constant<int, 0>{});
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kPairMmaWarp0) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(512) : "memory");
     }
