@@ -536,7 +536,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 const int* pages = page_table + (size_t)seq * table_stride;
                 const int n_pages_seq = (kv_len + kPageTokens - 1) / kPageTokens;
                 mbar_expect_tx(&sm.q_full, (rows1 > 0 ? 2 : 1) * kFaRows * D * 2);
-    #pragma unroll
+#pragma unroll
                 for (int a = 0; a < kAtoms; ++a) {  // an operand tile is stored as atoms of 64 dims (one swizzle span)
                     tma_load_2d(sm.q[0] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0, &sm.q_full);
                     if (rows1 > 0) tma_load_2d(sm.q[1] + a * kFaRows * 64, &map_q, head * D + a * 64, tok0 + q0 + kFaRows, &sm.q_full);
@@ -547,12 +547,12 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                         *abort_flag = 1; atomicCAS(&g_fa_status, 0, (11 << 8) | s); break;
                     }
                     mbar_expect_tx(&sm.kv_full[s], 2 * (64 * D * 2) + 2 * (D * 64 * 2));
-    #pragma unroll
+#pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int lp = j * 2 + h;  // logical page; pages the sequence does not have are read as zeros
                         const bool have = lp < n_pages_seq;
                         const int page = have ? pages[lp] : 0;
-    #pragma unroll
+#pragma unroll
                         for (int a = 0; a < kAtoms; ++a)
                             tma_load_2d(sm.k[s] + a * kFaKeys * 64 + h * 64 * 64, &map_k, a * 64,
                                         have ? (page * n_kv_heads + kvh) * 64 : k_rows_total, &sm.kv_full[s]);
@@ -588,7 +588,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                 // operand descriptors; a 16-element step along K adds 2 (32 bytes) to the start address field
                 auto scores = [&](int j) {  // S = Q K_j^T
                     const __nv_bfloat16* kt = sm.k[(kv_base + j) % PairStages<D>::value];
-    #pragma unroll
+#pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk)
                         umma_bf16(tmem + 128 * t, umma_desc(sm.q[t] + (kk / 4) * kFaRows * 64) + 2 * (kk % 4),
                                   umma_desc(kt + (kk / 4) * kFaKeys * 64) + 2 * (kk % 4), idesc_s, kk != 0);
@@ -613,7 +613,7 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const int s = (kv_base + i) % PairStages<D>::value;
                     const uint64_t vd0 = umma_desc(sm.v[s][0]), vd1 = umma_desc(sm.v[s][1]);
-    #pragma unroll
+#pragma unroll
                     for (int kk = 0; kk < kFaKeys / 16; ++kk)  // O += P V_i; 16 keys = 8 columns of P
                         umma_bf16_a_tmem(tmem + 256 + D * t, tmem + (D == 64 ? 384 + 64 * t : 128 * t) + 8 * kk,
                                          (kk < 4 ? vd0 : vd1) + 2 * (kk % 4), idesc_o, (i | kk) != 0);
@@ -646,10 +646,10 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t sr[4][32];  // this row's 128 scores
-    #pragma unroll
+#pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld32_issue(tmem_s + lane_base + c * 32, sr[c]);
                     tmem_ld_wait();
-    #pragma unroll
+#pragma unroll
                     for (int c = 0; c < 4; ++c) tie32(sr[c]);
                     // the scores are in registers: the next block's scores may be formed
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -659,16 +659,16 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     const bool masked = base + kFaKeys - 1 > p_first;  // the block reaches beyond the tile's first row
                     float m_blk = -INFINITY;
                     if (masked) {
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 4; ++c)
-    #pragma unroll
+#pragma unroll
                             for (int i = 0; i < 32; ++i)
                                 if (base + c * 32 + i <= pos) m_blk = fmaxf(m_blk, __uint_as_float(sr[c][i]));
                     } else {
                         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 4; ++c)
-    #pragma unroll
+#pragma unroll
                             for (int i = 0; i < 32; i += 2)
                                 m4[c] = max3(m4[c], __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
                         m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
@@ -688,11 +688,11 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                         const float corr = (m_ref == -INFINITY) ? 0.f : ex2((m_ref - m_new) * scale_log2);
                         l *= corr;
                         if (j > 0) {  // O holds earlier blocks: rescale this row (whole warps take part in the TMEM access)
-    #pragma unroll 1
+#pragma unroll 1
                             for (int c0 = 0; c0 < D; c0 += 32) {
                                 float o[32];
                                 tmem_ld32(tmem_o + lane_base + c0, o);
-    #pragma unroll
+#pragma unroll
                                 for (int i = 0; i < 32; ++i) o[i] *= corr;
                                 tmem_st32(tmem_o + lane_base + c0, o);
                             }
@@ -707,10 +707,10 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                     // probabilities as bfloat16 pairs into this row's lane of P: key k of the block in column k / 2
                     float l4[4] = {0.f, 0.f, 0.f, 0.f};
                     if (masked) {  // the few blocks on the diagonal: every key is compared with the row's position
-    #pragma unroll
+#pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             uint32_t pk[16];
-    #pragma unroll
+#pragma unroll
                             for (int i = 0; i < 32; i += 2) {
                                 const int key = base + c * 32 + i;
                                 const float p0 = key <= pos ? ex2(fmaf(__uint_as_float(sr[c][i]), scale_log2, -m_scaled)) : 0.f;
@@ -723,15 +723,35 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                         }
                     } else {       // two keys per multiply-add and per addition
                         const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-m_scaled, -m_scaled);
-    #pragma unroll
+                        // Every other pair of keys gets its powers of two from a cubic on the multiply-add pipe instead
+                        // of the special-function unit, which would otherwise bound the block: 2^x = 2^n * 2^f with
+                        // n = round(x) (taken from the bits of x + 1.5 * 2^23) and f = x - n in [-0.5, 0.5]; the cubic is
+                        // within 1.5e-4 of 2^f, a thirtieth of what rounding the probability to bfloat16 loses.
+                        const unsigned long long magic2 = pack2(12582912.f, 12582912.f), unmagic2 = pack2(-12582912.f, -12582912.f);
+                        const unsigned long long minus1 = pack2(-1.f, -1.f);
+                        const unsigned long long k0 = pack2(0.9999280571937561f, 0.9999280571937561f), k1 = pack2(0.6932609677314758f, 0.6932609677314758f);
+                        const unsigned long long k2 = pack2(0.2426111251115799f, 0.2426111251115799f), k3 = pack2(0.05517162010073662f, 0.05517162010073662f);
+#pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             uint32_t pk[16];
                             unsigned long long sum2 = pack2(0.f, 0.f);
-    #pragma unroll
+#pragma unroll
                             for (int i = 0; i < 32; i += 2) {
-                                float x0, x1;
+                                float x0, x1, p0, p1;
                                 unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), scale2, shift2), x0, x1);
-                                const float p0 = ex2(x0), p1 = ex2(x1);
+                                if (D != 64 || (i & 6) != 2) {
+                                    p0 = ex2(x0);
+                                    p1 = ex2(x1);
+                                } else {
+                                    const unsigned long long xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+                                    const unsigned long long tt = add2(xc, magic2);
+                                    const unsigned long long f = fma2(add2(tt, unmagic2), minus1, xc);
+                                    float q0, q1, t0, t1;
+                                    unpack2(fma2(fma2(fma2(k3, f, k2), f, k1), f, k0), q0, q1);
+                                    unpack2(tt, t0, t1);
+                                    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+                                    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+                                }
                                 __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                                 sum2 = add2(sum2, pack2(p0, p1));
                                 pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
@@ -772,12 +792,12 @@ attention_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const float inv_l = 1.0f / l;
                         __nv_bfloat16* orow = out + ((size_t)(tok0 + q0 + kFaRows * t + r) * n_heads + head) * D;
-    #pragma unroll 1
+#pragma unroll 1
                         for (int c0 = 0; c0 < D; c0 += 32) {
                             float o[32];
                             tmem_ld32(tmem_o + lane_base + c0, o);
                             if (r < rows_t) {
-    #pragma unroll
+#pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     __nv_bfloat162 a = __floats2bfloat162_rn(o[8 * i] * inv_l, o[8 * i + 1] * inv_l);
                                     __nv_bfloat162 b = __floats2bfloat162_rn(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
