@@ -63,6 +63,11 @@ class CausalLM:
         """Whether a decode step of this model may be recorded once and replayed as a CUDA graph."""
         return all(p.graph_safe for p in self.named_parts().values()) and all(b.graph_safe for b in self.blocks)
 
+    @property
+    def pad_safe(self) -> bool:
+        """Whether a short prompt may run as a recorded pass padded with tokens that are never committed."""
+        return all(p.pad_safe for p in self.named_parts().values()) and all(getattr(b, "pad_safe", False) for b in self.blocks)
+
     def cache_needs(self) -> dict[int, object]:
         """Cache entry id -> the need (KVCacheNeed, StateNeed, or a type of the mixer's own) of the runs that use it."""
         return dict(self._cache_needs)

@@ -223,6 +223,72 @@ class DecodeGraph:
         return self.tokens_host.tolist()
 
 
+class PromptGraph:
+    """One recorded prompt pass of a single sequence: ``n_tokens`` tokens (a whole number of pages' worth), fixed
+    page-table widths, a fixed number of wanted places.
+
+    A prompt of a few hundred tokens is a hundred-odd launches that the GPU finishes sooner than the host can issue
+    them; recorded once per size and replayed, the pass costs the host one copy and one launch.  A prompt is padded
+    with token 0 up to the end of its last page: the padding runs as ordinary tokens of the pass (causal attention
+    keeps it away from the real ones), writes keys and values into the part of that page no position has claimed
+    yet, and is never committed to the cache, so later tokens overwrite it before anything reads it.  Only models
+    whose parts all say ``pad_safe`` and ``graph_safe`` are run this way.  As in a recorded decode step, everything
+    that changes from pass to pass lives in one device buffer refreshed by a single copy."""
+
+    def __init__(self, model, cache: SequenceCache, n_tokens: int, widths: list[int], n_wanted: int):
+        self.model, self.cache, self.n_tokens, self.widths, self.n_wanted = model, cache, n_tokens, list(widths), n_wanted
+        self.sizes = [n_tokens, n_tokens, n_tokens, 2, 1, 1, n_wanted] + list(widths)
+        self.table_shapes = [(1, w) for w in widths]
+        total = sum(self.sizes)
+        self.host = torch.empty(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.empty(total, dtype=torch.int32, device=model.device)
+        self.done = torch.cuda.Event()
+        self.pending = False
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.logits: torch.Tensor | None = None
+        self.n_launches = 0
+        self.h2d_bytes = total * 4
+
+    def _launches(self, slot: int, start: int):
+        self.dev.copy_(self.host, non_blocking=True)
+        ctx, rows = _context_over(self.dev, self.sizes, self.table_shapes, self.model.dtype, self.model.device, [slot],
+                                  [start], [self.n_tokens])
+        return self.model.forward(ctx, self.cache, rows if self.n_wanted else None)
+
+    def run(self, slot: int, start: int, tokens: list[int], rows: list[int]) -> tuple[torch.Tensor | None, bool]:
+        """Logits at ``rows`` (None when none are wanted) and whether the pass was replayed."""
+        from ..kernels import ops
+
+        if self.pending:
+            self.done.synchronize()  # the run before must have read the staging buffer
+            self.pending = False
+        padded = list(tokens) + [0] * (self.n_tokens - len(tokens))
+        pieces, _, _ = _pack(self.cache, [slot], [start], [padded], rows, self.widths)
+        np.concatenate(pieces, out=self.host_np)
+        if self.graph is None:
+            out = self._launches(slot, start)   # the first pass of this size runs as ordinary launches, then is recorded
+            torch.cuda.synchronize()
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            import gc
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = self._launches(slot, start)
+            finally:
+                if gc_was_on:
+                    gc.enable()
+            self.n_launches = ops.launch_count() - before
+            self.graph = graph
+            return out, False
+        self.graph.replay()
+        self.done.record()
+        self.pending = True
+        return (self.logits.clone() if self.logits is not None else None), True
+
+
 class StepFunction:
     """``step(inputs)`` -> float32 logits [number of wanted places, vocab] on the device, in the
     order of the inputs and of each input's ``want``."""
@@ -243,6 +309,12 @@ class StepFunction:
         self.last_h2d_bytes = 0     # bytes of the last step's host-to-device copy (tokens, positions, page tables)
         self.last_d2h_bytes = 0     # bytes of the last step's copy of drawn tokens to the host (decode_and_sample)
         self.before_launch = None   # measurement hook: called between a recorded decode step's host work and its launch
+        # short prompts of one sequence as recorded passes (PromptGraph), a few dozen sizes kept, the oldest dropped
+        self.use_prompt_graphs = bool(self.use_graphs and getattr(model, "pad_safe", False))
+        self.max_prompt_graph_tokens = 1024   # beyond this the GPU is the slower side and a recording saves nothing
+        self.max_prompt_graphs = 32
+        self._prompt_graphs: dict[tuple, PromptGraph] = {}
+        self.prompt_graph_replays = 0
         self._drawn: dict[int, torch.Tensor] = {}   # per number of sequences: where every recorded draw leaves its tokens
         self._in_flight: list[DecodeGraph] = []     # steps launched by decode_ahead, oldest first, not yet collected
         self._fed_turn = 0
@@ -352,6 +424,38 @@ class StepFunction:
             return logits[torch.tensor(wanted, device=logits.device)]
         return logits if (reuse_output or not replayed) else logits.clone()
 
+    def _prompt_with_graph(self, seq: SequenceInput):
+        """The pass of one sequence's short prompt (or chunk) as a recorded pass; NotImplemented when it is not one
+        for that: too long, too many wanted places, a start inside a page, or a size whose pages are not reserved."""
+        cache = self.cache
+        start, n = cache.length(seq.slot), len(seq.tokens)
+        if n < 2 or n > self.max_prompt_graph_tokens or len(seq.want) > 8 or start % PAGE_TOKENS != 0:
+            return NotImplemented
+        padded = -(-n // PAGE_TOKENS) * PAGE_TOKENS          # up to the end of the last page the pass has reserved
+        widths = []
+        for gi in range(len(cache.paged_groups)):
+            need = max(len(r) for r in cache.page_rows(gi, [seq.slot]))
+            if need * PAGE_TOKENS < start + padded:
+                return NotImplemented                        # (a group that keeps fewer pages than positions)
+            w = 4
+            while w < need:
+                w *= 2
+            widths.append(w)
+        key = (padded, tuple(widths), len(seq.want))
+        g = self._prompt_graphs.pop(key, None)
+        if g is None:
+            while len(self._prompt_graphs) >= self.max_prompt_graphs:
+                self._prompt_graphs.pop(next(iter(self._prompt_graphs)))   # the one used longest ago
+            g = PromptGraph(self.model, cache, padded, widths, len(seq.want))
+        self._prompt_graphs[key] = g                          # (re-inserted: most recently used last)
+        logits, replayed = g.run(seq.slot, start, seq.tokens, list(seq.want))
+        self.last_h2d_bytes = g.h2d_bytes
+        if replayed:
+            self.prompt_graph_replays += 1
+            self.graph_launches += g.n_launches
+        cache.commit(seq.slot, n)
+        return logits
+
     def _validate(self, inputs: list[SequenceInput]) -> None:
         if not inputs:
             raise StepError("a step needs at least one sequence")
@@ -380,6 +484,10 @@ class StepFunction:
         cache.reserve([(s.slot, len(s.tokens)) for s in inputs])
         if self.use_graphs and len(inputs) <= self.max_graph_batch and all(len(s.tokens) == 1 for s in inputs):
             return self._decode_with_graph(inputs, self.reuse_output if reuse_output is None else reuse_output)
+        if self.use_prompt_graphs and len(inputs) == 1:
+            out = self._prompt_with_graph(inputs[0])
+            if out is not NotImplemented:
+                return out
         n_want = sum(len(s.want) for s in inputs)
         out_offsets, off = [], 0
         for s in inputs:

@@ -19,6 +19,7 @@ from .linear import Linear
 
 class GroupedQueryAttention(Mixer):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int, position: PositionEncoding,
                  window: int | None = None):

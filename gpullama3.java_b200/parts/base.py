@@ -91,6 +91,12 @@ class Part:
     # lengths: only then may a decode step be recorded once and replayed as a CUDA graph.
     graph_safe: bool = False
 
+    # True when tokens appended behind a pass's own tokens change nothing that the own tokens' results or any later
+    # step depend on: per-token parts, and mixers whose only memory is a cache that is read causally and written at
+    # each token's own position.  Only then may a short prompt run as a recorded pass padded to a whole page
+    # (a mixer that folds every token it sees into a state of fixed size is not: the padding would enter the state).
+    pad_safe: bool = False
+
     def parameters(self) -> dict[str, ParamSpec]:
         """Local parameter names -> shape and random-init kind."""
         return {}

@@ -15,6 +15,10 @@ class PreNormBlock(Block):
         # the block itself launches nothing; its decode step is as replayable as its parts' launches are
         return all(p.graph_safe for p in all_parts(self).values())
 
+    @property
+    def pad_safe(self):
+        return all(p.pad_safe for p in all_parts(self).values())
+
     def first_norm(self):
         return self.mixer_norm
 

@@ -16,6 +16,7 @@ from .linear import Linear
 
 class TokenEmbedding(Part):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -37,6 +38,7 @@ class TokenEmbedding(Part):
 
 class OutputHead(Part):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None):
         self.vocab_size, self.hidden_size, self.tied_to = vocab_size, hidden_size, tied_to

@@ -14,6 +14,7 @@ from .linear import Linear
 
 class SwiGLUFeedForward(FeedForward):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size

@@ -11,6 +11,7 @@ from .base import Norm, register_norm
 
 class RMSNorm(Norm):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, dim: int, eps: float):
         self.dim, self.eps = int(dim), float(eps)

@@ -51,6 +51,7 @@ def llama3_inverse_frequencies(head_dim: int, theta: float, scaling: dict | None
 
 class RotaryPositionEncoding(PositionEncoding):
     graph_safe = True
+    pad_safe = True
 
     def __init__(self, head_dim: int, theta: float, pairing: str = "half", scaling: dict | None = None,
                  rotary_dim: int | None = None):
@@ -88,6 +89,7 @@ class RotaryPositionEncoding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
+    pad_safe = True
 
     """Queries and keys pass unrotated (rotary_dim = 0)."""
 
