@@ -86,6 +86,28 @@ def build_context(dtype, device, cache: SequenceCache, slots: list[int], start_p
     return ctx, (rows if logit_rows else None)
 
 
+def _record(launches):
+    """Records ``launches()`` (which must have run once already as ordinary launches, so that every kernel library
+    is loaded and configured) into a CUDA graph without running it; returns the graph, what ``launches`` returned
+    inside the recording (tensors at fixed addresses) and the number of kernel launches recorded."""
+    import gc
+
+    from ..kernels import ops
+
+    torch.cuda.synchronize()
+    before = ops.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    gc_was_on = gc.isenabled()
+    gc.disable()  # a collection while recording could free device or pinned memory, which is not allowed then
+    try:
+        with torch.cuda.graph(graph):
+            out = launches()
+    finally:
+        if gc_was_on:
+            gc.enable()
+    return graph, out, ops.launch_count() - before
+
+
 class DecodeGraph:
     """One captured decode step for a fixed number of sequences and fixed page-table widths.
 
@@ -183,8 +205,6 @@ class DecodeGraph:
     def run(self, slots, start_pos, tokens, uniforms=None, before_launch=None) -> torch.Tensor:
         """``before_launch``: called when the host side of the step is done, right before the step's first
         launch (a measurement records its start event there)."""
-        from ..kernels import ops
-
         self.refresh(slots, start_pos, tokens, uniforms)
         if before_launch is not None:
             before_launch()
@@ -194,19 +214,7 @@ class DecodeGraph:
             out = self._launches(slots, start_pos)
             torch.cuda.synchronize()
             first_tokens = self.tokens_host.clone() if self.sampler is not None else None
-            before = ops.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            import gc
-            gc_was_on = gc.isenabled()
-            gc.disable()  # a collection while recording could free device or pinned memory, which is not allowed then
-            try:
-                with torch.cuda.graph(graph):
-                    self.logits = self._launches(slots, start_pos)
-            finally:
-                if gc_was_on:
-                    gc.enable()
-            self.n_launches = ops.launch_count() - before
-            self.graph = graph
+            self.graph, self.logits, self.n_launches = _record(lambda: self._launches(slots, start_pos))
             if first_tokens is not None:
                 self.tokens_host.copy_(first_tokens)
             return out
@@ -258,8 +266,6 @@ class PromptGraph:
 
     def run(self, slot: int, start: int, tokens: list[int], rows: list[int]) -> tuple[torch.Tensor | None, bool]:
         """Logits at ``rows`` (None when none are wanted) and whether the pass was replayed."""
-        from ..kernels import ops
-
         if self.pending:
             self.done.synchronize()  # the run before must have read the staging buffer
             self.pending = False
@@ -268,20 +274,7 @@ class PromptGraph:
         np.concatenate(pieces, out=self.host_np)
         if self.graph is None:
             out = self._launches(slot, start)   # the first pass of this size runs as ordinary launches, then is recorded
-            torch.cuda.synchronize()
-            before = ops.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            import gc
-            gc_was_on = gc.isenabled()
-            gc.disable()
-            try:
-                with torch.cuda.graph(graph):
-                    self.logits = self._launches(slot, start)
-            finally:
-                if gc_was_on:
-                    gc.enable()
-            self.n_launches = ops.launch_count() - before
-            self.graph = graph
+            self.graph, self.logits, self.n_launches = _record(lambda: self._launches(slot, start))
             return out, False
         self.graph.replay()
         self.done.record()
