@@ -2,7 +2,7 @@
 //
 // A is [M, K] (activations, row-major, row stride lda), W is [N, K] (a weight as the reference
 // stores it: one row per output, core/model/tensor/FloatTensor.java:98-100 of the reference
-// project).  Two kernels: tiles of 64 x 64 for prompts, and a weight-streaming one for a decode step's few rows
+// project).  Three kernels: tiles of 128 x 128 for prompts, of 64 x 64 for fewer than 128 rows, and a weight-streaming one for a decode step's few rows
 // (further down).  This is the kernel of the true 32-bit path (no tensor cores, no reduced-precision
 // matrix mode) and the fallback of the bfloat16 path for sizes or storage types the tensor-core
 // kernels refuse.  Epilogues:
@@ -68,6 +68,80 @@ gemm_generic_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W,
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int n = n0 + tx * 4 + j;
+                if (n >= N) continue;
+                TC* c = C + (size_t)m * ldc + n;
+                if (epilogue == 1) *c = from_f32<TC>(to_f32<TC>(*c) + acc[i][j]);
+                else *c = from_f32<TC>(acc[i][j]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product for prompts (M >= 128): tiles of 128 x 128, a thread owns 8 x 8 sums, so that a k-step costs four
+// 16-byte shared-memory loads per 64 multiply-adds instead of eight 4-byte loads per 16; the next tile's operands are
+// fetched into registers while the current one is multiplied.  Still plain 32-bit FMA in a fixed order of k.
+constexpr int kBigM = 128, kBigN = 128, kBigK = 16, kBigThreads = 256;
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(kBigThreads)
+gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
+                        int M, int N, int K, int epilogue) {
+    __shared__ __align__(16) float As[kBigK][kBigM + 4];
+    __shared__ __align__(16) float Ws[kBigK][kBigN + 4];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * kBigM, n0 = blockIdx.x * kBigN;
+    const int tx = tid % 16, ty = tid / 16;   // rows ty * 8 .. + 7, columns tx * 8 .. + 7
+    float acc[8][8] = {};
+    float ra[8], rw[8];                        // this thread's share of the next tile: 8 elements of each operand
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + i * kBigThreads, r = e / kBigK, k = k0 + e % kBigK;   // 16 lanes read along k
+            ra[i] = (m0 + r < M && k < K) ? to_f32<TA>(A[(size_t)(m0 + r) * lda + k]) : 0.f;
+            rw[i] = (n0 + r < N && k < K) ? to_f32<TW>(W[(size_t)(n0 + r) * ldw + k]) : 0.f;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += kBigK) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = tid + i * kBigThreads, r = e / kBigK, c = e % kBigK;
+            As[c][r] = ra[i];
+            Ws[c][r] = rw[i];
+        }
+        __syncthreads();
+        if (k0 + kBigK < K) fetch(k0 + kBigK);
+#pragma unroll
+        for (int k = 0; k < kBigK; ++k) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 8]), a1 = *reinterpret_cast<const float4*>(&As[k][ty * 8 + 4]);
+            const float4 w0 = *reinterpret_cast<const float4*>(&Ws[k][tx * 8]), w1 = *reinterpret_cast<const float4*>(&Ws[k][tx * 8 + 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + ty * 8 + i;
+        if (m >= M) continue;
+        if (epilogue == 2) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const int n = n0 + tx * 8 + j;
+                if (n + 1 < N) {
+                    const float gate = acc[i][j], up = acc[i][j + 1];
+                    C[(size_t)m * ldc + n / 2] = from_f32<TC>((gate / (1.0f + expf(-gate))) * up);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int n = n0 + tx * 8 + j;
                 if (n >= N) continue;
                 TC* c = C + (size_t)m * ldc + n;
                 if (epilogue == 1) *c = from_f32<TC>(to_f32<TC>(*c) + acc[i][j]);
@@ -166,6 +240,13 @@ extern "C" int b200_gemm_generic(const void* A, int a_dtype, int lda, const void
     if (M <= 16 && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && ((uintptr_t)A % (4 * a_el)) == 0 && ((uintptr_t)W % (4 * w_el)) == 0) {
         B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
             return b200::launch_fewrows<TA, TW, TC>(A, lda, W, ldw, C, ldc, M, N, K, epilogue, stream))));
+    }
+    if (M >= b200::kBigM && (M + b200::kBigM - 1) / b200::kBigM <= 65535) {
+        dim3 big((N + b200::kBigN - 1) / b200::kBigN, (M + b200::kBigM - 1) / b200::kBigM);
+        B200_DISPATCH_DTYPE(a_dtype, TA, B200_DISPATCH_DTYPE2(w_dtype, TW, B200_DISPATCH_DTYPE3(c_dtype, TC,
+            b200::gemm_generic_big_kernel<TA, TW, TC><<<big, b200::kBigThreads, 0, stream>>>(
+                (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue))));
+        return b200::launch_status();
     }
     dim3 grid((N + b200::kTileN - 1) / b200::kTileN, (M + b200::kTileM - 1) / b200::kTileM);
     if (grid.y > 65535) return b200::kErrUnsupportedSize;

@@ -39,7 +39,8 @@ _SIGNATURES = {
     "b200_rope_cache_write": ("rope_cache", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_attention_paged": ("attention_generic", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]),
+                                                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_void_p]),
     "b200_gemm_generic": ("gemm_generic", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                            c_int, c_int, c_int, c_int]),
     "b200_gemm_decode": ("gemm_decode", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -224,17 +225,23 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, seq_ids: torch.
 # --------------------------------------------------------------------------- attention
 def attention_paged(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, positions: torch.Tensor,
                     seq_ids: torch.Tensor, page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
-                    n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0) -> None:
+                    n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0, n_splits: int = 1) -> None:
     """Causal grouped-query attention of every token of ``q`` over the cached keys 0..position of
-    its sequence.  q: rows of ``q_row_stride`` elements whose first H*D are the rotated queries."""
+    its sequence.  q: rows of ``q_row_stride`` elements whose first H*D are the rotated queries.
+    ``n_splits`` > 1 cuts every token's keys into that many spans, one CTA each, merged by a second kernel (a decode
+    step: few tokens, long rows of keys)."""
     _dev(q, out, positions, seq_ids, page_table, k_pool, v_pool)
     assert out.is_contiguous() and out.shape[1] == n_heads * head_dim and out.dtype == q.dtype == k_pool.dtype
     assert tuple(k_pool.shape[1:]) == (n_kv_heads, PAGE_TOKENS, head_dim)
     assert tuple(v_pool.shape[1:]) == (n_kv_heads, head_dim, PAGE_TOKENS)
+    scratch = None
+    if n_splits > 1:
+        scratch = torch.empty(out.shape[0] * n_heads * n_splits * (head_dim + 2), dtype=torch.float32, device=q.device)
     _check(_fn("b200_attention_paged")(
         q.data_ptr(), q_row_stride, out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(), seq_ids.data_ptr(),
         page_table.data_ptr(), page_table.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), out.shape[0], n_heads,
-        n_kv_heads, head_dim, int(window), _stream()), "attention_paged")
+        n_kv_heads, head_dim, int(window), int(n_splits), scratch.data_ptr() if scratch is not None else None, _stream()),
+        "attention_paged")
 
 
 # --------------------------------------------------------------------------- matrix products

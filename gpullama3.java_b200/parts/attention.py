@@ -91,8 +91,11 @@ class GroupedQueryAttention(Mixer):
                                      cache.k, cache.v, self.n_heads, self.n_kv_heads, self.head_dim,
                                      self.position.rotary_dim, self.position.pairing, write_cache=writes_cache)
         if not attended and not fast.try_attention(qkv, out, ctx, table, cache, self):
+            # (the plain kernel: a step of few tokens cuts their keys into spans so that the GPU has CTAs to run)
+            rows = x.shape[0] * self.n_heads
+            splits = 1 if rows >= 1024 else max(1, min(16, 1024 // rows, ctx.capacity(cache.group) // 512))
             ops.attention_paged(qkv, qkv.shape[1], out, ctx.positions, ctx.seq_ids, table, cache.k, cache.v,
-                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0)
+                                self.n_heads, self.n_kv_heads, self.head_dim, self.window or 0, n_splits=splits)
         return self.o.add_to(out, residual, then_norm)
 
 

@@ -124,6 +124,11 @@ def test_attention_paged_against_plain(dtype, H, KVH, D, window):
     ops().attention_paged(qkv, qkv.shape[1], out, pos_t, seq_t, table, k_pool, v_pool, H, KVH, D, window)
     ref = torch.cat(refs).reshape(-1, H * D)
     torch.testing.assert_close(out.float().cpu(), ref.to(dtype).float(), **tol(dtype, ref))
+    # the keys of every token cut into spans (more spans than some tokens have tiles of keys: empty spans)
+    for n_splits in (2, 5):
+        cut = torch.full_like(out, 7.0)
+        ops().attention_paged(qkv, qkv.shape[1], cut, pos_t, seq_t, table, k_pool, v_pool, H, KVH, D, window, n_splits=n_splits)
+        torch.testing.assert_close(cut.float().cpu(), ref.to(dtype).float(), **tol(dtype, ref))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -141,6 +146,10 @@ def test_attention_finds_one_far_key_among_hundreds(dtype):
     ref = P.causal_attention(q.to(dtype).float().reshape(1, H, D).expand(n, H, D).contiguous(), k, v)[-1]
     torch.testing.assert_close(out.float().cpu().reshape(H, D), ref.to(dtype).float(), **tol(dtype, ref))
     assert float((out.float().cpu().reshape(H, D)[0] - v[target, 0]).abs().max()) < 0.05
+    cut = torch.empty_like(out)                               # the far key lies in the first of four spans
+    ops().attention_paged(qkv, qkv.shape[1], cut, torch.tensor([n - 1], dtype=torch.int32, device="cuda"),
+                          torch.tensor([0], dtype=torch.int32, device="cuda"), table, k_pool, v_pool, H, KVH, D, 0, n_splits=4)
+    assert float((cut.float().cpu().reshape(H, D)[0] - v[target, 0]).abs().max()) < 0.05
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
