@@ -153,9 +153,8 @@ gemm_generic_big_kernel(const TA* __restrict__ A, int lda, const TW* __restrict_
 
 // ---------------------------------------------------------------------------------------------
 // The same product for a decode step's few rows (M <= 16): tiles of 64 tokens would leave the FMA units idle and
-// read every weight through shared memory for nothing.  Here a warp owns two consecutive weight rows (a gate/up
-// pair of the gated epilogue) and streams them 16 bytes per lane, every element meeting all M tokens' activations
-// (which stay in L1); the lanes' sums are added in a fixed tree.  Still plain 32-bit FMA.
+// read every weight through shared memory for nothing.  Here the weight rows are streamed 16 bytes per lane, every
+// element meeting all M tokens' activations (which stay in L1); see gemm_fewrows_kernel.
 template <typename T> __device__ __forceinline__ float4 load4(const T* p);
 template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
 template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
@@ -164,62 +163,90 @@ template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bf
                        __uint_as_float(v.y & 0xffff0000u));
 }
 
-constexpr int kFewWarps = 8, kFewThreads = kFewWarps * 32;
+constexpr int kFewWarps = 8, kFewThreads = kFewWarps * 32, kFewRows = 4;
 
+// sum over the lanes of a warp by halving: afterwards v[0] of lane l is the sum of every lane's v[l] (31 exchanges
+// for 32 numbers, where a butterfly per number would need 160)
+__device__ __forceinline__ float reduce_by_halving(float (&v)[32], int lane) {
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float send = upper ? v[i] : v[i + half];
+            const float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    return v[0];
+}
+
+// A CTA owns four consecutive weight rows (two gate/up pairs of the gated epilogue); its eight warps split K between
+// them (a warp takes 128 elements of every 1024), so that a narrow output still gives every SM several CTAs and each
+// activation element loaded from L1 meets four weight rows.  MT tokens (8 or 16): 4 x MT sums per lane, summed over
+// the lanes by halving and over the warps in shared memory in warp order.  Still plain 32-bit FMA.
 template <typename TA, typename TW, typename TC, int MT>
 __global__ void __launch_bounds__(kFewThreads)
 gemm_fewrows_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C, int ldc,
                     int M, int N, int K, int epilogue) {
+    __shared__ float part[kFewWarps][kFewRows * MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * kFewWarps + warp) * 2;
-    if (n0 >= N) return;
-    const TW* w0 = W + (size_t)n0 * ldw;
-    const TW* w1 = W + (size_t)min(n0 + 1, N - 1) * ldw;
-    float acc0[MT], acc1[MT];
+    const int n0 = blockIdx.x * kFewRows;
+    const TW* w[kFewRows];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) { acc0[m] = 0.f; acc1[m] = 0.f; }
+    for (int r = 0; r < kFewRows; ++r) w[r] = W + (size_t)min(n0 + r, N - 1) * ldw;   // clamped: read, never stored
+    float acc[kFewRows * MT];
+#pragma unroll
+    for (int i = 0; i < kFewRows * MT; ++i) acc[i] = 0.f;
 #pragma unroll 2
-    for (int k = lane * 4; k < K; k += 128) {
-        const float4 a0 = load4<TW>(w0 + k), a1 = load4<TW>(w1 + k);
+    for (int k = (warp * 32 + lane) * 4; k < K; k += kFewWarps * 128) {
+        float4 wv[kFewRows];
+#pragma unroll
+        for (int r = 0; r < kFewRows; ++r) wv[r] = load4<TW>(w[r] + k);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < M) {
                 const float4 x = load4<TA>(A + (size_t)m * lda + k);
-                acc0[m] = fmaf(a0.w, x.w, fmaf(a0.z, x.z, fmaf(a0.y, x.y, fmaf(a0.x, x.x, acc0[m]))));
-                acc1[m] = fmaf(a1.w, x.w, fmaf(a1.z, x.z, fmaf(a1.y, x.y, fmaf(a1.x, x.x, acc1[m]))));
+#pragma unroll
+                for (int r = 0; r < kFewRows; ++r)
+                    acc[r * MT + m] = fmaf(wv[r].w, x.w, fmaf(wv[r].z, x.z, fmaf(wv[r].y, x.y, fmaf(wv[r].x, x.x, acc[r * MT + m]))));
             }
         }
     }
+    // lane l ends up with sum number l (and l + 32 for 16 tokens) of this warp
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int b = 0; b < kFewRows * MT / 32; ++b) {
+        float v[32];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], off);
-            acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], off);
+        for (int i = 0; i < 32; ++i) v[i] = acc[b * 32 + i];
+        part[warp][b * 32 + lane] = reduce_by_halving(v, lane);
+    }
+    __syncthreads();
+    // thread i < 4 * MT: row i / MT, token i % MT; the warps' sums are added in warp order
+    const int i = threadIdx.x;
+    if (i >= kFewRows * MT) return;
+    const int r = i / MT, m = i % MT, n = n0 + r;
+    float sum = 0.f;
+#pragma unroll
+    for (int wp = 0; wp < kFewWarps; ++wp) sum += part[wp][i];
+    if (epilogue == 2) {
+        float up = 0.f;   // the gate row's thread also adds up the up row (the next row of the CTA)
+        if ((r & 1) == 0) {
+#pragma unroll
+            for (int wp = 0; wp < kFewWarps; ++wp) up += part[wp][i + MT];
+            if (m < M && n + 1 < N) C[(size_t)m * ldc + n / 2] = from_f32<TC>((sum / (1.0f + expf(-sum))) * up);
         }
-    // lane m stores token m's two sums
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        if (lane != m || m >= M) continue;
-        if (epilogue == 2) {
-            if (n0 + 1 < N) C[(size_t)m * ldc + n0 / 2] = from_f32<TC>((acc0[m] / (1.0f + expf(-acc0[m]))) * acc1[m]);
-        } else {
-            TC* c = C + (size_t)m * ldc + n0;
-            if (epilogue == 1) {
-                c[0] = from_f32<TC>(to_f32<TC>(c[0]) + acc0[m]);
-                if (n0 + 1 < N) c[1] = from_f32<TC>(to_f32<TC>(c[1]) + acc1[m]);
-            } else {
-                c[0] = from_f32<TC>(acc0[m]);
-                if (n0 + 1 < N) c[1] = from_f32<TC>(acc1[m]);
-            }
-        }
+    } else if (m < M && n < N) {
+        TC* c = C + (size_t)m * ldc + n;
+        if (epilogue == 1) *c = from_f32<TC>(to_f32<TC>(*c) + sum);
+        else *c = from_f32<TC>(sum);
     }
 }
 
 template <typename TA, typename TW, typename TC>
 static int launch_fewrows(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N, int K, int epilogue,
                           cudaStream_t stream) {
-    const dim3 grid((N + 2 * kFewWarps - 1) / (2 * kFewWarps));
+    const dim3 grid((N + kFewRows - 1) / kFewRows);
     if (M <= 8)
         gemm_fewrows_kernel<TA, TW, TC, 8><<<grid, kFewThreads, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, epilogue);
     else
