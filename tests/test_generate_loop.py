@@ -339,3 +339,20 @@ def test_generation_stops_at_the_configurations_context_length():
     assert res[0].finish_reason == FINISH_CONTEXT and len(res[0].tokens) == 3     # 17 + 3 = 20 positions
     assert res[1].finish_reason == FINISH_LENGTH and len(res[1].tokens) == 10
     assert cache.live_slots() == []
+
+
+def test_span_rule_of_decode_attention():
+    """How many spans a decode step cuts its keys into: one wave of CTAs at most, up to 16 spans of at least two
+    blocks of 32 keys, beyond that at least 8 blocks a span, always a power of two."""
+    from gpullama3.java_b200.kernels.ops import attention_decode_splits as splits
+
+    assert splits(1, 8, 4096, 592) == 16        # batch 1 at 4,096 keys: 16 spans, not the 64 the GPU would hold
+    assert splits(1, 8, 1024, 592) == 16        # a short context still gets spans of two blocks
+    assert splits(1, 8, 16384, 592) == 64       # long rows: 8 blocks a span, 64 spans at most
+    assert splits(8, 8, 4096, 592) == 8         # batch 8: 9 would fit one wave, 8 is the power of two
+    assert splits(8, 8, 512, 592) == 8
+    assert splits(64, 8, 4096, 592) == 1        # the batch alone fills the GPU
+    assert splits(1, 8, 40, 592) == 1           # one block of keys
+    for args in [(3, 4, 777, 592), (1, 1, 100000, 296), (200, 8, 64, 592)]:
+        s = splits(*args)
+        assert s >= 1 and s & (s - 1) == 0 and s * args[0] * args[1] <= max(args[3], args[0] * args[1])

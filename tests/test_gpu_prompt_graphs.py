@@ -119,3 +119,31 @@ def test_a_part_that_is_not_pad_safe_keeps_the_model_off_recorded_prompts(sessio
         assert not StepFunction(model, model.new_cache(256)).use_prompt_graphs
     finally:
         del part.pad_safe
+
+
+def test_recordings_are_kept_up_to_a_number_and_the_oldest_goes(session_tmp):
+    from gpullama3.java_b200.engine.step import SequenceInput
+
+    cfg, weights, model, cache, step = _setup(session_tmp, "A", torch.bfloat16)
+    step.max_prompt_graphs = 2
+    sizes = [10, 70, 130, 10, 70]            # padded 64, 128, 192: the third pushes the first out, the fourth records it again
+    replays = []
+    for n in sizes:
+        slot = cache.acquire()
+        p = random_prompts(cfg["vocab_size"], [n], seed=n)[0]
+        got = step([SequenceInput(slot, p, [n - 1])])
+        ref = P.forward(cfg, weights, p, round_to=torch.bfloat16)
+        exact = P.forward(cfg, weights, p, dtype=torch.float64)
+        _check(torch.cat([got.cpu(), got.cpu()]), [n - 1, n - 1], ref, exact, torch.bfloat16, f"prompt of {n}")
+        cache.release(slot)
+        replays.append(step.prompt_graph_replays)
+        assert len(step._prompt_graphs) <= 2
+    assert replays == [0, 0, 0, 0, 0]        # 64 was dropped when 192 came, 128 when 64 came back: nothing is replayed
+    slot = cache.acquire()
+    step([SequenceInput(slot, random_prompts(cfg["vocab_size"], [100], seed=1)[0], [])])   # padded 128, no wanted place: a new key
+    step.max_prompt_graphs = 8
+    cache.release(slot)
+    slot = cache.acquire()
+    step([SequenceInput(slot, random_prompts(cfg["vocab_size"], [70], seed=70)[0], [69])])  # 128 with one wanted place: still recorded
+    cache.release(slot)
+    assert step.prompt_graph_replays == 1
