@@ -21,6 +21,10 @@
 //                      L2 add them to C; the SM never reads the residual stream, and nothing is strided (a
 //                      thread per row would touch 32 rows with every access).  Each element is added once.
 //                      (Stores of bfloat16 results through such boxes were measured and gained nothing.)
+//                      3 the query/key/value product of a prompt pass: rotation and cache write (RopeEpilogue).
+// Three kernels share these roles and epilogues: the one just described; pairs of CTAs on 256-row tiles
+// (gemm_tcgen05_pair_kernel, tcgen05 cta_group::2), which large products take; and K cut into spans over a cluster
+// (gemm_tcgen05_spans_kernel) for few tiles with a long K.  Tiles are walked in bands of rows (tile_coords).
 // Edges: TMA zero-fills rows and K beyond the tensors, stores are bounds-checked, so any M, N and
 // any K that keeps rows 16-byte aligned (K % 8 == 0) are accepted.
 // Every mbarrier wait is bounded: when a wait gives up, the kernel records a code in a status
