@@ -934,8 +934,10 @@ extern "C" int b200_gemm_tcgen05(const void* A, int lda, const void* W, int ldw,
     // the pair kernel is the faster one at every shape tried, by 5 to 25 %)
     if (cta_pair == 0 && tile_width == 0 && k_spans == 0) {
         const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-        if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2)
-            return launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+        if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2) {
+            const int st = launch_pair_width<256, 6>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
+            if (st != kErrUnsupportedSize) return st;   // (no two SMs that can form a pair: the single-CTA kernels below)
+        }
     }
     const int spans = k_spans > 0 ? k_spans : (tile_width > 0 ? 1 : k_spans_for(M, N, K));
     if (spans > 1) {
@@ -979,8 +981,10 @@ extern "C" int b200_gemm_tcgen05_qkv_rope(const void* A, int lda, const void* W,
     rope.n_heads = n_heads; rope.n_kv_heads = n_kv_heads; rope.head_dim = head_dim; rope.pairing = pairing;
     rope.write_cache = write_cache ? 1 : 0;
     const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2)
-        return launch_pair<256, 6, 3, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, rope);
+    if (pair_tiles * 3 >= (long long)(sm_count() / 2) * 2) {
+        const int st = launch_pair<256, 6, 3, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, rope);
+        if (st != kErrUnsupportedSize) return st;
+    }
     if (k_spans_for(M, N, K) == 1 && tile_width_for(M, N) == 256)
         return launch_tc<256, 4, 3, __nv_bfloat16>(A, lda, W, ldw, C, ldc, M, N, K, stream, rope);
     return kErrUnsupportedSize;
