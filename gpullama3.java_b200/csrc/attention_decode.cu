@@ -193,7 +193,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // rows g and g + 8; l is this lane's share
-    const float sqrt_d = sqrtf((float)D);
+    // scores are scaled by a multiplication: a division by sqrt(d) that is no power of two (head sizes 32, 96, 128) is a
+    // subroutine that, with this kernel's registers all taken, cost more than the block's tensor-core work
+    const float inv_sqrt_d = 1.f / sqrtf((float)D);
 
     for (int blk = blk_begin + warp; blk < blk_end; blk += kAttnDecodeWarps) {
         const int base = blk * 32;
@@ -239,10 +241,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             for (int e = 0; e < 2; ++e) {
                 const int key = base + 8 * t + 2 * i + e;
                 const bool ok = key >= lo && key < n_cached;
-                s[i][e] = ok ? s[i][e] / sqrt_d : -INFINITY;
+                s[i][e] = ok ? s[i][e] * inv_sqrt_d : -INFINITY;
                 bm_lo = fmaxf(bm_lo, s[i][e]);
                 if (HI) {
-                    s[i][2 + e] = ok ? s[i][2 + e] / sqrt_d : -INFINITY;
+                    s[i][2 + e] = ok ? s[i][2 + e] * inv_sqrt_d : -INFINITY;
                     bm_hi = fmaxf(bm_hi, s[i][2 + e]);
                 }
             }
@@ -351,15 +353,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < 16; idx += kAttnDecodeThreads) {
+        for (int idx = warp; idx < 16; idx += kAttnDecodeWarps) {   // a warp per head: its lanes share the dimensions
             float sc = -INFINITY;
             if (mine && idx < group) {
                 float dot = 0.f;
-                for (int d = 0; d < D; ++d) dot += q_s[idx * D + d] * k_s[d];
-                sc = dot / sqrt_d;
+                for (int d = lane; d < D; d += 32) dot += q_s[idx * D + d] * k_s[d];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                sc = dot * inv_sqrt_d;
             }
-            ml_s[(kAttnDecodeWarps * 16 + idx) * 2] = sc;
-            ml_s[(kAttnDecodeWarps * 16 + idx) * 2 + 1] = mine && idx < group ? 1.f : 0.f;
+            if (lane == 0) {
+                ml_s[(kAttnDecodeWarps * 16 + idx) * 2] = sc;
+                ml_s[(kAttnDecodeWarps * 16 + idx) * 2 + 1] = mine && idx < group ? 1.f : 0.f;
+            }
         }
         for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads)
             o_s[(size_t)kAttnDecodeWarps * 16 * D + idx] = mine ? v_s[idx % D] : 0.f;
