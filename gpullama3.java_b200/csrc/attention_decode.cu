@@ -504,6 +504,38 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
 
 }  // namespace b200
 
+// How many CTAs of the kernel for (head_dim, heads per kv head, fused or not) one SM holds at once: what the choice of
+// spans should plan for (heads of 64 hold four, heads of 128 two).  0 for sizes the kernel does not take.
+extern "C" int b200_attention_decode_ctas_per_sm(int head_dim, int group, int fused) {
+    using namespace b200;
+    if (group < 1 || group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128) return 0;
+    const int slots = kAttnDecodeWarps + (fused ? 1 : 0);
+    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 19 * head_dim : 0));
+    int n = 0;
+    cudaError_t e = cudaSuccess;
+#define B200_OCC_H(KB, F, HI)                                                                                          \
+    do {                                                                                                              \
+        auto kernel = attention_decode_kernel<KB, F, HI>;                                                             \
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kAttnDecodeThreads, smem); \
+    } while (0)
+#define B200_OCC(KB)                                                                                                   \
+    do {                                                                                                              \
+        if (fused) { if (group > 8) B200_OCC_H(KB, true, true); else B200_OCC_H(KB, true, false); }                   \
+        else { if (group > 8) B200_OCC_H(KB, false, true); else B200_OCC_H(KB, false, false); }                       \
+    } while (0)
+    switch (head_dim / 32) {
+        case 1: B200_OCC(1); break;
+        case 2: B200_OCC(2); break;
+        case 3: B200_OCC(3); break;
+        default: B200_OCC(4); break;
+    }
+#undef B200_OCC
+#undef B200_OCC_H
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
 // Queries already rotated, keys and values of the step already in the cache.  early_start: whether the kernel
 // may be scheduled while its predecessor on the stream still runs (0 for a long kernel that fills the GPU).
 extern "C" int b200_attention_decode(const void* q, int q_row_stride, void* out, const int* kv_lens,

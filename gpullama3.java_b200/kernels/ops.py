@@ -453,10 +453,20 @@ def attention_decode_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int
     return dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) and n_heads // n_kv_heads <= 16
 
 
-def resident_ctas(device) -> int:
-    """The number of CTAs the spans of decode attention are planned for: four per SM, which is what the kernel
-    for heads of 64 holds at once.  (Heads of 128 hold two; planning for two or three changed no step time.)"""
-    return 4 * _sm_count(torch.device(device))
+_ctas_per_sm: dict = {}
+
+
+def resident_ctas(device, head_dim: int = 64, group: int = 4, fused: bool = True) -> int:
+    """The number of CTAs of decode attention the GPU holds at once, which is what the spans are planned for: the
+    occupancy the driver reports for the kernel of these sizes (heads of 64 hold four per SM, heads of 128 two)
+    times the SMs.  Four per SM for sizes that kernel does not take."""
+    key = (head_dim, group > 8, fused)
+    per_sm = _ctas_per_sm.get(key)
+    if per_sm is None:
+        query = library("attention_decode").b200_attention_decode_ctas_per_sm
+        query.argtypes, query.restype = [c_int, c_int, c_int], c_int
+        per_sm = _ctas_per_sm[key] = query(head_dim, group, 1 if fused else 0) or 4
+    return per_sm * _sm_count(torch.device(device))
 
 
 def attention_decode_splits(n_seqs: int, n_kv_heads: int, max_kv_len: int, resident_ctas: int) -> int:

@@ -58,7 +58,8 @@ class GroupedQueryAttention(Mixer):
         capacity = ctx.capacity(cache.group)
         if self.window:
             capacity = min(capacity, self.window)
-        splits = ops.attention_decode_splits(ctx.n_seqs, self.n_kv_heads, capacity, ops.resident_ctas(ctx.device))
+        resident = ops.resident_ctas(ctx.device, self.head_dim, self.n_heads // self.n_kv_heads)
+        splits = ops.attention_decode_splits(ctx.n_seqs, self.n_kv_heads, capacity, resident)
         return splits, ops.attention_decode_early_start(ctx.n_seqs, self.n_kv_heads, capacity, splits)
 
     def load(self, tensors, dtype, device):
