@@ -100,11 +100,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     constexpr int D = KB * 32;
     constexpr int NJ = D / 8;  // output tiles of 8 dims
     constexpr int SLOTS = kAttnDecodeWarps + (FUSED ? 1 : 0);  // partials merged per CTA: the warps, and the new key
-    extern __shared__ float smem[];  // [SLOTS][16][D] outputs, [SLOTS][16][2] (m, l); fused: q [16][D], k [D], v [D], cos [D/2], sin [D/2]
+    // Rows of the tiles that exist: 8 without the upper half.  (Shared memory is taken from the SM's L1, through which the
+    // kernel's loads travel: the less of it a CTA holds, the more bytes the SM keeps in flight.)
+    constexpr int RS = HI ? 16 : 8;
+    extern __shared__ float smem[];  // [SLOTS][RS][D] outputs, [SLOTS][RS][2] (m, l); fused: q [RS][D], k [D], v [D], cos [D/2], sin [D/2]
     float* o_s = smem;
-    float* ml_s = smem + SLOTS * 16 * D;
-    float* q_s = ml_s + SLOTS * 16 * 2;
-    float* k_s = q_s + 16 * D;
+    float* ml_s = smem + SLOTS * RS * D;
+    float* q_s = ml_s + SLOTS * RS * 2;
+    float* k_s = q_s + RS * D;
     float* v_s = k_s + D;
     float* cs_s = v_s + D;       // fused: cosine and sine of the step's position for each of the D/2 pairs
     float* sn_s = cs_s + D / 2;
@@ -300,7 +303,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
         l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
     }
-    float* ow = o_s + (size_t)warp * 16 * D;
+    float* ow = o_s + (size_t)warp * RS * D;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         ow[g * D + 8 * j + 2 * t] = o[j][0];
@@ -311,11 +314,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         }
     }
     if (t == 0) {
-        ml_s[(warp * 16 + g) * 2] = m_lo;
-        ml_s[(warp * 16 + g) * 2 + 1] = l_lo;
+        ml_s[(warp * RS + g) * 2] = m_lo;
+        ml_s[(warp * RS + g) * 2 + 1] = l_lo;
         if (HI) {
-            ml_s[(warp * 16 + g + 8) * 2] = m_hi;
-            ml_s[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+            ml_s[(warp * RS + g + 8) * 2] = m_hi;
+            ml_s[(warp * RS + g + 8) * 2 + 1] = l_hi;
         }
     }
     if (FUSED) {
@@ -353,7 +356,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
             }
         }
         __syncthreads();
-        for (int idx = warp; idx < 16; idx += kAttnDecodeWarps) {   // a warp per head: its lanes share the dimensions
+        for (int idx = warp; idx < RS; idx += kAttnDecodeWarps) {   // a warp per head: its lanes share the dimensions
             float sc = -INFINITY;
             if (mine && idx < group) {
                 float dot = 0.f;
@@ -363,26 +366,26 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
                 sc = dot * inv_sqrt_d;
             }
             if (lane == 0) {
-                ml_s[(kAttnDecodeWarps * 16 + idx) * 2] = sc;
-                ml_s[(kAttnDecodeWarps * 16 + idx) * 2 + 1] = mine && idx < group ? 1.f : 0.f;
+                ml_s[(kAttnDecodeWarps * RS + idx) * 2] = sc;
+                ml_s[(kAttnDecodeWarps * RS + idx) * 2 + 1] = mine && idx < group ? 1.f : 0.f;
             }
         }
         for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads)
-            o_s[(size_t)kAttnDecodeWarps * 16 * D + idx] = mine ? v_s[idx % D] : 0.f;
+            o_s[(size_t)kAttnDecodeWarps * RS * D + idx] = mine ? v_s[idx % D] : 0.f;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < group * D; idx += kAttnDecodeThreads) {
         const int row = idx / D, d = idx % D;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < SLOTS; ++w) m = fmaxf(m, ml_s[(w * 16 + row) * 2]);
+        for (int w = 0; w < SLOTS; ++w) m = fmaxf(m, ml_s[(w * RS + row) * 2]);
         float l = 0.f, acc = 0.f;
 #pragma unroll
         for (int w = 0; w < SLOTS; ++w) {
-            const float mw = ml_s[(w * 16 + row) * 2];
+            const float mw = ml_s[(w * RS + row) * 2];
             const float f = mw == -INFINITY ? 0.f : expf(mw - m);
-            l += ml_s[(w * 16 + row) * 2 + 1] * f;
-            acc += o_s[((size_t)w * 16 + row) * D + d] * f;
+            l += ml_s[(w * RS + row) * 2 + 1] * f;
+            acc += o_s[((size_t)w * RS + row) * D + d] * f;
         }
         const int head = kvh * group + row;
         if (n_splits == 1) {
@@ -465,7 +468,8 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
     float* part_ml = scratch + (size_t)n_seqs * n_heads * n_splits * head_dim;
     dim3 grid(n_splits, n_kv_heads, n_seqs);
     const int slots = kAttnDecodeWarps + (fused ? 1 : 0);
-    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 19 * head_dim : 0));
+    const int tile_rows = group > 8 ? 16 : 8;   // rows of the tiles that exist (see the kernel)
+    const size_t smem = sizeof(float) * ((size_t)slots * tile_rows * (head_dim + 2) + (fused ? (tile_rows + 3) * head_dim : 0));
     auto qq = (const __nv_bfloat16*)q;
     auto kk = (__nv_bfloat16*)k_pool;
     auto vv = (__nv_bfloat16*)v_pool;
@@ -510,7 +514,8 @@ extern "C" int b200_attention_decode_ctas_per_sm(int head_dim, int group, int fu
     using namespace b200;
     if (group < 1 || group > 16 || head_dim % 32 != 0 || head_dim < 32 || head_dim > 128) return 0;
     const int slots = kAttnDecodeWarps + (fused ? 1 : 0);
-    const size_t smem = sizeof(float) * ((size_t)slots * 16 * (head_dim + 2) + (fused ? 19 * head_dim : 0));
+    const int tile_rows = group > 8 ? 16 : 8;   // rows of the tiles that exist (see the kernel)
+    const size_t smem = sizeof(float) * ((size_t)slots * tile_rows * (head_dim + 2) + (fused ? (tile_rows + 3) * head_dim : 0));
     int n = 0;
     cudaError_t e = cudaSuccess;
 #define B200_OCC_H(KB, F, HI)                                                                                          \
