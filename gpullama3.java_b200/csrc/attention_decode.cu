@@ -407,6 +407,34 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_heads + head
     const float* ml = part_ml + row * n_splits * 2;
+    if (n_splits <= 8) {
+        // everything a thread needs is asked for at once (one trip to L2 instead of one for the maxima and one for the
+        // rest); the arithmetic and its order are those of the general path below
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            float ms[8], ls[8], po[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool ok = j < n_splits;
+                ms[j] = ok ? ml[2 * j] : -INFINITY;
+                ls[j] = ok ? ml[2 * j + 1] : 0.f;
+                po[j] = ok ? part_o[(row * n_splits + j) * D + d] : 0.f;
+            }
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
+            float l = 0.f, acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < n_splits) {
+                    const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
+                    l += ls[j] * f;
+                    acc += po[j] * f;
+                }
+            }
+            out[row * D + d] = __float2bfloat16_rn(acc / l);
+        }
+        return;
+    }
     float m = -INFINITY;
     for (int s0 = 0; s0 < n_splits; s0 += 8) {
         float ms[8];
