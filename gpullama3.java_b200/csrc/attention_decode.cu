@@ -398,6 +398,34 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     }
 }
 
+template <int N>
+__device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ part_o, const float* __restrict__ ml,
+                                                    __nv_bfloat16* __restrict__ out, size_t row, int n_splits, int D) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float ms[N], ls[N], po[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            const bool ok = j < n_splits;
+            ms[j] = ok ? ml[2 * j] : -INFINITY;
+            ls[j] = ok ? ml[2 * j + 1] : 0.f;
+            po[j] = ok ? part_o[(row * n_splits + j) * D + d] : 0.f;
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < N; ++j) m = fmaxf(m, ms[j]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            if (j < n_splits) {
+                const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
+                l += ls[j] * f;
+                acc += po[j] * f;
+            }
+        }
+        out[row * D + d] = __float2bfloat16_rn(acc / l);
+    }
+}
+
 // One CTA per (sequence, head), one thread per dimension.  The partial results of up to 8 spans are requested
 // together before any is used (a loop over a run-time count of spans that loads, scales and adds one span at a time
 // pays one round trip to L2 per span); they are added in span order, so the sum is the same.
@@ -407,34 +435,10 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_heads + head
     const float* ml = part_ml + row * n_splits * 2;
-    if (n_splits <= 8) {
-        // everything a thread needs is asked for at once (one trip to L2 instead of one for the maxima and one for the
-        // rest); the arithmetic and its order are those of the general path below
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            float ms[8], ls[8], po[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool ok = j < n_splits;
-                ms[j] = ok ? ml[2 * j] : -INFINITY;
-                ls[j] = ok ? ml[2 * j + 1] : 0.f;
-                po[j] = ok ? part_o[(row * n_splits + j) * D + d] : 0.f;
-            }
-            float m = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
-            float l = 0.f, acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (j < n_splits) {
-                    const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
-                    l += ls[j] * f;
-                    acc += po[j] * f;
-                }
-            }
-            out[row * D + d] = __float2bfloat16_rn(acc / l);
-        }
-        return;
-    }
+    // up to 16 spans: everything a thread needs is asked for at once (one trip to L2 instead of one for the maxima and one
+    // for the rest, per group of 8 spans); the arithmetic and its order are those of the general path below
+    if (n_splits <= 8) { merge_spans_at_once<8>(part_o, ml, out, row, n_splits, D); return; }
+    if (n_splits <= 16) { merge_spans_at_once<16>(part_o, ml, out, row, n_splits, D); return; }
     float m = -INFINITY;
     for (int s0 = 0; s0 < n_splits; s0 += 8) {
         float ms[8];
