@@ -257,8 +257,9 @@ def test_gemm_generic_and_its_epilogues(a_dtype, w_dtype, M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32, 50, 64])
-@pytest.mark.parametrize("N, K", [(16, 32), (50, 96), (200, 2048), (4098, 64), (5000, 1056)])
+@pytest.mark.parametrize("N, K", [(16, 32), (50, 96), (200, 2048), (4098, 64), (5000, 1056), (2400, 1088)])
 def test_gemm_decode_and_its_epilogues(M, N, K):
+    # (2400 x 1088: the grid of up to three CTAs per SM whose rounds are six k-blocks, ending inside a round)
     o = ops()
     g = torch.Generator().manual_seed(M * N + K)
     a = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
