@@ -932,7 +932,7 @@ extern "C" int b200_attention_prefill_tc(const void* q, int q_row_stride, int n_
         !make_map_2d(&mk, k_pool, k_rows, head_dim, head_dim, 64, 64) || !make_map_2d(&mv, v_pool, v_rows, 64, 64, 64, head_dim))
         return kErrUnsupportedSize;
     // tiles in pairs when there are enough pairs to give every SM one (fewer: the single-tile kernel fills more SMs)
-    if (window <= 0 && (long long)((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows)) * n_heads * n_seqs >= 148) {
+    if (window <= 0 && (long long)((max_q_len + 2 * kFaRows - 1) / (2 * kFaRows)) * n_heads * n_seqs >= device_sm_count()) {
         if (head_dim == 64)
             return launch_pair<64>(mq, mk, mv, out, cu_seqlens, kv_lens, page_table, table_stride, n_seqs, max_q_len, n_heads,
                                    n_kv_heads, (int)k_rows, (int)v_rows, stream);

@@ -72,6 +72,18 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaPeekAtLastError(); }
 
+// SMs of the current device (asked once per device; 148, a B200's, only if the driver does not answer).
+inline int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cached[dev];
+}
+
 // Programmatic dependent launch.  A kernel launched with launch_pdl may start while its
 // predecessor on the stream is still running; it must call pdl_wait() before it touches anything a
 // predecessor wrote (or writes anything a predecessor reads).  What it does before that call

@@ -257,10 +257,10 @@ static int launch_one(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, i
     if (MTT * NT >= 8) B200_U(2);
     // 8-row CTAs of a short grid (at most two per SM) can afford twice the loads in flight; a longer grid
     // needs the registers for a third and fourth resident CTA instead
-    if (MT == 0 && NT == 1 && N <= 2 * 148 * 8) B200_U(((MT == 0 && NT == 1) ? 8 : 4));
+    if (MT == 0 && NT == 1 && N <= 2 * device_sm_count() * 8) B200_U(((MT == 0 && NT == 1) ? 8 : 4));
     // up to three CTAs per SM: six k-blocks in flight, where that saves rounds (hidden 3072: o in 2 rounds instead of 3,
     // down in 6 instead of 8; the 3B shape's step 2.21 -> 2.13 ms)
-    if (MT == 0 && NT == 1 && N <= 3 * 148 * 8 && (K / 32 + 47) / 48 < (K / 32 + 31) / 32)
+    if (MT == 0 && NT == 1 && N <= 3 * device_sm_count() * 8 && (K / 32 + 47) / 48 < (K / 32 + 31) / 32)
         B200_U(((MT == 0 && NT == 1) ? 6 : 4));
     B200_U(4);
 #undef B200_U

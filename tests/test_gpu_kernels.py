@@ -523,6 +523,18 @@ def test_gemm_skinny_and_its_epilogues(M, N, K, splits):
     assert not o.gemm_skinny(torch.zeros(129, K, dtype=torch.bfloat16, device="cuda"), w, torch.empty(129, N, device="cuda"))
 
 
+def test_decode_attention_reports_the_ctas_an_sm_holds():
+    """The spans of decode attention are planned for what the GPU holds at once: the occupancy of the kernel
+    for the head size (more for small heads than for large ones), 4 per SM as a stand-in for sizes that kernel
+    does not take."""
+    o = ops()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    small, large = o.resident_ctas("cuda:0", 64, 4), o.resident_ctas("cuda:0", 128, 4)
+    assert small % sms == 0 and large % sms == 0 and small >= large >= sms
+    assert o.resident_ctas("cuda:0", 48, 4) == 4 * sms            # no kernel for heads of 48: the stand-in
+    assert o.resident_ctas("cuda:0", 64, 16) >= sms               # groups of more than 8 heads: the full-tile variant
+
+
 @pytest.mark.parametrize("H, KVH, D, window", [(4, 2, 32, 0), (32, 8, 64, 0), (3, 1, 96, 0), (16, 1, 128, 0),
                                                (8, 8, 64, 0), (24, 2, 32, 0), (8, 2, 64, 100), (4, 1, 128, 33)])
 @pytest.mark.parametrize("n_splits", [1, 2, 3, 8, 16])
