@@ -41,7 +41,7 @@ extern "C" int b200_random_fill(void* out, int dtype, long long n, unsigned long
                                 cudaStream_t stream) {
     if (n <= 0) return 0;
     const long long want = (n + 255) / 256;
-    const unsigned int blocks = (unsigned int)(want < device_sm_count() * 32 ? want : device_sm_count() * 32);
+    const unsigned int blocks = (unsigned int)(want < b200::device_sm_count() * 32 ? want : b200::device_sm_count() * 32);
     B200_DISPATCH_DTYPE(dtype, T,
         b200::random_fill_kernel<T><<<blocks, 256, 0, stream>>>((T*)out, n, key, scale, offset));
     return b200::launch_status();
