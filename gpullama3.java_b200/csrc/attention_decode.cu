@@ -88,6 +88,49 @@ __device__ __forceinline__ float rotate_elem(const __nv_bfloat16* x, int d, int 
     return first ? v0 * cs - v1 * sn : v0 * sn + v1 * cs;
 }
 
+// How the n_seqs x n_splits CTAs of a kv head are shared out among the sequences.  Every sequence gets one span and a
+// share of the others in proportion to the blocks of 32 keys it reads, so that in a batch of unequal lengths the CTAs of
+// the longest sequence do not outlast all others (equal lengths: n_splits each, as if there were no plan).  The spans of
+// sequence i are numbered prefix_i .. prefix_i + count_i - 1 among all spans; partial results are stored under that
+// number, and the merge kernel evaluates the same plan.  Lengths are read before the dependency wait, like kv_lens[seq].
+constexpr int kSpanPlanMaxSeqs = 64;   // larger batches (whose grids fill the GPU with one or two spans) keep equal counts
+
+__device__ __forceinline__ int cached_blocks(const int* __restrict__ kv_lens, int i, int window, bool own_key_apart) {
+    const int kv_len = kv_lens[i];
+    const int lo = window > 0 ? max(0, kv_len - window) : 0;
+    const int n_cached = own_key_apart ? kv_len - 1 : kv_len;
+    return n_cached > lo ? (n_cached - 1) / 32 - lo / 32 + 1 : 0;
+}
+
+// prefix and count of sequence `seq` (find_cta < 0), or of the sequence that owns CTA number `find_cta`; false if that
+// CTA is left over (the counts are rounded down, so up to n_seqs CTAs of a kv head may be)
+__device__ __forceinline__ bool span_plan(const int* __restrict__ kv_lens, int n_seqs, int n_splits, int window,
+                                          bool own_key_apart, int seq, int find_cta, int& owner, int& prefix, int& count) {
+    bool planned = n_splits > 1 && n_seqs <= kSpanPlanMaxSeqs;
+    unsigned int total = 0;
+    if (planned) {
+        for (int i = 0; i < n_seqs; ++i) total += (unsigned int)cached_blocks(kv_lens, i, window, own_key_apart);
+        planned = total > 0 && total < (1u << 20);   // (the products below stay inside 32 bits)
+    }
+    if (!planned) {
+        owner = find_cta < 0 ? seq : find_cta / n_splits;
+        prefix = owner * n_splits;
+        count = n_splits;
+        return true;
+    }
+    const unsigned int spare = (unsigned int)n_seqs * (unsigned int)(n_splits - 1);
+    int at = 0;
+    bool found = false;
+    for (int i = 0; i < n_seqs; ++i) {
+        const int c = 1 + (int)((unsigned int)cached_blocks(kv_lens, i, window, own_key_apart) * spare / total);
+        if (find_cta < 0 ? i == seq : (find_cta >= at && find_cta < at + c)) {
+            owner = i; prefix = at; count = c; found = true;
+        }
+        at += c;
+    }
+    return found;
+}
+
 // KB: head_dim / 32.  FUSED: rotation and cache write of the step done here.  HI: the group has more than 8 heads,
 // so rows 8..15 of the tiles exist (without them a lane keeps half the sums, and more CTAs fit an SM).
 template <int KB, bool FUSED, bool HI>
@@ -112,18 +155,26 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     float* cs_s = v_s + D;       // fused: cosine and sine of the step's position for each of the D/2 pairs
     float* sn_s = cs_s + D / 2;
 
-    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int kvh = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int group = n_heads / n_kv_heads;
     pdl_launch_dependents();
     // Lengths and page tables were copied to the device before the step's first kernel started, so they are read
     // before the wait for the predecessor; the queries, the step's key and value and the cache are read after it.
+    // Which sequence this CTA works for, as which of its spans, and how many spans that sequence has:
+    int seq, span_first, span_count;
+    if (!span_plan(kv_lens, (int)gridDim.z, n_splits, window, FUSED && rope.write_cache, -1,
+                   (int)(blockIdx.z * gridDim.x + blockIdx.x), seq, span_first, span_count)) {
+        pdl_wait();   // (a CTA that is left over; it still waits, so that this kernel's end implies its predecessor's)
+        return;
+    }
+    const int split = (int)(blockIdx.z * gridDim.x + blockIdx.x) - span_first;
     const int kv_len = kv_lens[seq];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;
     // keys read from the cache: all of them, or all but the step's own when this kernel writes that one
     const int n_cached = (FUSED && rope.write_cache) ? kv_len - 1 : kv_len;
     const int first_block = lo / 32, last_block = n_cached > lo ? (n_cached - 1) / 32 : first_block - 1;
-    const int per_split = max(1, (last_block - first_block + 1 + n_splits - 1) / n_splits);
+    const int per_split = max(1, (last_block - first_block + 1 + span_count - 1) / span_count);
     const int blk_begin = first_block + split * per_split;
     const int blk_end = min(blk_begin + per_split, last_block + 1);
     const int* pages = page_table + (size_t)seq * table_stride;
@@ -324,7 +375,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
     if (FUSED) {
         // The step's own key and value.  The CTA of the last span stores them at the sequence's last position
         // and adds them to the softmax as one more partial: m = q.k / sqrt(d), l = 1, o = v.
-        const bool mine = rope.write_cache && split == n_splits - 1;
+        const bool mine = rope.write_cache && split == span_count - 1;
         if (mine) {
             const int pos = kv_len - 1;
             const __nv_bfloat16* row = q + (size_t)seq * q_row_stride;
@@ -391,24 +442,27 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, _
         if (n_splits == 1) {
             out[((size_t)seq * n_heads + head) * D + d] = __float2bfloat16_rn(acc / l);
         } else {
-            const size_t p = ((size_t)seq * n_heads + head) * n_splits + split;
+            const size_t p = (size_t)(span_first + split) * n_heads + head;
             part_o[p * D + d] = acc;
             if (d == 0) { part_ml[p * 2] = m; part_ml[p * 2 + 1] = l; }
         }
     }
 }
 
+// `first`: index of the row's first partial result; the next span's lies `stride` partials further.
 template <int N>
-__device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ part_o, const float* __restrict__ ml,
-                                                    __nv_bfloat16* __restrict__ out, size_t row, int n_splits, int D) {
+__device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                    __nv_bfloat16* __restrict__ out, size_t row, size_t first, size_t stride,
+                                                    int count, int D) {
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float ms[N], ls[N], po[N];
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-            const bool ok = j < n_splits;
-            ms[j] = ok ? ml[2 * j] : -INFINITY;
-            ls[j] = ok ? ml[2 * j + 1] : 0.f;
-            po[j] = ok ? part_o[(row * n_splits + j) * D + d] : 0.f;
+            const bool ok = j < count;
+            const size_t q = first + (size_t)j * stride;
+            ms[j] = ok ? part_ml[2 * q] : -INFINITY;
+            ls[j] = ok ? part_ml[2 * q + 1] : 0.f;
+            po[j] = ok ? part_o[q * D + d] : 0.f;
         }
         float m = -INFINITY;
 #pragma unroll
@@ -416,7 +470,7 @@ __device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ pa
         float l = 0.f, acc = 0.f;
 #pragma unroll
         for (int j = 0; j < N; ++j) {
-            if (j < n_splits) {
+            if (j < count) {
                 const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
                 l += ls[j] * f;
                 acc += po[j] * f;
@@ -426,42 +480,48 @@ __device__ __forceinline__ void merge_spans_at_once(const float* __restrict__ pa
     }
 }
 
-// One CTA per (sequence, head), one thread per dimension.  The partial results of up to 8 spans are requested
+// One CTA per (sequence, head), one thread per dimension.  The sequence's spans are found by the plan the attention
+// kernel followed (evaluated before the dependency wait).  The partial results of up to 8 spans are requested
 // together before any is used (a loop over a run-time count of spans that loads, scales and adds one span at a time
 // pays one round trip to L2 per span); they are added in span order, so the sum is the same.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+                                              __nv_bfloat16* __restrict__ out, const int* __restrict__ kv_lens, int n_heads,
+                                              int n_splits, int D, int window, int own_key_apart) {
     pdl_launch_dependents();
-    pdl_wait();
     const size_t row = blockIdx.x;  // seq * n_heads + head
-    const float* ml = part_ml + row * n_splits * 2;
+    const int seq = (int)(blockIdx.x / n_heads), head = (int)(blockIdx.x % n_heads);
+    int owner, span_first, count;
+    span_plan(kv_lens, (int)(gridDim.x / n_heads), n_splits, window, own_key_apart != 0, seq, -1, owner, span_first, count);
+    pdl_wait();
+    const size_t first = (size_t)span_first * n_heads + head, stride = (size_t)n_heads;
     // up to 16 spans: everything a thread needs is asked for at once (one trip to L2 instead of one for the maxima and one
     // for the rest, per group of 8 spans); the arithmetic and its order are those of the general path below
-    if (n_splits <= 8) { merge_spans_at_once<8>(part_o, ml, out, row, n_splits, D); return; }
-    if (n_splits <= 16) { merge_spans_at_once<16>(part_o, ml, out, row, n_splits, D); return; }
+    if (count <= 8) { merge_spans_at_once<8>(part_o, part_ml, out, row, first, stride, count, D); return; }
+    if (count <= 16) { merge_spans_at_once<16>(part_o, part_ml, out, row, first, stride, count, D); return; }
     float m = -INFINITY;
-    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+    for (int s0 = 0; s0 < count; s0 += 8) {
         float ms[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ms[j] = s0 + j < n_splits ? ml[2 * (s0 + j)] : -INFINITY;
+        for (int j = 0; j < 8; ++j) ms[j] = s0 + j < count ? part_ml[2 * (first + (size_t)(s0 + j) * stride)] : -INFINITY;
 #pragma unroll
         for (int j = 0; j < 8; ++j) m = fmaxf(m, ms[j]);
     }
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float l = 0.f, acc = 0.f;
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+        for (int s0 = 0; s0 < count; s0 += 8) {
             float ms[8], ls[8], po[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int s = s0 + j;
-                const bool ok = s < n_splits;
-                ms[j] = ok ? ml[2 * s] : -INFINITY;
-                ls[j] = ok ? ml[2 * s + 1] : 0.f;
-                po[j] = ok ? part_o[(row * n_splits + s) * D + d] : 0.f;
+                const int sp = s0 + j;
+                const bool ok = sp < count;
+                const size_t q = first + (size_t)sp * stride;
+                ms[j] = ok ? part_ml[2 * q] : -INFINITY;
+                ls[j] = ok ? part_ml[2 * q + 1] : 0.f;
+                po[j] = ok ? part_o[q * D + d] : 0.f;
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                if (s0 + j < n_splits) {
+                if (s0 + j < count) {
                     const float f = ms[j] == -INFINITY ? 0.f : expf(ms[j] - m);
                     l += ls[j] * f;
                     acc += po[j] * f;
@@ -535,7 +595,8 @@ static int launch_attention_decode(const void* q, int q_row_stride, void* out, c
 #undef B200_LAUNCH_H
     if (st != 0 || n_splits == 1) return st;
     return launch_pdl(attention_decode_merge_kernel, dim3(n_seqs * n_heads), dim3(head_dim <= 64 ? 64 : 128), 0, stream,
-                      (const float*)part_o, (const float*)part_ml, oo, n_splits, head_dim);
+                      (const float*)part_o, (const float*)part_ml, oo, kv_lens, n_heads, n_splits, head_dim, window,
+                      (fused && rope.write_cache) ? 1 : 0);
 }
 
 }  // namespace b200
