@@ -4,7 +4,8 @@
 // kernel is a stream of K and V pages from HBM.  One CTA takes (a span of keys, one kv head, one
 // sequence); the query heads that share the kv head (n_heads / n_kv_heads, up to 16) are the rows
 // of the tensor-core tiles, so each key and value is read once for all of them.  Long sequences
-// are cut into `n_splits` spans so that a small batch still fills the GPU; every span leaves an
+// are cut into spans so that a small batch still fills the GPU (`n_splits` per sequence on average;
+// a longer sequence of the batch gets more of them, see span_plan); every span leaves an
 // unnormalised partial (running max m, sum l, output o) in scratch memory and a second kernel
 // merges the spans in a fixed order (no atomics).  The mathematics is the reference's
 // (inference/InferenceCore.java:106-145 of the reference project): scores q.k / sqrt(d) over the
@@ -69,7 +70,8 @@ __device__ __forceinline__ uint4 keep_first(uint4 v, int n) {
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Partials in scratch: o [seq][head][split][d] floats, then ml [seq][head][split][2] floats.
+// Partials in scratch: o [span][head][d] floats, then ml [span][head][2] floats, `span` counted over all sequences
+// (n_seqs x n_splits of them at most; sequence i's are prefix_i .. prefix_i + count_i - 1 of span_plan).
 struct RopeArgs {            // what the fused variant needs beyond the plain one
     const float* inv_freq;   // [head_dim / 2]
     int pairing;             // 0: (2j, 2j+1); 1: (j, j + head_dim/2)
